@@ -1,0 +1,337 @@
+// GPTQ solve, part 1: act-order permutation, dead columns + dampening, and the factor
+// U (upper) with U^T U = (H + damp I)^-1, all on device in fp32.
+//
+// Factorisation.  Let J be the index reversal.  If J H J = L L^T (ordinary lower Cholesky)
+// then H = V V^T with V = J L J upper triangular, hence H^-1 = V^-T V^-1 and the wanted
+// factor is U = V^-1 = J L^-1 J (upper, positive diagonal, so it equals the upper Cholesky
+// factor of H^-1).  That is one Cholesky and one triangular inverse (2/3 K^3 flops) instead
+// of Cholesky, Cholesky-inverse and a second Cholesky (4/3 K^3).
+//   1. A = J H J                                   (reverse copy into the workspace)
+//   2. blocked right-looking Cholesky of A, 128-column blocks: diagonal block factored and
+//      inverted in shared memory by one CTA; panel and trailing updates are tile GEMMs
+//   3. blocked right-looking inverse X = L^-1 in place (rank-128 GEMM updates)
+//   4. U = J X J written over H, strictly lower part zeroed
+// A pivot <= 0 (or NaN) sets *status; the host then takes the reference's identity fallback.
+#include "common.cuh"
+#include "sgemm.cuh"
+
+namespace b200q {
+namespace solve {
+
+constexpr int NB = 128;
+
+// ---------------------------------------------------------------------------------------
+// act-order: stable descending rank by counting
+__global__ void __launch_bounds__(256) perm_kernel(const float* __restrict__ H, int64_t K, int64_t ldh,
+                                                   int32_t* __restrict__ perm) {
+  __shared__ float sd[1024];
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const float di = (i < K) ? H[i * ldh + i] : 0.0f;
+  int rank = 0;
+  for (int64_t j0 = 0; j0 < K; j0 += 1024) {
+    for (int t = threadIdx.x; t < 1024; t += blockDim.x) {
+      int64_t j = j0 + t;
+      sd[t] = (j < K) ? H[j * ldh + j] : -INFINITY;
+    }
+    __syncthreads();
+    if (i < K) {
+      const int lim = (int)min((int64_t)1024, K - j0);
+      for (int t = 0; t < lim; ++t) {
+        const float dj = sd[t];
+        rank += (dj > di) || (dj == di && (j0 + t) < i);
+      }
+    }
+    __syncthreads();
+  }
+  if (i < K) perm[rank] = (int32_t)i;
+}
+
+template <int DT>
+__global__ void gather_cols_kernel(const void* __restrict__ W, int64_t N, int64_t K, int64_t ldw,
+                                   const int32_t* __restrict__ perm, float* __restrict__ out, int64_t ldo) {
+  using E = Elem<DT>;
+  const int64_t total = N * K;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i / K, c = i - r * K;
+    int64_t src = perm ? (int64_t)perm[c] : c;
+    out[r * ldo + c] = E::load((const typename E::type*)W + r * ldw + src);
+  }
+}
+
+__global__ void permute_hessian_kernel(const float* __restrict__ H, int64_t K, int64_t ldh,
+                                       const int32_t* __restrict__ perm, float* __restrict__ out,
+                                       int64_t ldo) {
+  const int64_t total = K * K;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i / K, c = i - r * K;
+    out[r * ldo + c] = H[(int64_t)perm[r] * ldh + perm[c]];
+  }
+}
+
+template <int DT>
+__global__ void scatter_cols_kernel(const float* __restrict__ Wf, int64_t N, int64_t K, int64_t ldf,
+                                    const int32_t* __restrict__ perm, void* __restrict__ out, int64_t ldo) {
+  using E = Elem<DT>;
+  const int64_t total = N * K;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i / K, c = i - r * K;
+    int64_t dst = perm ? (int64_t)perm[c] : c;
+    E::store((typename E::type*)out + r * ldo + dst, Wf[r * ldf + c]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// dead columns and dampening
+__global__ void zero_dead_columns_kernel(const float* __restrict__ H, int64_t K, int64_t ldh,
+                                         float* __restrict__ W, int64_t N, int64_t ldf) {
+  // one warp per column; only dead columns touch W
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t c = warp; c < K; c += nwarps) {
+    if (H[c * ldh + c] == 0.0f)
+      for (int64_t r = lane; r < N; r += 32) W[r * ldf + c] = 0.0f;
+  }
+}
+__global__ void __launch_bounds__(1024) damp_kernel(float* __restrict__ H, int64_t K, int64_t ldh,
+                                                    float percdamp) {
+  __shared__ float s_part[32];
+  __shared__ float s_damp;
+  float sum = 0.0f;
+  for (int64_t i = threadIdx.x; i < K; i += blockDim.x) {
+    float d = H[i * ldh + i];
+    if (d == 0.0f) { d = 1.0f; H[i * ldh + i] = 1.0f; }
+    sum += d;
+  }
+  sum = warp_sum(sum);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = (threadIdx.x < (blockDim.x >> 5)) ? s_part[threadIdx.x] : 0.0f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) s_damp = percdamp * (v / (float)K);
+  }
+  __syncthreads();
+  const float damp = s_damp;
+  for (int64_t i = threadIdx.x; i < K; i += blockDim.x) H[i * ldh + i] += damp;
+}
+
+// ---------------------------------------------------------------------------------------
+// index reversal copies
+__global__ void reverse_in_kernel(const float* __restrict__ H, int64_t K, int64_t ldh,
+                                  float* __restrict__ A, int64_t lda) {
+  const int64_t total = K * K;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i / K, c = i - r * K;
+    A[r * lda + c] = H[(K - 1 - r) * ldh + (K - 1 - c)];
+  }
+}
+__global__ void reverse_out_kernel(const float* __restrict__ A, int64_t K, int64_t lda,
+                                   float* __restrict__ U, int64_t ldu) {
+  const int64_t total = K * K;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i / K, c = i - r * K;
+    U[r * ldu + c] = (c >= r) ? A[(K - 1 - r) * lda + (K - 1 - c)] : 0.0f;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Diagonal block: Cholesky of the n x n (n <= 128) block at A[k0,k0] in shared memory, L
+// written back (upper part of the block zeroed), L^-1 written to Dinv (128 x 128, zero padded).
+__global__ void __launch_bounds__(256) chol_diag_kernel(float* __restrict__ A, int64_t lda, int k0, int n,
+                                                        float* __restrict__ Dinv, int* __restrict__ status) {
+  extern __shared__ float sm[];
+  float* L = sm;                   // [NB][NB+1]
+  float* X = sm + NB * (NB + 1);   // [NB][NB+1]
+  const int tid = threadIdx.x;
+  constexpr int LD = NB + 1;
+  for (int idx = tid; idx < NB * NB; idx += blockDim.x) {
+    int r = idx / NB, c = idx - r * NB;
+    L[r * LD + c] = (r < n && c < n && c <= r) ? A[(int64_t)(k0 + r) * lda + (k0 + c)] : 0.0f;
+    X[r * LD + c] = 0.0f;
+  }
+  __syncthreads();
+  for (int j = 0; j < n; ++j) {
+    if (tid == 0) {
+      float d = L[j * LD + j];
+      if (!(d > 0.0f)) {  // also catches NaN
+        if (atomicCAS(status, 0, B200Q_NOT_POSITIVE_DEFINITE) == 0) status[1] = k0 + j + 1;
+        d = 1.0f;
+      }
+      L[j * LD + j] = sqrtf(d);
+    }
+    __syncthreads();
+    const float djj = L[j * LD + j];
+    for (int r = j + 1 + tid; r < n; r += blockDim.x) L[r * LD + j] = __fdiv_rn(L[r * LD + j], djj);
+    __syncthreads();
+    // trailing update of the lower triangle: L[r][c] -= L[r][j] * L[c][j], j < c <= r
+    const int m = n - j - 1;
+    for (int idx = tid; idx < m * m; idx += blockDim.x) {
+      int rr = idx / m, cc = idx - rr * m;
+      if (cc <= rr) {
+        int r = j + 1 + rr, c = j + 1 + cc;
+        L[r * LD + c] = fmaf(-L[r * LD + j], L[c * LD + j], L[r * LD + c]);
+      }
+    }
+    __syncthreads();
+  }
+  // inverse by forward substitution: thread c solves L x = e_c
+  if (tid < n) {
+    const int c = tid;
+    for (int r = c; r < n; ++r) {
+      float s = (r == c) ? 1.0f : 0.0f;
+      for (int k = c; k < r; ++k) s = fmaf(-L[r * LD + k], X[k * LD + c], s);
+      X[r * LD + c] = __fdiv_rn(s, L[r * LD + r]);
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < NB * NB; idx += blockDim.x) {
+    int r = idx / NB, c = idx - r * NB;
+    Dinv[idx] = X[r * LD + c];
+    if (r < n && c < n) A[(int64_t)(k0 + r) * lda + (k0 + c)] = L[r * LD + c];
+  }
+}
+
+// X[k,k] = Linv_kk
+__global__ void copy_block_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t ldd, int n) {
+  for (int idx = threadIdx.x + blockIdx.x * blockDim.x; idx < n * n; idx += blockDim.x * gridDim.x) {
+    int r = idx / n, c = idx - r * n;
+    dst[(int64_t)r * ldd + c] = src[r * NB + c];
+  }
+}
+
+static inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+}  // namespace solve
+}  // namespace b200q
+
+using namespace b200q;
+using namespace b200q::solve;
+
+extern "C" {
+
+int b200q_actorder_perm(const float* H, int64_t K, int64_t ldh, int32_t* perm, void* stream) {
+  if (!H || !perm || K <= 0 || ldh < K) return B200Q_ERR_ARG;
+  perm_kernel<<<(int)((K + 255) / 256), 256, 0, (cudaStream_t)stream>>>(H, K, ldh, perm);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_gather_columns_f32(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw, const int32_t* perm,
+                             float* Wf, int64_t ldf, void* stream) {
+  if (!W || !Wf || N <= 0 || K <= 0 || ldw < K || ldf < K) return B200Q_ERR_ARG;
+  int grid = grid_for((N * K + 255) / 256, 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (wdtype == B200Q_BF16) gather_cols_kernel<B200Q_BF16><<<grid, 256, 0, st>>>(W, N, K, ldw, perm, Wf, ldf);
+  else if (wdtype == B200Q_F32) gather_cols_kernel<B200Q_F32><<<grid, 256, 0, st>>>(W, N, K, ldw, perm, Wf, ldf);
+  else return B200Q_ERR_UNSUPPORTED;
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_permute_hessian(const float* H, int64_t K, int64_t ldh, const int32_t* perm, float* Hp, int64_t ldp,
+                          void* stream) {
+  if (!H || !perm || !Hp || K <= 0 || ldh < K || ldp < K || H == Hp) return B200Q_ERR_ARG;
+  permute_hessian_kernel<<<grid_for((K * K + 255) / 256, 8), 256, 0, (cudaStream_t)stream>>>(H, K, ldh, perm, Hp, ldp);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_scatter_columns_cast(const float* Wf, int64_t N, int64_t K, int64_t ldf, const int32_t* perm, void* out,
+                               int odtype, int64_t ldo, void* stream) {
+  if (!Wf || !out || N <= 0 || K <= 0 || ldf < K || ldo < K) return B200Q_ERR_ARG;
+  int grid = grid_for((N * K + 255) / 256, 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (odtype == B200Q_BF16) scatter_cols_kernel<B200Q_BF16><<<grid, 256, 0, st>>>(Wf, N, K, ldf, perm, out, ldo);
+  else if (odtype == B200Q_F32) scatter_cols_kernel<B200Q_F32><<<grid, 256, 0, st>>>(Wf, N, K, ldf, perm, out, ldo);
+  else return B200Q_ERR_UNSUPPORTED;
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_gptq_prepare(float* H, int64_t K, int64_t ldh, float* Wf, int64_t N, int64_t ldf, float percdamp,
+                       void* stream) {
+  if (!H || K <= 0 || ldh < K) return B200Q_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (Wf && N > 0) {
+    zero_dead_columns_kernel<<<grid_for((K * 32 + 255) / 256, 4), 256, 0, st>>>(H, K, ldh, Wf, N, ldf);
+    B200Q_LAUNCH_CHECK();
+  }
+  damp_kernel<<<1, 1024, 0, st>>>(H, K, ldh, percdamp);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+size_t b200q_gptq_factor_workspace_bytes(int64_t K) {
+  if (K <= 0) return 0;
+  int64_t lda = round_up(K, 32);
+  int64_t nb = (K + NB - 1) / NB;
+  return (size_t)(K * lda + nb * NB * NB) * sizeof(float);
+}
+
+int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* status, void* stream) {
+  if (!H || !workspace || !status || K <= 0 || ldh < K || K > (1 << 24)) return B200Q_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t lda = round_up(K, 32);
+  const int nb = (int)((K + NB - 1) / NB);
+  float* A = (float*)workspace;
+  float* Dinv = A + K * lda;  // nb blocks of 128 x 128
+  const size_t diag_smem = 2 * NB * (NB + 1) * sizeof(float);
+  B200Q_TRY(cudaFuncSetAttribute(chol_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)diag_smem));
+
+  reverse_in_kernel<<<grid_for((K * K + 255) / 256, 8), 256, 0, st>>>(H, K, ldh, A, lda);
+  B200Q_LAUNCH_CHECK();
+
+  // ---- Cholesky: A = L L^T (lower) ----
+  for (int k = 0; k < nb; ++k) {
+    const int k0 = k * NB;
+    const int n = (int)min((int64_t)NB, K - k0);
+    float* Dk = Dinv + (int64_t)k * NB * NB;
+    chol_diag_kernel<<<1, 256, diag_smem, st>>>(A, lda, k0, n, Dk, status);
+    B200Q_LAUNCH_CHECK();
+    const int rem = (int)(K - k0 - n);
+    if (rem <= 0) break;
+    float* P = A + (int64_t)(k0 + n) * lda + k0;  // panel below the diagonal block: rem x n
+    // P <- P * L_kk^-T   (out[r][c] = sum_m P[r][m] * Linv[c][m])
+    B200Q_TRY(sgemm::launch(sgemm::kNT, P, lda, Dk, NB, P, lda, rem, n, n, 1.0f, 0.0f, sgemm::kAllTiles, st));
+    // trailing: A22 -= P P^T on the lower block triangle
+    float* A22 = A + (int64_t)(k0 + n) * lda + (k0 + n);
+    B200Q_TRY(sgemm::launch(sgemm::kNT, P, lda, P, lda, A22, lda, rem, rem, n, -1.0f, 1.0f, sgemm::kLowerTiles, st));
+  }
+
+  // ---- inverse in place: X = L^-1 (lower) ----
+  for (int k = 0; k < nb; ++k) {
+    const int k0 = k * NB;
+    const int n = (int)min((int64_t)NB, K - k0);
+    float* Dk = Dinv + (int64_t)k * NB * NB;
+    float* rowk = A + (int64_t)k0 * lda;  // X[k, 0:k0] accumulators, n x k0
+    if (k0 > 0) {
+      // X[k, :k0] <- Linv_kk * S[k, :k0]
+      B200Q_TRY(sgemm::launch(sgemm::kNN, Dk, NB, rowk, lda, rowk, lda, n, k0, n, 1.0f, 0.0f, sgemm::kAllTiles, st));
+    }
+    const int rem = (int)(K - k0 - n);
+    if (rem > 0) {
+      float* Lik = A + (int64_t)(k0 + n) * lda + k0;  // L[i,k] for i > k: rem x n
+      if (k0 > 0) {
+        // S[i, :k0] -= L[i,k] * X[k, :k0]
+        float* Si = A + (int64_t)(k0 + n) * lda;
+        B200Q_TRY(sgemm::launch(sgemm::kNN, Lik, lda, rowk, lda, Si, lda, rem, k0, n, -1.0f, 1.0f, sgemm::kAllTiles, st));
+      }
+      // S[i, k] = -L[i,k] * Linv_kk   (in place on the panel)
+      B200Q_TRY(sgemm::launch(sgemm::kNN, Lik, lda, Dk, NB, Lik, lda, rem, n, n, -1.0f, 0.0f, sgemm::kAllTiles, st));
+    }
+    copy_block_kernel<<<16, 256, 0, st>>>(Dk, A + (int64_t)k0 * lda + k0, lda, n);
+    B200Q_LAUNCH_CHECK();
+  }
+
+  reverse_out_kernel<<<grid_for((K * K + 255) / 256, 8), 256, 0, st>>>(A, K, lda, H, ldh);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,451 @@
+// GPTQ Hessian accumulation as a symmetric rank-k update on the 5th-generation tensor cores.
+//
+//   H_lower += alpha * X^T X        X: [T, K] bf16 row-major, H: [K, K] fp32
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer: 64-token x 64-column boxes of X into a 4-stage shared-memory
+//               ring (128-byte swizzle).  The contraction runs over tokens, so both operands
+//               are "MN-major": the contiguous dimension of X is the M / N dimension.
+//   warp 1      issues tcgen05.mma (M=128, N=256, K=16, bf16 in, fp32 accumulate in TMEM) and
+//               owns the TMEM allocation (2 accumulators x 256 columns = all 512 columns).
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, scale by alpha, add into H.
+// Work units are (128 x 256 tile on or below the diagonal) x (token split); with more than one
+// split the epilogue adds with red.global (fp32 atomics), otherwise with plain load/add/store.
+//
+// Every wait on an mbarrier is bounded: on expiry the kernel records a status, lets copies in
+// flight land, frees TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace b200q {
+namespace syrk {
+
+constexpr int kTileM = 128;        // rows of H per tile
+constexpr int kTileN = 256;        // columns of H per tile
+constexpr int kBlockT = 64;        // tokens per pipeline stage
+constexpr int kStages = 4;
+constexpr int kChunk = 64;         // columns per TMA box (128 bytes of bf16)
+constexpr int kChunkBytes = kChunk * kBlockT * 2;            // 8 KiB
+constexpr int kABytes = (kTileM / kChunk) * kChunkBytes;     // 16 KiB
+constexpr int kBBytes = (kTileN / kChunk) * kChunkBytes;     // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;               // 48 KiB
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P1;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P1;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false if the barrier did not flip in time or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      if (status) atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+
+// Shared-memory matrix descriptor for an MN-major operand stored as 64-column chunks of
+// [tokens][64] bf16 rows (128 bytes) with the 128-byte swizzle:
+//   leading byte offset = distance between 64-column chunks, stride byte offset = distance
+//   between groups of 8 token rows (1024 bytes); version 1; layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D fp32, A and B bf16, both MN-major, M=128, N=256, dense.
+constexpr uint32_t kInstrDesc = (1u << 4)                     // c_format = F32
+                                | (1u << 7) | (1u << 10)      // a_format, b_format = BF16
+                                | (1u << 15) | (1u << 16)     // a_major, b_major = MN
+                                | ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+
+// Tile list: block row bi (128 rows) pairs with 256-column blocks bj <= bi/2.
+__device__ __forceinline__ void decode_tile(int idx, int& bi, int& bj) {
+  int b = 0, cum = 0;
+  while (true) {
+    int cnt = (b >> 1) + 1;
+    if (idx < cum + cnt) break;
+    cum += cnt;
+    ++b;
+  }
+  bi = b;
+  bj = idx - cum;
+}
+inline int num_tiles(int nb) {  // nb = number of 128-row blocks
+  int n = 0;
+  for (int b = 0; b < nb; ++b) n += (b >> 1) + 1;
+  return n;
+}
+
+struct Params {
+  float* H;
+  int64_t ldh;
+  int K;
+  int64_t T;
+  int tiles;
+  int splits;
+  int64_t tokens_per_split;  // multiple of kBlockT
+  float alpha;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+syrk_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment (swizzle atom)
+  unsigned char* aligned = smem_raw + (base - raw);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + kStages * kStageBytes);
+  // barrier layout: full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * kStages + 2 + b); };
+  __shared__ uint32_t s_tmem_base;
+  __shared__ volatile int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 4); }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&s_tmem_base)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = s_tmem_base;
+
+  const int total_units = p.tiles * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        int bi, bj;
+        decode_tile(u % p.tiles, bi, bj);
+        const int split = u / p.tiles;
+        const int64_t t_begin = (int64_t)split * p.tokens_per_split;
+        const int64_t t_end = min(p.T, t_begin + p.tokens_per_split);
+        const int iters = (int)((t_end - t_begin + kBlockT - 1) / kBlockT);
+        for (int it = 0; it < iters; ++it) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, &s_abort, p.status, 1)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), kStageBytes);
+          const uint32_t sa = base + stage * kStageBytes;
+          const int t0 = (int)(t_begin + (int64_t)it * kBlockT);
+#pragma unroll
+          for (int c = 0; c < kTileM / kChunk; ++c)
+            tma_load_2d(sa + c * kChunkBytes, &xmap, full_bar(stage), bi * kTileM + c * kChunk, t0);
+#pragma unroll
+          for (int c = 0; c < kTileN / kChunk; ++c)
+            tma_load_2d(sa + kABytes + c * kChunkBytes, &xmap, full_bar(stage),
+                        bj * kTileN + c * kChunk, t0);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    int stage = 0;
+    uint32_t phase = 0;
+    int local = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++local) {
+      const int split = u / p.tiles;
+      const int64_t t_begin = (int64_t)split * p.tokens_per_split;
+      const int64_t t_end = min(p.T, t_begin + p.tokens_per_split);
+      const int iters = (int)((t_end - t_begin + kBlockT - 1) / kBlockT);
+      if (iters <= 0) continue;
+      const int buf = local & 1;
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      if (!mbar_wait(acce_bar(buf), acc_phase ^ 1u, &s_abort, p.status, 2)) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kTileN);
+      for (int it = 0; it < iters; ++it) {
+        if (!mbar_wait(full_bar(stage), phase, &s_abort, p.status, 3)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (lane == 0) {
+          const uint32_t sa = base + stage * kStageBytes;
+#pragma unroll
+          for (int kk = 0; kk < kBlockT / 16; ++kk) {
+            const uint64_t da = make_desc(sa + kk * 2048, kChunkBytes, 1024);
+            const uint64_t db = make_desc(sa + kABytes + kk * 2048, kChunkBytes, 1024);
+            tcgen05_mma_bf16(d_tmem, da, db, kInstrDesc, (it | kk) ? 1u : 0u);
+          }
+          tcgen05_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (it == iters - 1) tcgen05_commit(accf_bar(buf));
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int local = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++local) {
+      int bi, bj;
+      decode_tile(u % p.tiles, bi, bj);
+      const int split = u / p.tiles;
+      const int64_t t_begin = (int64_t)split * p.tokens_per_split;
+      const int64_t t_end = min(p.T, t_begin + p.tokens_per_split);
+      if (t_end <= t_begin) continue;
+      const int buf = local & 1;
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      if (!mbar_wait(accf_bar(buf), acc_phase, &s_abort, p.status, 4)) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = bi * kTileM + q * 32 + lane;
+      const int col_base = bj * kTileN;
+      const int row_blk_end = bi * kTileM + kTileM;  // columns >= this belong to the upper part
+#pragma unroll 1
+      for (int c = 0; c < kTileN / 32; ++c) {
+        const int col0 = col_base + c * 32;
+        if (col0 >= row_blk_end || col0 >= p.K) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTileN + c * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < p.K) {
+          float* dst = p.H + (int64_t)row * p.ldh + col0;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            if (col0 + v * 4 < p.K) {
+              float a = __uint_as_float(r[4 * v]) * p.alpha, b = __uint_as_float(r[4 * v + 1]) * p.alpha;
+              float cc = __uint_as_float(r[4 * v + 2]) * p.alpha, d = __uint_as_float(r[4 * v + 3]) * p.alpha;
+              if (p.splits > 1) {
+                red_add_v4(dst + 4 * v, a, b, cc, d);
+              } else {
+                float4 h = *reinterpret_cast<float4*>(dst + 4 * v);
+                h.x += a; h.y += b; h.z += cc; h.w += d;
+                *reinterpret_cast<float4*>(dst + 4 * v) = h;
+              }
+            }
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acce_bar(buf));
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  if (s_abort) {
+    // let TMA copies and MMAs already issued drain before shared memory and TMEM are given up
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+}
+
+// H[i][j] = H[j][i] = scale * H[i][j] for j <= i, by 32x32 blocks through shared memory.
+__global__ void __launch_bounds__(256) finalize_kernel(float* __restrict__ H, int64_t K, int64_t ldh,
+                                                       float scale) {
+  __shared__ float tile[32][33];
+  const int nb = (int)((K + 31) / 32);
+  const int64_t nblk = (int64_t)nb * (nb + 1) / 2;
+  for (int64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+    // blk -> (bi >= bj)
+    int bi = (int)((sqrt(8.0 * (double)blk + 1.0) - 1.0) * 0.5);
+    while ((int64_t)bi * (bi + 1) / 2 > blk) --bi;
+    while ((int64_t)(bi + 1) * (bi + 2) / 2 <= blk) ++bi;
+    const int bj = (int)(blk - (int64_t)bi * (bi + 1) / 2);
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int r = ty; r < 32; r += 8) {
+      int64_t i = (int64_t)bi * 32 + r, j = (int64_t)bj * 32 + tx;
+      float v = 0.0f;
+      if (i < K && j < K) {
+        v = H[i * ldh + j] * scale;
+        if (bi != bj || j <= i) H[i * ldh + j] = v;
+      }
+      tile[r][tx] = v;
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+      // element (j-block row r, i-block col tx) of the mirrored block
+      int64_t j = (int64_t)bj * 32 + r, i = (int64_t)bi * 32 + tx;
+      if (i < K && j < K && (bi != bj || j < i)) H[j * ldh + i] = tile[tx][r];
+    }
+    __syncthreads();
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+}  // namespace syrk
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* H, int64_t ldh,
+                       float alpha, int* status, void* stream) {
+  using namespace b200q::syrk;
+  if (!X || !H || T < 0 || K <= 0 || ldx < K || ldh < K) return B200Q_ERR_ARG;
+  if (K % 8 || ldx % 8 || ((uintptr_t)X) % 16 || ((uintptr_t)H) % 16 || ldh % 4) return B200Q_ERR_ARG;
+  if (T == 0) return B200Q_OK;
+  if (K > (1 << 20) || T > (int64_t)2000000000) return B200Q_ERR_UNSUPPORTED;
+  EncodeTiledFn encode = get_encode_fn();
+  if (!encode) { set_last_error("cuTensorMapEncodeTiled entry point", cudaErrorUnknown); return B200Q_ERR_CUDA; }
+
+  CUtensorMap map;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)T};
+  cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kChunk, (cuuint32_t)kBlockT};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(X), dims, strides, box,
+                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) { set_last_error("cuTensorMapEncodeTiled", cudaErrorInvalidValue); return B200Q_ERR_CUDA; }
+
+  Params p;
+  p.H = H; p.ldh = ldh; p.K = (int)K; p.T = T; p.alpha = alpha; p.status = status;
+  const int nb = (int)((K + kTileM - 1) / kTileM);
+  p.tiles = num_tiles(nb);
+  // token splits: enough units to fill the machine several times over, each split long enough
+  // (>= 512 tokens) to hide its epilogue behind the next unit's main loop
+  const int64_t max_splits = (T + 511) / 512;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= (int)(max_splits < 64 ? max_splits : 64); ++s) {
+    int64_t units = (int64_t)p.tiles * s;
+    int64_t waves = (units + kNumSMs - 1) / kNumSMs;
+    double eff = (double)units / (double)(waves * kNumSMs);
+    // prefer fewer splits unless the gain is real (atomics + epilogues are not free)
+    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+  }
+  p.splits = best;
+  int64_t tps = (T + p.splits - 1) / p.splits;
+  p.tokens_per_split = ((tps + kBlockT - 1) / kBlockT) * kBlockT;
+
+  cudaStream_t st = (cudaStream_t)stream;
+  B200Q_TRY(cudaFuncSetAttribute(syrk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  int64_t units = (int64_t)p.tiles * p.splits;
+  int grid = (int)(units < kNumSMs ? units : kNumSMs);
+  syrk_kernel<<<grid, kThreads, kSmemBytes, st>>>(map, p);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_hessian_finalize(float* H, int64_t K, int64_t ldh, float scale, void* stream) {
+  if (!H || K <= 0 || ldh < K) return B200Q_ERR_ARG;
+  int64_t nb = (K + 31) / 32;
+  int64_t nblk = nb * (nb + 1) / 2;
+  b200q::syrk::finalize_kernel<<<grid_for(nblk, 8), 256, 0, (cudaStream_t)stream>>>(H, K, ldh, scale);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+}  // extern "C"

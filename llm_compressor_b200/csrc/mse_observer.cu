@@ -1,0 +1,264 @@
+// MSE shrink-grid observer: all shrink candidates evaluated in one pass over the weight.
+//
+// For each group the elements stay in registers (GROUP strategies) or shared memory
+// (CHANNEL) while every candidate p = 1 - i/grid is tried: qparams from (p*min, p*max),
+// fake-quantise, sum |q - x|^norm, keep the strictly smallest.  Arithmetic is done in the
+// weight's dtype step by step (bf16 weights: every elementwise result is rounded to bf16,
+// sums are accumulated in float32 and rounded once), like the element-wise torch ops of the
+// reference.  The reference stops the whole search once `patience` consecutive candidates
+// improved no group anywhere; pass 1 records per candidate whether any group improved, a
+// one-thread kernel derives the stopping step, and pass 2 (a no-op unless the search stops
+// early) repeats the search up to that step.
+#include "common.cuh"
+
+namespace b200q {
+namespace mse {
+
+struct Cfg {
+  int symmetric, scale_kind, zp_kind, mx_offset;
+  float qmin, qmax, half_range, range, eps;
+  int kind;
+  int steps, patience;
+  float grid, norm, expand;
+};
+
+// qparams of calculate_qparams without a global scale, in dtype T (TB: bf16).
+template <bool TB>
+__device__ __forceinline__ void qparams_local(float mn, float mx, const Cfg& c, float& s, float& zp) {
+  mn = fminf(mn, 0.0f);
+  mx = fmaxf(mx, 0.0f);
+  if (c.symmetric) {
+    float amax = fmaxf(fabsf(mn), fabsf(mx));
+    if (c.scale_kind == B200Q_SCALE_E8M0) {
+      int biased;
+      if (TB) { uint32_t b = __float_as_uint(amax) >> 16; b = (b + 32u) & 0xFF80u; biased = (int)((b >> 7) & 0xFFu); }
+      else { uint32_t b = __float_as_uint(amax); b = (b + (1u << 21)) & 0xFF800000u; biased = (int)((b >> 23) & 0xFFu); }
+      float e = (biased == 0) ? 0.0f : fminf(fmaxf((float)(biased - c.mx_offset), 0.0f), 255.0f);
+      s = __uint_as_float(e >= 1.0f ? ((uint32_t)e << 23) : 0x00400000u);
+    } else {
+      s = rnd_if<TB>(__fdiv_rn(amax, c.half_range));
+      if (c.scale_kind == B200Q_SCALE_FP8) s = e4m3_round(fminf(fmaxf(s, -448.0f), 448.0f));
+    }
+    zp = 0.0f;
+  } else {
+    float d = rnd_if<TB>(mx - mn);
+    s = rnd_if<TB>(__fdiv_rn(d, c.range));
+    float z = rnd_if<TB>(__fdiv_rn(mn, s));
+    z = rnd_if<TB>(c.qmin - z);
+    z = fminf(fmaxf(z, c.qmin), c.qmax);
+    zp = (z != z) ? 0.0f : z;
+  }
+  if (s == 0.0f) s = c.eps;
+  if (c.zp_kind == B200Q_ZP_INT8) zp = rintf(fminf(fmaxf(zp, -128.0f), 127.0f));
+  else if (c.zp_kind == B200Q_ZP_UINT8) zp = rintf(fminf(fmaxf(zp, 0.0f), 255.0f));
+  else zp = e4m3_round(fminf(fmaxf(zp, -448.0f), 448.0f));
+}
+
+template <bool TB>
+__device__ __forceinline__ float elem_error(float x, float s, float z, const Cfg& c) {
+  QRange qr{c.qmin, c.qmax, c.kind};
+  float q = quant_code<TB>(x, s, z, qr);
+  float fq = dequant_code<TB>(q, s, z);
+  float d = rnd_if<TB>(fabsf(rnd_if<TB>(fq - x)));
+  float e = (d == 0.0f) ? 0.0f : powf(d, c.norm);
+  return rnd_if<TB>(e);
+}
+
+__device__ __forceinline__ float shrink_factor(int i, float grid) {
+  return (float)(1.0 - (double)i / (double)grid);
+}
+
+// ctl[0] = number of steps to run, ctl[1..] = per-step "some group improved" flags
+template <int DT>
+__global__ void __launch_bounds__(256) mse_group_kernel(const void* __restrict__ W, int64_t N, int64_t K,
+                                                        int64_t ldw, int g, Cfg c, int* __restrict__ ctl,
+                                                        int pass, void* __restrict__ mn_out,
+                                                        void* __restrict__ mx_out) {
+  using E = Elem<DT>;
+  using T = typename E::type;
+  constexpr bool TB = E::is_bf16;
+  const int limit = (pass == 0) ? c.steps : ctl[0];
+  if (pass == 1 && limit >= c.steps) return;  // the search never stopped early
+  const int lanes = g >> 3;
+  const int64_t cpr = K >> 3, total = N * cpr, gpr = K / g;
+  for (int64_t ch = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; ch < ((total + 31) & ~31LL);
+       ch += (int64_t)gridDim.x * blockDim.x) {
+    const bool live = ch < total;
+    float v[8];
+    float lo = INFINITY, hi = -INFINITY;
+    int64_t row = 0, cc = 0;
+    if (live) {
+      row = ch / cpr; cc = ch - row * cpr;
+      const T* src = (const T*)W + row * ldw + cc * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { v[i] = E::load(src + i); lo = fminf(lo, v[i]); hi = fmaxf(hi, v[i]); }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    }
+    for (int o = lanes >> 1; o > 0; o >>= 1) {
+      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    const float mn = rnd_if<TB>(lo * c.expand), mx = rnd_if<TB>(hi * c.expand);
+    float best_err = TB ? 3.3895313892515355e38f : 3.402823466e38f;  // finfo(dtype).max
+    float best_mn = mn, best_mx = mx;
+    for (int i = 0; i < limit; ++i) {
+      const float p = shrink_factor(i, c.grid);
+      const float smn = rnd_if<TB>(mn * p), smx = rnd_if<TB>(mx * p);
+      float s, z;
+      qparams_local<TB>(smn, smx, c, s, z);
+      float err = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) err += elem_error<TB>(v[e], s, z, c);
+      for (int o = lanes >> 1; o > 0; o >>= 1) err += __shfl_xor_sync(0xffffffffu, err, o);
+      err = rnd_if<TB>(err);
+      if (live && err < best_err) {
+        best_err = err; best_mn = smn; best_mx = smx;
+        if (pass == 0 && (cc % lanes) == 0 && ((volatile int*)ctl)[1 + i] == 0) atomicOr(&ctl[1 + i], 1);
+      }
+    }
+    if (live && (cc % lanes) == 0) {
+      int64_t gi = row * gpr + (cc * 8) / g;
+      E::store((T*)mn_out + gi, best_mn);
+      E::store((T*)mx_out + gi, best_mx);
+    }
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256) mse_channel_kernel(const void* __restrict__ W, int64_t N, int64_t K,
+                                                          int64_t ldw, Cfg c, int* __restrict__ ctl, int pass,
+                                                          void* __restrict__ mn_out, void* __restrict__ mx_out) {
+  using E = Elem<DT>;
+  using T = typename E::type;
+  constexpr bool TB = E::is_bf16;
+  extern __shared__ float srow[];
+  __shared__ float s_a[8], s_b[8];
+  __shared__ float s_bc[2];
+  const int limit = (pass == 0) ? c.steps : ctl[0];
+  if (pass == 1 && limit >= c.steps) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int64_t row = blockIdx.x; row < N; row += gridDim.x) {
+    float lo = INFINITY, hi = -INFINITY;
+    for (int64_t x = threadIdx.x; x < K; x += blockDim.x) {
+      float v = E::load((const T*)W + row * ldw + x);
+      srow[x] = v; lo = fminf(lo, v); hi = fmaxf(hi, v);
+    }
+    lo = warp_min(lo); hi = warp_max(hi);
+    if (lane == 0) { s_a[warp] = lo; s_b[warp] = hi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < nw; ++w) { lo = fminf(lo, s_a[w]); hi = fmaxf(hi, s_b[w]); }
+      s_bc[0] = lo; s_bc[1] = hi;
+    }
+    __syncthreads();
+    const float mn = rnd_if<TB>(s_bc[0] * c.expand), mx = rnd_if<TB>(s_bc[1] * c.expand);
+    float best_err = TB ? 3.3895313892515355e38f : 3.402823466e38f;
+    float best_mn = mn, best_mx = mx;
+    for (int i = 0; i < limit; ++i) {
+      const float p = shrink_factor(i, c.grid);
+      const float smn = rnd_if<TB>(mn * p), smx = rnd_if<TB>(mx * p);
+      float s, z;
+      qparams_local<TB>(smn, smx, c, s, z);
+      float err = 0.0f;
+      for (int64_t x = threadIdx.x; x < K; x += blockDim.x) err += elem_error<TB>(srow[x], s, z, c);
+      err = warp_sum(err);
+      __syncthreads();
+      if (lane == 0) s_a[warp] = err;
+      __syncthreads();
+      float tot = 0.0f;
+      for (int w = 0; w < nw; ++w) tot += s_a[w];
+      tot = rnd_if<TB>(tot);
+      if (tot < best_err) {
+        best_err = tot; best_mn = smn; best_mx = smx;
+        if (pass == 0 && threadIdx.x == 0 && ((volatile int*)ctl)[1 + i] == 0) atomicOr(&ctl[1 + i], 1);
+      }
+    }
+    if (threadIdx.x == 0) {
+      E::store((T*)mn_out + row, best_mn);
+      E::store((T*)mx_out + row, best_mx);
+    }
+    __syncthreads();
+  }
+}
+
+// ctl[0] <- number of candidates the reference's loop evaluates before it breaks
+__global__ void stop_step_kernel(int* ctl, int steps, int patience) {
+  int stale = 0, run = steps;
+  for (int i = 0; i < steps; ++i) {
+    if (ctl[1 + i]) stale = 0;
+    else if (++stale >= patience) { run = i + 1; break; }
+  }
+  ctl[0] = run;
+}
+__global__ void clear_ctl_kernel(int* ctl, int n) {
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ctl[i] = 0;
+}
+
+}  // namespace mse
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+size_t b200q_observe_mse_workspace_bytes(int64_t, int64_t, const b200q_qargs*, int steps) {
+  return sizeof(int) * (size_t)(steps + 1 > 1 ? steps + 1 : 1);
+}
+
+int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw, const b200q_qargs* qa,
+                      float maxshrink, int patience, float grid, float norm, float expand, void* mn_out,
+                      void* mx_out, void* scratch, void* stream) {
+  using namespace b200q::mse;
+  if (!W || !qa || !mn_out || !mx_out || !scratch || N <= 0 || K <= 0 || ldw < K) return B200Q_ERR_ARG;
+  if (wdtype != B200Q_BF16 && wdtype != B200Q_F32) return B200Q_ERR_UNSUPPORTED;
+  QRange qr;
+  int rc = make_qrange(qa, &qr); if (rc) return rc;
+  Cfg c;
+  c.symmetric = qa->symmetric; c.scale_kind = qa->scale_kind; c.zp_kind = qa->zp_kind;
+  c.mx_offset = (qa->num_bits == 4) ? 2 : 8;
+  c.qmin = qr.qmin; c.qmax = qr.qmax; c.range = qr.qmax - qr.qmin; c.half_range = c.range / 2.0f; c.kind = qr.kind;
+  if (!qa->symmetric && qr.kind == kFp4) return B200Q_ERR_UNSUPPORTED;
+  if (qa->scale_kind == B200Q_SCALE_FP8) c.eps = 0.125f;
+  else if (qa->scale_kind == B200Q_SCALE_E8M0) c.eps = 1.0f;
+  else c.eps = (wdtype == B200Q_BF16) ? 0.0078125f : 1.1920928955078125e-07f;
+  c.steps = (int)((double)maxshrink * (double)grid);
+  c.patience = patience; c.grid = grid; c.norm = norm; c.expand = expand;
+  if (c.steps < 0) return B200Q_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  int* ctl = (int*)scratch;
+  clear_ctl_kernel<<<1, 128, 0, st>>>(ctl, c.steps + 1);
+  B200Q_LAUNCH_CHECK();
+  const bool grp = qa->strategy == B200Q_GROUP || qa->strategy == B200Q_TENSOR_GROUP;
+  for (int pass = 0; pass < 2; ++pass) {
+    if (grp) {
+      int g = qa->group_size;
+      if (!(g >= 8 && g <= 256 && (g & (g - 1)) == 0 && K % g == 0)) return B200Q_ERR_UNSUPPORTED;
+      int grid_sz = grid_for((N * (K >> 3) + 255) / 256, 4);
+      if (wdtype == B200Q_BF16) mse_group_kernel<B200Q_BF16><<<grid_sz, 256, 0, st>>>(W, N, K, ldw, g, c, ctl, pass, mn_out, mx_out);
+      else mse_group_kernel<B200Q_F32><<<grid_sz, 256, 0, st>>>(W, N, K, ldw, g, c, ctl, pass, mn_out, mx_out);
+    } else if (qa->strategy == B200Q_CHANNEL) {
+      size_t smem = (size_t)K * sizeof(float);
+      if (smem > 200 * 1024) return B200Q_ERR_UNSUPPORTED;
+      int grid_sz = grid_for(N, smem > 100 * 1024 ? 1 : 2);
+      if (wdtype == B200Q_BF16) {
+        B200Q_TRY(cudaFuncSetAttribute(mse_channel_kernel<B200Q_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        mse_channel_kernel<B200Q_BF16><<<grid_sz, 256, smem, st>>>(W, N, K, ldw, c, ctl, pass, mn_out, mx_out);
+      } else {
+        B200Q_TRY(cudaFuncSetAttribute(mse_channel_kernel<B200Q_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        mse_channel_kernel<B200Q_F32><<<grid_sz, 256, smem, st>>>(W, N, K, ldw, c, ctl, pass, mn_out, mx_out);
+      }
+    } else {
+      return B200Q_ERR_UNSUPPORTED;
+    }
+    B200Q_LAUNCH_CHECK();
+    if (pass == 0) {
+      stop_step_kernel<<<1, 1, 0, st>>>(ctl, c.steps, c.patience);
+      B200Q_LAUNCH_CHECK();
+    }
+  }
+  return B200Q_OK;
+}
+
+}  // extern "C"

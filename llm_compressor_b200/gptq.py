@@ -1,0 +1,148 @@
+"""GPTQ math functions with the reference's names and contracts, on b200q kernels.
+
+Drop-in for ``make_empty_hessian`` / ``accumulate_hessian`` / ``quantize_weight`` of
+src/llmcompressor/modifiers/gptq/gptq_quantize.py (:19-25, :28-64, :67-264).
+"""
+from __future__ import annotations
+
+import math
+import warnings
+
+import torch
+
+from . import _lib, ops
+from .observers import Observer
+from .quant_args import QuantizationArgs
+
+__all__ = ["make_empty_hessian", "accumulate_hessian", "accumulate_hessian_lower",
+           "finalize_hessian", "quantize_weight", "GPTQ_PRECISION"]
+
+GPTQ_PRECISION = torch.float32
+
+
+def make_empty_hessian(module: torch.nn.Module, device=None) -> torch.Tensor:
+    weight = module.weight
+    num_columns = weight.shape[1]
+    device = device if device is not None else weight.device
+    return torch.zeros((num_columns, num_columns), device=device, dtype=GPTQ_PRECISION)
+
+
+def _tokens_2d(inp: torch.Tensor, device) -> tuple[torch.Tensor, int]:
+    """[B,S,K] / [S,K] / [B,...,K] activations -> ([tokens, K] bf16 contiguous rows, B)."""
+    inp = inp.to(device=device)
+    if inp.ndim == 2:
+        inp = inp.unsqueeze(0)
+    elif inp.ndim > 3:
+        inp = inp.reshape(inp.shape[0], -1, inp.shape[-1])
+    num_added = inp.shape[0]
+    x = inp.reshape(-1, inp.shape[-1])
+    if x.dtype != torch.bfloat16:
+        # the kernel contracts bf16 operands; float16/float32 activations are rounded once here
+        x = x.to(torch.bfloat16)
+    if x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    return x, num_added
+
+
+def accumulate_hessian_lower(inp: torch.Tensor, H: torch.Tensor, num_samples):
+    """Hook-path accumulation: H_lower += 2 X^T X (tiles on and below the diagonal only),
+    sample count += number of sequences.  ``finalize_hessian`` mirrors and normalises once,
+    before the solve.  ``num_samples`` may be a python number or a tensor."""
+    x, added = _tokens_2d(inp, H.device)
+    ops.hessian_syrk(x, H, alpha=2.0)
+    num_samples += added
+    return H, num_samples
+
+
+def finalize_hessian(H: torch.Tensor, num_samples) -> torch.Tensor:
+    """Mirror the lower triangle and divide by the sample count (base.py:336), in place."""
+    n = float(num_samples)
+    ops.hessian_finalize(H, 1.0 / n if n else 1.0)
+    return H
+
+
+def accumulate_hessian(inp, module, H, num_samples):
+    """Same contract as the reference: mutates and returns (H, num_samples) with H the full
+    symmetric matrix after every call.  Only Linear-like modules (weight [out, in]) are
+    handled; the sample count grows by the number of sequences, not tokens."""
+    if isinstance(module, torch.nn.Conv2d):
+        raise NotImplementedError("Conv2d Hessians are outside this package's path")
+    H, num_samples = accumulate_hessian_lower(inp, H, num_samples)
+    ops.hessian_finalize(H, 1.0)
+    return H, num_samples
+
+
+def quantize_weight(module, quant_args, hessian: torch.Tensor, blocksize: int = 128,
+                    percdamp: float = 0.01):
+    """GPTQ-quantise ``module.weight`` given its Hessian (already divided by the sample
+    count).  Returns ``(loss, dict)`` with the fake-quantised weight in the original dtype,
+    ``weight_scale``, ``weight_zero_point`` and, where they apply, ``weight_global_scale`` and
+    ``weight_g_idx``.  ``hessian`` is consumed.  ``module.weight_observer`` must hold
+    statistics unless act-order "group" re-observes; ``module.weight`` is not touched."""
+    args = QuantizationArgs.of(quant_args)
+    strategy, actorder = args.strategy, args.actorder
+    weight = module.weight.data if isinstance(module.weight, torch.nn.Parameter) else module.weight
+    final_dtype = weight.dtype
+    observer: Observer = module.weight_observer
+    N, K = weight.shape
+    H = hessian
+    if H.shape != (K, K) or H.dtype != torch.float32:
+        raise ValueError("hessian must be float32 [in_features, in_features]")
+    if strategy not in ("tensor", "channel", "group", "tensor_group", "block"):
+        raise ValueError(f"Quantization strategy is not supported for GPTQ: {strategy}")
+
+    if actorder == "group" and strategy not in ("group", "tensor_group"):
+        warnings.warn("ActivationOrdering.GROUP requires a grouped quantization strategy; "
+                      "falling back to actorder=None for this module.")
+        actorder = None
+
+    perm = None
+    if actorder:
+        perm = ops.actorder_perm(H)
+        W = ops.gather_columns_f32(weight, perm)
+        H = ops.permute_hessian(H, perm)
+    else:
+        W = ops.gather_columns_f32(weight, None)
+
+    if actorder == "group":
+        observer.delete_statistics(check_fused=False)
+        observer(W)
+
+    col_group = None
+    if strategy in ("group", "tensor_group", "block"):
+        divisor = args.group_size if strategy != "block" else args.block_structure[1]
+        g_idx = torch.arange(K, device=W.device, dtype=torch.int32) // divisor
+        if actorder == "weight":
+            g_idx = g_idx[perm.long()]
+            col_group = g_idx
+
+    qparams = observer.get_qparams()
+    scale, zero_point, global_scale = qparams["scale"], qparams["zero_point"], qparams["global_scale"]
+
+    ops.gptq_prepare(H, W, percdamp)
+    status = ops.gptq_factor(H)
+    U = H
+    if status == _lib.NOT_POSITIVE_DEFINITE:
+        warnings.warn(
+            "Failed to invert hessian due to numerical instability. Consider increasing "
+            "GPTQModifier.dampening_frac, increasing the number of calibration samples, or "
+            "shuffling the calibration dataset. Falling back to round-to-nearest for this module.")
+        U = None
+
+    losses = ops.gptq_sweep(W, U, scale, zero_point, args, blocksize=blocksize, col_group=col_group,
+                            global_scale=global_scale)
+
+    Wq = ops.scatter_columns_cast(W, final_dtype, perm)
+    loss = float(losses.sum().item())
+    out = {
+        "weight": Wq,
+        "weight_scale": scale.to(final_dtype),
+        "weight_zero_point": zero_point.to(args.zp_dtype),
+    }
+    if global_scale is not None:
+        out["weight_global_scale"] = global_scale.to(final_dtype)
+    if actorder == "group":
+        invperm = torch.empty_like(perm)
+        invperm[perm.long()] = torch.arange(K, device=perm.device, dtype=perm.dtype)
+        out["weight_g_idx"] = g_idx[invperm.long()]
+    return loss, out

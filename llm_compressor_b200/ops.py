@@ -1,0 +1,315 @@
+"""torch-tensor front end of the C-ABI kernels: one function per entry point.
+
+torch is used for device memory and the current stream only; every computation is a call
+into ``libb200q.so``.  All tensors must live on a CUDA device.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import check, ptr, stream_ptr
+from .quant_args import QuantizationArgs
+
+_DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"b200q kernels take bfloat16 or float32 tensors, got {t.dtype}") from None
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _lib.B200QError("b200q kernels need CUDA tensors; there is no CPU path")
+
+
+def _2d(w: torch.Tensor):
+    if w.ndim != 2 or w.stride(1) != 1:
+        raise ValueError("expected a 2-D tensor with contiguous rows")
+    return w.shape[0], w.shape[1], w.stride(0)
+
+
+def _zp_storage(args: QuantizationArgs):
+    return args.zp_dtype
+
+
+# ------------------------------------------------------------------------------ observers
+def observe_minmax(w: torch.Tensor, args: QuantizationArgs):
+    """(min_vals, max_vals) of qparam shape, in w's dtype."""
+    _need_cuda(w)
+    lib = _lib.load()
+    N, K, ld = _2d(w)
+    qa = args.c_struct()
+    shape = args.qparam_shape(N, K)
+    mn = torch.empty(shape, dtype=w.dtype, device=w.device)
+    mx = torch.empty(shape, dtype=w.dtype, device=w.device)
+    nbytes = lib.b200q_observe_minmax_workspace_bytes(N, K, qa)
+    scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=w.device)
+    check(lib.b200q_observe_minmax(ptr(w), _dt(w), N, K, ld, qa, ptr(mn), ptr(mx), ptr(scratch),
+                                   stream_ptr()), "b200q_observe_minmax")
+    return mn, mx
+
+
+def observe_mse(w, args, maxshrink=0.20, patience=5, grid=100.0, norm=2.4, expand=1.0):
+    _need_cuda(w)
+    lib = _lib.load()
+    N, K, ld = _2d(w)
+    if args.strategy == "tensor_group" and args.scale_dtype is not None:
+        args = args.model_copy(update={"scale_dtype": None})
+    qa = args.c_struct()
+    shape = args.qparam_shape(N, K)
+    mn = torch.empty(shape, dtype=w.dtype, device=w.device)
+    mx = torch.empty(shape, dtype=w.dtype, device=w.device)
+    steps = int(maxshrink * grid)
+    nbytes = lib.b200q_observe_mse_workspace_bytes(N, K, qa, steps)
+    scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=w.device)
+    check(lib.b200q_observe_mse(ptr(w), _dt(w), N, K, ld, qa, float(maxshrink), int(patience),
+                                float(grid), float(norm), float(expand), ptr(mn), ptr(mx),
+                                ptr(scratch), stream_ptr()), "b200q_observe_mse")
+    return mn, mx
+
+
+def absmax_accumulate(mn, mx, absmax: torch.Tensor):
+    _need_cuda(mn, mx, absmax)
+    assert absmax.dtype == torch.float32
+    check(_lib.load().b200q_absmax_accumulate(ptr(mn), ptr(mx), _dt(mn), mn.numel(), ptr(absmax),
+                                              stream_ptr()), "b200q_absmax_accumulate")
+
+
+def global_scale_from_absmax(absmax: torch.Tensor, stat_dtype: torch.dtype) -> torch.Tensor:
+    out = torch.empty(1, dtype=torch.float32, device=absmax.device)
+    check(_lib.load().b200q_global_scale_finalize(ptr(absmax), _DT[stat_dtype], ptr(out),
+                                                  stream_ptr()), "b200q_global_scale_finalize")
+    return out
+
+
+def qparams(mn, mx, args: QuantizationArgs, global_scale=None):
+    """(scale, zero_point) of the statistics' shape."""
+    _need_cuda(mn, mx, global_scale)
+    mn, mx = mn.contiguous(), mx.contiguous()
+    sdt = torch.float32 if global_scale is not None else mn.dtype
+    scale = torch.empty(mn.shape, dtype=sdt, device=mn.device)
+    zp = torch.empty(mn.shape, dtype=_zp_storage(args), device=mn.device)
+    check(_lib.load().b200q_qparams(ptr(mn), ptr(mx), _dt(mn), mn.numel(), args.c_struct(),
+                                    ptr(global_scale), ptr(scale), ptr(zp), stream_ptr()),
+          "b200q_qparams")
+    return scale, zp
+
+
+# ------------------------------------------------------------------------ quantize / pack
+def _prep_params(w, scale, zp, g_idx, global_scale):
+    _need_cuda(w, scale, zp, g_idx, global_scale)
+    scale = scale.contiguous()
+    zp = None if zp is None else zp.contiguous()
+    if g_idx is not None:
+        g_idx = g_idx.to(torch.int32).contiguous()
+        if bool((g_idx < 0).any()):
+            g_idx = None  # uninitialised g_idx means column order
+    if global_scale is not None:
+        global_scale = global_scale.to(torch.float32).contiguous()
+    return scale, zp, g_idx, global_scale
+
+
+def fake_quantize(w, scale, zp, args: QuantizationArgs, g_idx=None, global_scale=None):
+    scale, zp, g_idx, global_scale = _prep_params(w, scale, zp, g_idx, global_scale)
+    N, K, ld = _2d(w)
+    out = torch.empty((N, K), dtype=w.dtype, device=w.device)
+    check(_lib.load().b200q_fake_quantize(ptr(w), _dt(w), N, K, ld, ptr(scale), _dt(scale), ptr(zp),
+                                          ptr(g_idx), ptr(global_scale), args.c_struct(), ptr(out),
+                                          out.stride(0), stream_ptr()), "b200q_fake_quantize")
+    return out
+
+
+def quantize_pack(w, scale, zp, args: QuantizationArgs, g_idx=None, global_scale=None,
+                  pack_int8=False):
+    """Storage codes: int32 words (int4, or int8 with pack_int8), int8 / float8 bytes, or
+    uint8 nibble pairs (FP4)."""
+    scale, zp, g_idx, global_scale = _prep_params(w, scale, zp, g_idx, global_scale)
+    N, K, ld = _2d(w)
+    dev = w.device
+    if args.type == "int" and args.num_bits == 4:
+        out = torch.empty((N, -(-K // 8)), dtype=torch.int32, device=dev)
+    elif args.type == "int" and args.num_bits == 8:
+        out = (torch.empty((N, -(-K // 4)), dtype=torch.int32, device=dev) if pack_int8
+               else torch.empty((N, K), dtype=torch.int8, device=dev))
+    elif args.type == "float" and args.num_bits == 8:
+        out = torch.empty((N, K), dtype=torch.float8_e4m3fn, device=dev)
+    elif args.type == "float" and args.num_bits == 4:
+        out = torch.empty((N, K // 2), dtype=torch.uint8, device=dev)
+    else:
+        raise ValueError(f"unsupported code type {args.type}{args.num_bits}")
+    check(_lib.load().b200q_quantize_pack(ptr(w), _dt(w), N, K, ld, ptr(scale), _dt(scale), ptr(zp),
+                                          ptr(g_idx), ptr(global_scale), args.c_struct(),
+                                          int(pack_int8), ptr(out), stream_ptr()),
+          "b200q_quantize_pack")
+    return out
+
+
+def pack_zero_points(zp: torch.Tensor, num_bits: int) -> torch.Tensor:
+    _need_cuda(zp)
+    zp = zp.to(torch.int8).contiguous()
+    N, G = zp.shape
+    pf = 32 // num_bits
+    out = torch.empty((-(-N // pf), G), dtype=torch.int32, device=zp.device)
+    check(_lib.load().b200q_pack_zero_points(ptr(zp), N, G, num_bits, ptr(out), stream_ptr()),
+          "b200q_pack_zero_points")
+    return out
+
+
+def compress_scale(scale: torch.Tensor, kind: str) -> torch.Tensor:
+    """kind "fp8" -> float8_e4m3fn tensor, "e8m0" -> uint8 biased exponents."""
+    _need_cuda(scale)
+    scale = scale.contiguous()
+    out = torch.empty(scale.shape, dtype=torch.uint8, device=scale.device)
+    k = {"fp8": _lib.SCALE_FP8, "e8m0": _lib.SCALE_E8M0}[kind]
+    check(_lib.load().b200q_compress_scale(ptr(scale), _dt(scale), scale.numel(), k, ptr(out),
+                                           stream_ptr()), "b200q_compress_scale")
+    return out.view(torch.float8_e4m3fn) if kind == "fp8" else out
+
+
+def _code_buffer(args, N, K, dev):
+    if args.num_bits == 4:
+        if args.type == "int":
+            return torch.empty((N, K // 8), dtype=torch.int32, device=dev)
+        return torch.empty((N, K // 2), dtype=torch.uint8, device=dev)
+    if args.type == "int":
+        return torch.empty((N, K // 4), dtype=torch.int32, device=dev)
+    return torch.empty((N, K), dtype=torch.float8_e4m3fn, device=dev)
+
+
+def rtn_quantize_pack(w, args: QuantizationArgs):
+    """One pass: statistics -> qparams -> codes.  Returns dict(scale, zero_point,
+    scale_store, codes); int8 codes come packed four to an int32 word."""
+    _need_cuda(w)
+    N, K, ld = _2d(w)
+    dev = w.device
+    shape = args.qparam_shape(N, K)
+    scale = torch.empty(shape, dtype=w.dtype, device=dev)
+    zp = torch.empty(shape, dtype=_zp_storage(args), device=dev)
+    store = torch.empty(shape, dtype=torch.uint8, device=dev) if args.is_mx else None
+    out = _code_buffer(args, N, K, dev)
+    check(_lib.load().b200q_rtn_quantize_pack(ptr(w), _dt(w), N, K, ld, args.c_struct(), ptr(scale),
+                                              ptr(zp), ptr(store), ptr(out), stream_ptr()),
+          "b200q_rtn_quantize_pack")
+    return dict(scale=scale, zero_point=zp, scale_store=store, codes=out)
+
+
+def nvfp4_quantize_pack(w, global_scale: torch.Tensor):
+    _need_cuda(w, global_scale)
+    N, K, ld = _2d(w)
+    dev = w.device
+    scale = torch.empty((N, K // 16), dtype=w.dtype, device=dev)
+    store = torch.empty((N, K // 16), dtype=torch.uint8, device=dev)
+    out = torch.empty((N, K // 2), dtype=torch.uint8, device=dev)
+    gs = global_scale.to(torch.float32).contiguous()
+    check(_lib.load().b200q_nvfp4_quantize_pack(ptr(w), _dt(w), N, K, ld, ptr(gs), ptr(scale),
+                                                ptr(store), ptr(out), stream_ptr()),
+          "b200q_nvfp4_quantize_pack")
+    return dict(scale=scale, scale_store=store.view(torch.float8_e4m3fn), codes=out)
+
+
+# ------------------------------------------------------------------------------- Hessian
+def hessian_syrk(x: torch.Tensor, H: torch.Tensor, alpha: float = 2.0, status=None):
+    """H_lower += alpha * x^T x ; x [T,K] bf16 with contiguous rows."""
+    _need_cuda(x, H)
+    if x.dtype != torch.bfloat16:
+        raise TypeError("hessian_syrk takes bfloat16 activations")
+    T, K, ld = _2d(x)
+    assert H.dtype == torch.float32 and H.shape == (K, K) and H.stride(1) == 1
+    check(_lib.load().b200q_hessian_syrk(ptr(x), T, K, ld, ptr(H), H.stride(0), float(alpha),
+                                         ptr(status), stream_ptr()), "b200q_hessian_syrk")
+    return H
+
+
+def hessian_finalize(H: torch.Tensor, scale: float = 1.0):
+    _need_cuda(H)
+    K = H.shape[0]
+    check(_lib.load().b200q_hessian_finalize(ptr(H), K, H.stride(0), float(scale), stream_ptr()),
+          "b200q_hessian_finalize")
+    return H
+
+
+# ---------------------------------------------------------------------------- GPTQ solve
+def actorder_perm(H: torch.Tensor) -> torch.Tensor:
+    _need_cuda(H)
+    K = H.shape[0]
+    perm = torch.empty(K, dtype=torch.int32, device=H.device)
+    check(_lib.load().b200q_actorder_perm(ptr(H), K, H.stride(0), ptr(perm), stream_ptr()),
+          "b200q_actorder_perm")
+    return perm
+
+
+def gather_columns_f32(w: torch.Tensor, perm=None) -> torch.Tensor:
+    _need_cuda(w, perm)
+    N, K, ld = _2d(w)
+    out = torch.empty((N, K), dtype=torch.float32, device=w.device)
+    check(_lib.load().b200q_gather_columns_f32(ptr(w), _dt(w), N, K, ld, ptr(perm), ptr(out),
+                                               out.stride(0), stream_ptr()),
+          "b200q_gather_columns_f32")
+    return out
+
+
+def permute_hessian(H: torch.Tensor, perm: torch.Tensor) -> torch.Tensor:
+    _need_cuda(H, perm)
+    K = H.shape[0]
+    out = torch.empty_like(H)
+    check(_lib.load().b200q_permute_hessian(ptr(H), K, H.stride(0), ptr(perm), ptr(out),
+                                            out.stride(0), stream_ptr()), "b200q_permute_hessian")
+    return out
+
+
+def scatter_columns_cast(wf: torch.Tensor, dtype: torch.dtype, perm=None) -> torch.Tensor:
+    _need_cuda(wf, perm)
+    N, K, ld = _2d(wf)
+    out = torch.empty((N, K), dtype=dtype, device=wf.device)
+    check(_lib.load().b200q_scatter_columns_cast(ptr(wf), N, K, ld, ptr(perm), ptr(out), _DT[dtype],
+                                                 out.stride(0), stream_ptr()),
+          "b200q_scatter_columns_cast")
+    return out
+
+
+def gptq_prepare(H: torch.Tensor, wf: torch.Tensor, percdamp: float):
+    _need_cuda(H, wf)
+    K = H.shape[0]
+    N = wf.shape[0]
+    check(_lib.load().b200q_gptq_prepare(ptr(H), K, H.stride(0), ptr(wf), N, wf.stride(0),
+                                         float(percdamp), stream_ptr()), "b200q_gptq_prepare")
+
+
+def gptq_factor(H: torch.Tensor) -> int:
+    """In place H -> U (upper, U^T U = H^-1).  Returns 0, or NOT_POSITIVE_DEFINITE."""
+    _need_cuda(H)
+    lib = _lib.load()
+    K = H.shape[0]
+    ws = torch.empty(max(lib.b200q_gptq_factor_workspace_bytes(K), 4), dtype=torch.uint8,
+                     device=H.device)
+    status = torch.zeros(2, dtype=torch.int32, device=H.device)
+    check(lib.b200q_gptq_factor(ptr(H), K, H.stride(0), ptr(ws), ptr(status), stream_ptr()),
+          "b200q_gptq_factor")
+    return int(status[0].item())
+
+
+def gptq_sweep(wf, U, scale, zp, args: QuantizationArgs, blocksize=128, col_group=None,
+               global_scale=None) -> torch.Tensor:
+    """Runs the column sweep in place on wf; returns per-row losses."""
+    _need_cuda(wf, U, scale, zp, col_group, global_scale)
+    lib = _lib.load()
+    N, K, ld = _2d(wf)
+    scale = scale.contiguous()
+    zp = None if zp is None else zp.contiguous()
+    if col_group is not None:
+        col_group = col_group.to(torch.int32).contiguous()
+    if global_scale is not None:
+        global_scale = global_scale.to(torch.float32).contiguous()
+    losses = torch.empty(N, dtype=torch.float32, device=wf.device)
+    ws = torch.empty(max(lib.b200q_gptq_sweep_workspace_bytes(N, K, blocksize), 4),
+                     dtype=torch.uint8, device=wf.device)
+    check(lib.b200q_gptq_sweep(ptr(wf), N, K, ld, ptr(U), 0 if U is None else U.stride(0),
+                               ptr(scale), _dt(scale), ptr(zp), ptr(col_group), ptr(global_scale),
+                               args.c_struct(), int(blocksize), ptr(losses), ptr(ws), stream_ptr()),
+          "b200q_gptq_sweep")
+    return losses

@@ -1,0 +1,203 @@
+"""Hessian SYRK, the on-device factorisation and the GPTQ sweep against the golden fixtures
+(outputs of the reference's gptq_quantize.py) and the CPU oracle.
+
+Tolerances are the ones the path is specified with: Hessians within 1e-3 relative Frobenius
+norm; GPTQ: at least 99.5 % identical values of the fake-quantised weight (one value per integer
+code), scales identical, per-layer loss within 1 %."""
+import pytest
+import torch
+
+import oracle
+from helpers import args_from, bits_equal, mismatch, synth_acts, synth_weight
+from llm_compressor_b200 import gptq, observers, ops
+from test_oracle_golden import spec_from
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+HESSIAN_RTOL = 1e-3
+CODE_MATCH = 0.995
+LOSS_RTOL = 0.01
+
+
+def rel_fro(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).norm() / b.norm())
+
+
+# ------------------------------------------------------------------------------- Hessian
+def test_hessian_golden(golden):
+    for name, c in golden["hessian_cases"].items():
+        x = c["x"]
+        K = x.shape[-1]
+        lin = torch.nn.Linear(K, 8, bias=False, device=DEV)
+        H = gptq.make_empty_hessian(lin)
+        n = torch.zeros((), device=DEV)
+        H, n = gptq.accumulate_hessian(x.to(DEV), lin, H, n)
+        H, n = gptq.accumulate_hessian((x * 0.5).to(DEV), lin, H, n)
+        assert float(n) == float(c["n"]), name
+        assert rel_fro(H, c["H"]) < HESSIAN_RTOL, (name, rel_fro(H, c["H"]))
+        assert torch.equal(H, H.t()), name
+
+
+@pytest.mark.parametrize("T,K", [(192, 64), (300, 264), (2048, 512), (4096, 2048), (1000, 1160), (8192, 4096)])
+def test_hessian_vs_oracle(T, K):
+    x = synth_acts(1, T, K, seed=T + K)
+    H_ref = oracle.make_empty_hessian(K)
+    H_ref, n_ref = oracle.accumulate_hessian(x, H_ref, 0)
+    H = torch.zeros(K, K, device=DEV)
+    H, n = gptq.accumulate_hessian_lower(x.to(DEV), H, 0)
+    H = gptq.finalize_hessian(H, 1)
+    assert n == n_ref == 1
+    err = rel_fro(H, H_ref)
+    assert err < HESSIAN_RTOL, err
+    assert torch.equal(H, H.t())
+    # linearity: accumulating the same batch again doubles H
+    H2 = torch.zeros(K, K, device=DEV)
+    gptq.accumulate_hessian_lower(x.to(DEV), H2, 0)
+    gptq.accumulate_hessian_lower(x.to(DEV), H2, 0)
+    gptq.finalize_hessian(H2, 2)
+    assert rel_fro(H2, H_ref) < HESSIAN_RTOL
+
+
+def test_hessian_noncontiguous_and_3d():
+    x = synth_acts(3, 100, 136, seed=9)  # [B,S,K] with K % 8 == 0
+    H_ref, n_ref = oracle.accumulate_hessian(x, oracle.make_empty_hessian(136), 0)
+    lin = torch.nn.Linear(136, 4, bias=False, device=DEV)
+    H, n = gptq.accumulate_hessian(x.to(DEV), lin, gptq.make_empty_hessian(lin), 0)
+    assert n == n_ref == 3
+    assert rel_fro(H, H_ref) < HESSIAN_RTOL
+
+
+# ------------------------------------------------------------------------------- factor
+@pytest.mark.parametrize("K", [32, 130, 256, 1000, 2048])
+def test_factor_matches_float64(K):
+    g = torch.Generator().manual_seed(K)
+    X = torch.randn(4 * K, K, generator=g) * (0.25 + 2 * torch.rand(K, generator=g))
+    H = (2 * X.t() @ X / 4).float()
+    H[torch.arange(K), torch.arange(K)] += 0.01 * H.diag().mean()
+    Hd = H.double()
+    U_ref = torch.linalg.cholesky(torch.cholesky_inverse(torch.linalg.cholesky(Hd)), upper=True)
+    Hg = H.clone().to(DEV)
+    status = ops.gptq_factor(Hg)
+    assert status == 0
+    U = Hg.cpu().double()
+    assert float(U.tril(-1).abs().max()) == 0.0
+    err = float((U - U_ref).norm() / U_ref.norm())
+    # the reference's own float32 chain on CPU, for scale
+    U32 = torch.linalg.cholesky(torch.cholesky_inverse(torch.linalg.cholesky(H.clone())), upper=True).double()
+    err32 = float((U32 - U_ref).norm() / U_ref.norm())
+    assert err < max(5e-5, 4 * err32), (err, err32)
+
+
+def test_factor_reports_not_positive_definite():
+    K = 128
+    H = torch.eye(K)
+    H[5, 5] = -3.0
+    assert ops.gptq_factor(H.to(DEV)) == 1
+
+
+# ------------------------------------------------------------------------------- GPTQ
+def run_gptq(weight, args, hessian, blocksize, percdamp, observer_name=None):
+    N, K = weight.shape
+    lin = torch.nn.Linear(K, N, bias=False, device=DEV, dtype=weight.dtype)
+    lin.weight.data = weight.to(DEV)
+    obs = observers.Observer.load_from_registry(observer_name or args.observer, base_name="weight", args=args)
+    lin.weight_observer = obs
+    obs(lin.weight.data)
+    before = lin.weight.data.clone()
+    loss, out = gptq.quantize_weight(lin, args, hessian.clone().to(DEV), blocksize=blocksize, percdamp=percdamp)
+    assert torch.equal(lin.weight.data, before), "quantize_weight must not touch module.weight"
+    return loss, out
+
+
+GPTQ_CASES = ["w4a16_g128", "w4a16_g32_bs64", "w4a16_g128_actorder_weight", "w4a16_g128_actorder_group",
+              "w4a16_asym_g128", "w4_channel", "w4_tensor", "w8a16_channel", "fp8_channel", "nvfp4", "mxfp4",
+              "w4a16_g128_dead_cols", "w4a16_g128_not_pd", "w4a16_g128_fp32w"]
+
+
+@pytest.mark.parametrize("name", GPTQ_CASES)
+def test_gptq_golden(golden, name):
+    c = golden["gptq_cases"][name]
+    args = args_from(c["args"])
+    if name.endswith("not_pd"):
+        with pytest.warns(UserWarning, match="Falling back to round-to-nearest"):
+            loss, out = run_gptq(c["weight"], args, c["hessian"], c["blocksize"], c["percdamp"])
+    else:
+        loss, out = run_gptq(c["weight"], args, c["hessian"], c["blocksize"], c["percdamp"])
+    ref = c["out"]
+    assert set(out) == set(ref)
+    assert bits_equal(out["weight_scale"], ref["weight_scale"])
+    assert bits_equal(out["weight_zero_point"], ref["weight_zero_point"])
+    if "weight_global_scale" in ref:
+        assert bits_equal(out["weight_global_scale"], ref["weight_global_scale"])
+    if "weight_g_idx" in ref:
+        assert torch.equal(out["weight_g_idx"].cpu().long(), ref["weight_g_idx"].long())
+    mm = mismatch(out["weight"], ref["weight"])
+    assert mm <= 1 - CODE_MATCH, mm
+    assert loss == pytest.approx(c["loss"], rel=LOSS_RTOL)
+
+
+@pytest.mark.parametrize("N,K,scheme", [(256, 1024, "W4A16"), (96, 640, "W4A16"), (128, 512, "FP8_DYNAMIC"),
+                                        (64, 512, "NVFP4A16")])
+def test_gptq_vs_oracle_larger(N, K, scheme):
+    spec = oracle.preset(scheme)
+    args = args_from({k: getattr(spec, k) for k in ("num_bits", "type", "symmetric", "strategy", "group_size",
+                                                     "scale_dtype", "zp_dtype")})
+    w = synth_weight(N, K, seed=N + K)
+    x = synth_acts(8, K // 2, K, seed=3)
+    H, n = oracle.accumulate_hessian(x, oracle.make_empty_hessian(K), 0)
+    Hn = H / n
+    loss_ref, ref = oracle.quantize_weight(w, spec, Hn.clone())
+    loss, out = run_gptq(w, args, Hn, 128, 0.01)
+    assert bits_equal(out["weight_scale"], ref["weight_scale"])
+    mm = mismatch(out["weight"], ref["weight"])
+    assert mm <= 1 - CODE_MATCH, mm
+    assert loss == pytest.approx(loss_ref, rel=LOSS_RTOL)
+
+
+def test_end_to_end_hessian_then_gptq_then_pack():
+    """Hook path on device (SYRK -> finalize -> solve -> pack) against the oracle end to end."""
+    from llm_compressor_b200 import compressors
+    N, K = 128, 512
+    spec = oracle.preset("W4A16")
+    args = args_from(dict(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128))
+    w = synth_weight(N, K, seed=1)
+    xs = [synth_acts(2, 256, K, seed=20 + i) for i in range(3)]
+    Href, nref = oracle.make_empty_hessian(K), 0
+    for x in xs:
+        Href, nref = oracle.accumulate_hessian(x, Href, nref)
+    loss_ref, ref = oracle.quantize_weight(w, spec, Href / nref)
+    packed_ref = oracle.compress_weight(
+        {"weight": ref["weight"], "weight_scale": ref["weight_scale"], "weight_zero_point": ref["weight_zero_point"]}, spec)
+    H, n = torch.zeros(K, K, device=DEV), 0
+    for x in xs:
+        H, n = gptq.accumulate_hessian_lower(x.to(DEV), H, n)
+    gptq.finalize_hessian(H, n)
+    assert rel_fro(H, Href / nref) < HESSIAN_RTOL
+    loss, out = run_gptq(w, args, H, 128, 0.01)
+    packed = compressors.compress_state_dict(
+        {"weight": out["weight"], "weight_scale": out["weight_scale"], "weight_zero_point": out["weight_zero_point"]}, args)
+    assert mismatch(out["weight"], ref["weight"]) <= 1 - CODE_MATCH
+    # nibble-level agreement of the packed words
+    a = packed["weight_packed"].cpu().view(torch.uint8)
+    b = packed_ref["weight_packed"].view(torch.uint8)
+    nib = ((a & 0xF) != (b & 0xF)).float().mean() + ((a >> 4) != (b >> 4)).float().mean()
+    assert float(nib) / 2 <= 1 - CODE_MATCH
+    assert loss == pytest.approx(loss_ref, rel=LOSS_RTOL)
+
+
+# ------------------------------------------------------------------------------- MSE observer
+def test_mse_golden(golden):
+    worst = 0.0
+    for name, c in golden["mse_cases"].items():
+        args = args_from(c["args"])
+        obs = observers.Observer.load_from_registry("memoryless_mse", base_name="weight", args=args)
+        obs(c["weight"].to(DEV))
+        mm = max(mismatch(obs.min_vals, c["min"]), mismatch(obs.max_vals, c["max"]))
+        worst = max(worst, mm)
+        # a differing group must still be within the 1e-3 relative scale tolerance of the path
+        qp = obs.get_qparams()
+        s, s_ref = qp["scale"].float().cpu(), c["scale"].float()
+        rel = ((s - s_ref).abs() / s_ref.abs().clamp_min(1e-30))
+        assert float((rel > 1e-3).float().mean()) <= 0.02, (name, float(rel.max()))
+    assert worst <= 0.05, worst

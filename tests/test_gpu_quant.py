@@ -1,0 +1,157 @@
+"""Observer / qparams / quantize / pack kernels against the golden fixtures (outputs of
+the reference on the same inputs) and against the CPU oracle on larger seeded inputs.
+Everything goes through the C ABI (ctypes) and must be bit-exact."""
+import pytest
+import torch
+
+import oracle
+from helpers import args_from, bits_equal, mismatch, synth_weight
+from llm_compressor_b200 import compressors, observers, ops
+from test_oracle_golden import spec_from
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+SCHEMES = ["w4a16_g128", "w4a16_g32", "w4a16_asym_g128", "w4_channel", "w4_tensor", "w8a16_channel",
+           "w8_asym_channel", "w8_g128", "fp8_channel", "fp8_tensor", "fp8_block", "nvfp4", "mxfp4",
+           "mxfp8"]
+
+
+@pytest.mark.parametrize("name", SCHEMES)
+def test_golden_observer_qparams_quantize_pack(golden, name):
+    c = golden["ct_cases"][name]
+    args = args_from(c["args"])
+    w = c["weight"].to(DEV)
+    mn, mx = ops.observe_minmax(w, args)
+    assert bits_equal(mn, c["min"]) and bits_equal(mx, c["max"])
+    obs = observers.Observer.load_from_registry("memoryless_minmax", base_name="weight", args=args)
+    qp = obs(w).get_qparams()
+    assert bits_equal(qp["scale"], c["scale"])
+    assert bits_equal(qp["zero_point"], c["zero_point"])
+    if c["global_scale"] is None:
+        assert qp["global_scale"] is None
+    else:
+        assert bits_equal(qp["global_scale"], c["global_scale"])
+    fq = ops.fake_quantize(w, qp["scale"], qp["zero_point"], args, global_scale=qp["global_scale"])
+    assert bits_equal(fq, c["fake_quant"].to(w.dtype)), mismatch(fq, c["fake_quant"].to(w.dtype))
+    assert compressors.infer_module_format(args) == c["format"]
+    sd = {"weight": w, "weight_scale": qp["scale"].to(w.dtype), "weight_zero_point": qp["zero_point"]}
+    if qp["global_scale"] is not None:
+        sd["weight_global_scale"] = qp["global_scale"]
+    out = compressors.compress_state_dict(sd, args)
+    assert set(out) == set(c["compressed"])
+    for k, v in c["compressed"].items():
+        assert bits_equal(out[k], v), (k, mismatch(out[k], v))
+
+
+@pytest.mark.parametrize("name", SCHEMES)
+@pytest.mark.parametrize("shape", [(256, 1024), (7, 40), (64, 2048)])
+def test_oracle_parity_larger(golden, name, shape):
+    args = args_from(golden["ct_cases"][name]["args"])
+    N, K = shape
+    if args.strategy in ("group", "tensor_group") and K % args.group_size:
+        pytest.skip("group size does not divide K")
+    spec = spec_from(golden["ct_cases"][name]["args"])
+    w = synth_weight(N, K, seed=N * 7 + K)
+    wd = w.to(DEV)
+    o = oracle.WeightObserver(spec)
+    o(w)
+    omn, omx = o.min_vals.clone(), o.max_vals.clone()
+    oqp = o.get_qparams()
+    mn, mx = ops.observe_minmax(wd, args)
+    assert bits_equal(mn, omn) and bits_equal(mx, omx)
+    obs = observers.MemorylessMinMaxObserver("weight", args)
+    qp = obs(wd).get_qparams()
+    assert bits_equal(qp["scale"], oqp["scale"])
+    assert bits_equal(qp["zero_point"], oqp["zero_point"])
+    ofq = oracle.fake_quantize(w, oqp["scale"], oqp["zero_point"], spec, global_scale=oqp["global_scale"])
+    fq = ops.fake_quantize(wd, qp["scale"], qp["zero_point"], args, global_scale=qp["global_scale"])
+    assert bits_equal(fq, ofq.to(w.dtype)), mismatch(fq, ofq.to(w.dtype))
+    if args.type == "float" and args.num_bits == 4 and K % 2:
+        return
+    sd = {"weight": w, "weight_scale": oqp["scale"].to(w.dtype), "weight_zero_point": oqp["zero_point"]}
+    if oqp["global_scale"] is not None:
+        sd["weight_global_scale"] = oqp["global_scale"]
+    ref = oracle.compress_weight(sd, spec)
+    out = compressors.compress_state_dict({k: v.to(DEV) for k, v in sd.items()}, args)
+    assert set(out) == set(ref)
+    for k, v in ref.items():
+        assert bits_equal(out[k], v), (k, mismatch(out[k], v))
+
+
+@pytest.mark.parametrize("name", ["w4a16_g128", "w4a16_g32", "w4a16_asym_g128", "w8_g128", "w8a16_channel",
+                                  "w4_channel", "fp8_channel", "mxfp4", "mxfp8"])
+def test_fused_rtn_matches_unfused(golden, name):
+    """One-pass statistics -> qparams -> codes equals the observer + compressor sequence."""
+    args = args_from(golden["ct_cases"][name]["args"])
+    spec = spec_from(golden["ct_cases"][name]["args"])
+    w = synth_weight(128, 1024, seed=11)
+    o = oracle.WeightObserver(spec)
+    oqp = o(w).get_qparams()
+    sd = {"weight": w, "weight_scale": oqp["scale"].to(w.dtype), "weight_zero_point": oqp["zero_point"]}
+    ref = oracle.compress_weight(sd, spec)
+    r = ops.rtn_quantize_pack(w.to(DEV), args)
+    assert bits_equal(r["scale"], oqp["scale"].to(w.dtype))
+    assert bits_equal(r["zero_point"], oqp["zero_point"])
+    codes = r["codes"]
+    if "weight_packed" in ref:
+        assert bits_equal(codes, ref["weight_packed"]), mismatch(codes, ref["weight_packed"])
+    else:
+        exp = ref["weight"]
+        if exp.dtype == torch.int8:  # fused path packs int8 four to a word
+            exp = oracle.pack_int32(exp, 8)
+        assert bits_equal(codes, exp), mismatch(codes, exp)
+    if args.is_mx:
+        assert bits_equal(r["scale_store"], ref["weight_scale"])
+
+
+def test_fused_nvfp4_and_shared_global_scale(golden):
+    c = golden["ct_cases"]["nvfp4_fused3"]
+    args = args_from(c["args"])
+    mods = []
+    for w in c["weights"]:
+        m = torch.nn.Linear(w.shape[1], w.shape[0], bias=False, device=DEV, dtype=w.dtype)
+        m.weight.data = w.to(DEV)
+        m.weight_observer = observers.MemorylessMinMaxObserver("weight", args)
+        mods.append(m)
+    observers.fuse_observers([(m.weight_observer, m) for m in mods])
+    for m in mods:
+        m.weight_observer(m.weight.data)
+    qps = [m.weight_observer.get_qparams() for m in mods]
+    for qp, s_ref, g_ref in zip(qps, c["scales"], c["global_scales"]):
+        assert bits_equal(qp["global_scale"], g_ref)
+        assert bits_equal(qp["scale"], s_ref)
+    assert all(not m.weight_observer.has_statistics for m in mods)
+    # one-pass NVFP4 with the shared scale equals the oracle's compress
+    spec = spec_from(c["args"])
+    for m, qp in zip(mods, qps):
+        w = m.weight.data.cpu()
+        sd = {"weight": w, "weight_scale": qp["scale"].cpu().to(w.dtype),
+              "weight_zero_point": qp["zero_point"].cpu(), "weight_global_scale": qp["global_scale"].cpu()}
+        ref = oracle.compress_weight(sd, spec)
+        r = ops.nvfp4_quantize_pack(m.weight.data, qp["global_scale"])
+        assert bits_equal(r["codes"], ref["weight_packed"])
+        assert bits_equal(r["scale_store"], ref["weight_scale"])
+
+
+def test_actorder_g_idx_pack(golden):
+    """pack with a column -> group map (act-order "group") equals the oracle."""
+    spec = oracle.preset("W4A16")
+    args = args_from(dict(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128))
+    w = synth_weight(32, 512, seed=5)
+    g = torch.Generator().manual_seed(0)
+    perm = torch.randperm(512, generator=g)
+    g_idx = (torch.arange(512) // 128)[torch.argsort(perm)].to(torch.int32)
+    o = oracle.WeightObserver(spec)
+    oqp = o(w[:, perm].contiguous()).get_qparams()
+    sd = {"weight": w, "weight_scale": oqp["scale"], "weight_zero_point": oqp["zero_point"], "weight_g_idx": g_idx}
+    ref = oracle.compress_weight(sd, spec)
+    out = compressors.compress_state_dict({k: v.to(DEV) for k, v in sd.items()}, args)
+    assert bits_equal(out["weight_packed"], ref["weight_packed"])
+
+
+def test_rejects_cpu_tensors():
+    from llm_compressor_b200._lib import B200QError
+    args = args_from(dict(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128))
+    with pytest.raises(B200QError):
+        ops.observe_minmax(torch.zeros(4, 128, dtype=torch.bfloat16), args)
