@@ -11,6 +11,8 @@
 // early) repeats the search up to that step.
 #include "common.cuh"
 
+#include <string.h>
+
 namespace b200q {
 namespace mse {
 
@@ -45,8 +47,8 @@ __device__ __forceinline__ void qparams_local(float mn, float mx, const Cfg& c, 
     s = rnd_if<TB>(__fdiv_rn(d, c.range));
     float z = rnd_if<TB>(__fdiv_rn(mn, s));
     z = rnd_if<TB>(c.qmin - z);
-    z = fminf(fmaxf(z, c.qmin), c.qmax);
-    zp = (z != z) ? 0.0f : z;
+    // 0/0 for an all-zero group: torch's clamp keeps the NaN and the integer cast makes it 0
+    zp = (z != z) ? 0.0f : fminf(fmaxf(z, c.qmin), c.qmax);
   }
   if (s == 0.0f) s = c.eps;
   if (c.zp_kind == B200Q_ZP_INT8) zp = rintf(fminf(fmaxf(zp, -128.0f), 127.0f));
@@ -225,6 +227,13 @@ int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t l
   else c.eps = (wdtype == B200Q_BF16) ? 0.0078125f : 1.1920928955078125e-07f;
   c.steps = (int)((double)maxshrink * (double)grid);
   c.patience = patience; c.grid = grid; c.norm = norm; c.expand = expand;
+  if (wdtype == B200Q_BF16) {
+    // torch casts the python exponent to the tensor's dtype: |e|.pow(2.4) on bf16 uses 2.40625
+    uint32_t b;
+    memcpy(&b, &norm, 4);
+    b = (b + 0x7FFFu + ((b >> 16) & 1u)) & 0xFFFF0000u;
+    memcpy(&c.norm, &b, 4);
+  }
   if (c.steps < 0) return B200Q_ERR_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   int* ctl = (int*)scratch;

@@ -70,8 +70,8 @@ __device__ __forceinline__ void qparams_one(float mn, float mx, const QParamCfg&
     s = rnd_if<TB>(__fdiv_rn(d, c.range));
     float z = rnd_if<TB>(__fdiv_rn(mn, s));
     z = rnd_if<TB>(c.qmin - z);
-    z = fminf(fmaxf(z, c.qmin), c.qmax);
-    zp = (z != z) ? 0.0f : z;
+    // 0/0 for an all-zero group: torch's clamp keeps the NaN and the integer cast makes it 0
+    zp = (z != z) ? 0.0f : fminf(fmaxf(z, c.qmin), c.qmax);
   }
   if (c.has_global) s = g * s;
   if (c.scale_kind == B200Q_SCALE_FP8) {
