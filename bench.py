@@ -1,0 +1,474 @@
+"""Benchmark of the calibrate-and-quantize hot path on B200.
+
+Workload (BASELINE.json configs[2]): GPTQ W4A16, symmetric int4, group 128, block 128,
+dampening 0.01, no act-order, on a Llama-3-8B-shaped decoder (hidden 4096, intermediate
+14336, 32 query / 8 KV heads, 32 layers) with 512 x 2048 calibration tokens.
+
+One STEP is the hot path of one decoder layer: accumulate the Hessians of its four distinct
+Linear inputs over all 1,048,576 calibration tokens, then for its seven Linear modules observe,
+factor, sweep and pack to int4.  Weights and activations are synthetic (seeded normal,
+per-column scales); every layer has the same shapes, so the metric - wall seconds of the hot
+path for the 32-layer model - is 32 x the mean step time.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Under torchrun (N > 1) the calibration sequences are split across ranks, partial Hessians are
+sum-reduced (NCCL) to the rank that owns each Hessian, owners solve and pack, and the
+fake-quantised weights are broadcast back (strong scaling: total work fixed).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, KV_OUT, LAYERS = 4096, 14336, 1024, 32
+SEQS, SEQ_LEN = 512, 2048
+METRIC = "gptq_w4a16_llama3_8b_hotpath_wall_s"
+# (name, out_features, input group)
+MODULES = [("q_proj", HIDDEN, "attn_in"), ("k_proj", KV_OUT, "attn_in"), ("v_proj", KV_OUT, "attn_in"),
+           ("o_proj", HIDDEN, "o_in"), ("gate_proj", INTER, "mlp_in"), ("up_proj", INTER, "mlp_in"),
+           ("down_proj", HIDDEN, "down_in")]
+GROUP_K = {"attn_in": HIDDEN, "o_in": HIDDEN, "mlp_in": HIDDEN, "down_in": INTER}
+
+
+def f_syrk(tokens: int, K: int) -> float:
+    """Algorithmic flops of a symmetric rank-k update: one multiply-add per token for each of
+    the K(K+1)/2 distinct entries."""
+    return float(tokens) * K * (K + 1)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(tflops=p.get("bf16_tflops_sustained", 1394.5), hbm=p.get("hbm_gbs", 6538.0), source="measured")
+    return dict(tflops=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            }
+            while not self._stop_evt.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:  # noqa: BLE001
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+                time.sleep(0.2)
+        except Exception as e:  # noqa: BLE001
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+# ======================================================================================
+# CPU arm: the oracle (a port of the reference's torch code) on the host cores
+# ======================================================================================
+def cpu_reference_step_seconds(sample_scale: float = 1.0):
+    """Time a bounded sample of one layer's hot path with the CPU oracle and extrapolate to
+    the full layer.  Returns (seconds_per_layer, cores, description)."""
+    import torch
+
+    import oracle
+
+    torch.manual_seed(0)
+    cores = torch.get_num_threads()
+    spec = oracle.preset("W4A16")
+    t_h = {}
+    for K in (HIDDEN, INTER):
+        x = torch.randn(1, SEQ_LEN, K).to(torch.bfloat16)
+        H = oracle.make_empty_hessian(K)
+        oracle.accumulate_hessian(x[:, :64], H, 0)  # warm the BLAS threads
+        t0 = time.perf_counter()
+        oracle.accumulate_hessian(x, H, 0)
+        t_h[K] = time.perf_counter() - t0
+        del H
+    # the reference keeps one Hessian per Linear: 6 of width 4096 and 1 of width 14336 per layer
+    hess_layer = SEQS * (6 * t_h[HIDDEN] + t_h[INTER])
+    # observe + quantize_weight + pack on the real q_proj shape, timed in full; the other modules
+    # are scaled by their share of the solve's arithmetic (N K^2 sweep + 4/3 K^3 factorisations)
+    N_s, K_s = HIDDEN, HIDDEN
+    w = (torch.randn(N_s, K_s) * 0.02).to(torch.bfloat16)
+    xs = torch.randn(1, SEQ_LEN, K_s).to(torch.bfloat16)
+    Hs, ns = oracle.accumulate_hessian(xs, oracle.make_empty_hessian(K_s), 0)
+    Hs[torch.arange(K_s), torch.arange(K_s)] += 0.1 * Hs.diag().mean()  # 2048 tokens < K: keep it PD
+    t0 = time.perf_counter()
+    obs = oracle.WeightObserver(spec)
+    obs(w)
+    _, out = oracle.quantize_weight(w, spec, Hs / ns, observer=obs)
+    oracle.compress_weight({"weight": out["weight"], "weight_scale": out["weight_scale"],
+                            "weight_zero_point": out["weight_zero_point"]}, spec)
+    t_q = time.perf_counter() - t0
+
+    def work(n_out, K):
+        return n_out * K * K + 4.0 / 3.0 * K ** 3
+
+    solve_layer = sum(t_q * work(n_out, GROUP_K[grp]) / work(N_s, K_s) for _, n_out, grp in MODULES)
+    desc = (f"oracle on {cores} host threads: accumulate_hessian on one 2048-token sequence at K=4096 "
+            f"({t_h[HIDDEN]:.2f} s) and K=14336 ({t_h[INTER]:.2f} s), x512 sequences x (6+1) modules; "
+            f"observe+quantize_weight+pack on a 4096x4096 module ({t_q:.2f} s) scaled to the seven "
+            f"modules by N*K^2 + 4/3*K^3")
+    return hess_layer + solve_layer, cores, desc
+
+
+def run_reference(args):
+    """`--impl reference`: the reference's CPU path (the oracle port) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for i in range(args.warmup + args.steps):
+        sec, cores, desc = cpu_reference_step_seconds()
+        if i >= args.warmup:
+            vals.append(sec)
+    step_s = sum(vals) / len(vals)
+    value = step_s * LAYERS
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[2]: GPTQ W4A16 g128, Llama-3-8B shapes, 512x2048 calibration tokens",
+                   "step": "one decoder layer (bounded CPU sample, extrapolated)", "layers": LAYERS},
+        "cpu_baseline": {"value": value, "unit": "s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ======================================================================================
+# GPU arm
+# ======================================================================================
+class LayerBench:
+    def __init__(self, rank, world, tokens_per_call, seqs, device):
+        import torch
+
+        from llm_compressor_b200.observers import MemorylessMinMaxObserver
+        from llm_compressor_b200.quant_args import QuantizationArgs
+
+        self.torch = torch
+        self.rank, self.world, self.dev = rank, world, device
+        self.qargs = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128)
+        self.Observer = MemorylessMinMaxObserver
+        # this rank's share of the calibration sequences (src/llmcompressor/datasets/utils.py:244-253)
+        lo, hi = (seqs * rank) // world, (seqs * (rank + 1)) // world
+        self.local_seqs, self.total_seqs = hi - lo, seqs
+        self.local_tokens = self.local_seqs * SEQ_LEN
+        self.tokens_per_call = min(tokens_per_call, self.local_tokens)
+        g = torch.Generator(device=device).manual_seed(1 + rank)
+        self.X = {}
+        for name, K in GROUP_K.items():
+            x = torch.empty(self.local_tokens, K, dtype=torch.bfloat16, device=device)
+            colscale = 0.25 + 2.0 * torch.rand(K, generator=g, device=device)
+            for t0 in range(0, self.local_tokens, 65536):
+                t1 = min(self.local_tokens, t0 + 65536)
+                x[t0:t1] = (torch.randn(t1 - t0, K, generator=g, device=device) * colscale).to(torch.bfloat16)
+            self.X[name] = x
+        gw = torch.Generator(device=device).manual_seed(0)
+        self.mods = []
+        for name, n_out, grp in MODULES:
+            lin = torch.nn.Linear(GROUP_K[grp], n_out, bias=False, device=device, dtype=torch.bfloat16)
+            lin.weight.data = (torch.randn(n_out, GROUP_K[grp], generator=gw, device=device) * 0.02).to(torch.bfloat16)
+            lin.requires_grad_(False)
+            self.mods.append((name, lin, grp))
+        self.H = {g_: torch.zeros(K, K, dtype=torch.float32, device=device) for g_, K in GROUP_K.items()}
+        # owners of the Hessian groups: greedy bin packing by K, heaviest first
+        loads, self.owner = [0] * world, {}
+        for g_ in sorted(GROUP_K, key=lambda n: -GROUP_K[n]):
+            r = loads.index(min(loads))
+            self.owner[g_] = r
+            loads[r] += GROUP_K[g_] ** 3
+        self.syrk_events = []
+
+    def step(self, from_host=None, record=False):
+        """One decoder layer.  `from_host`: HostFeeder supplying activation chunks from pinned
+        host memory (end-to-end arm); otherwise activations are resident in HBM."""
+        torch = self.torch
+        from llm_compressor_b200 import compressors, gptq
+        import torch.distributed as dist
+
+        for g_, H in self.H.items():
+            H.zero_()
+        n = {g_: 0 for g_ in self.H}
+        for g_, K in GROUP_K.items():
+            X = self.X[g_]
+            for t0 in range(0, self.local_tokens, self.tokens_per_call):
+                t1 = min(self.local_tokens, t0 + self.tokens_per_call)
+                chunk = from_host.next_chunk(g_, t0, t1) if from_host is not None else X[t0:t1]
+                seqs = (t1 - t0) // SEQ_LEN
+                if record:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                gptq.accumulate_hessian_lower(chunk.view(seqs, SEQ_LEN, K), self.H[g_], 0)
+                if record:
+                    e1.record()
+                    self.syrk_events.append((e0, e1, t1 - t0, K))
+                if from_host is not None:
+                    from_host.release(chunk)
+                n[g_] += seqs
+        if self.world > 1:
+            for g_ in self.H:
+                dist.reduce(self.H[g_], dst=self.owner[g_], op=dist.ReduceOp.SUM)
+        results = {}
+        for g_, K in GROUP_K.items():
+            if self.owner[g_] != self.rank:
+                continue
+            gptq.finalize_hessian(self.H[g_], self.total_seqs)
+            factor = gptq.factor_hessian(self.H[g_], percdamp=0.01, actorder=None)
+            self.H[g_] = factor.U if factor.U is not None else self.H[g_]
+            for name, lin, grp in self.mods:
+                if grp != g_:
+                    continue
+                lin.weight_observer = self.Observer("weight", self.qargs)
+                lin.weight_observer(lin.weight.data)
+                loss, out = gptq.quantize_weight(lin, self.qargs, None, blocksize=128, percdamp=0.01, factor=factor)
+                packed = compressors.compress_state_dict(
+                    {"weight": out["weight"], "weight_scale": out["weight_scale"],
+                     "weight_zero_point": out["weight_zero_point"]}, self.qargs)
+                results[name] = (loss, out["weight"], packed)
+        if self.world > 1:
+            # every rank needs the fake-quantised weights to propagate activations
+            # (src/llmcompressor/utils/dist.py:55-88)
+            for name, lin, grp in self.mods:
+                if name in results:
+                    buf = results[name][1]
+                else:
+                    buf = torch.empty_like(lin.weight.data)
+                dist.broadcast(buf, src=self.owner[grp])
+        return results
+
+
+class HostFeeder:
+    """Pinned host copies of the activations, streamed to the device in double-buffered
+    chunks on a copy stream (the end-to-end arm's host->device leg)."""
+
+    def __init__(self, bench: LayerBench, budget_bytes: int):
+        torch = bench.torch
+        self.torch, self.b = torch, bench
+        self.copy_stream = torch.cuda.Stream()
+        self.host, self.cycle = {}, {}
+        need = sum(x.numel() * 2 for x in bench.X.values())
+        frac = min(1.0, budget_bytes / need)
+        for g_, x in bench.X.items():
+            rows = max(bench.tokens_per_call, int(x.shape[0] * frac) // bench.tokens_per_call * bench.tokens_per_call)
+            rows = min(rows, x.shape[0])
+            h = torch.empty(rows, x.shape[1], dtype=torch.bfloat16, pin_memory=True)
+            h.copy_(x[:rows])
+            self.host[g_], self.cycle[g_] = h, rows
+        self.pool_fraction = frac
+        self.bufs = {}
+        self.h2d_bytes = 0
+        self.pending = None
+
+    def _buf(self, K, slot):
+        key = (K, slot)
+        if key not in self.bufs:
+            self.bufs[key] = (self.torch.empty(self.b.tokens_per_call, K, dtype=self.torch.bfloat16, device=self.b.dev),
+                              self.torch.cuda.Event(), self.torch.cuda.Event())
+        return self.bufs[key]
+
+    def start_step(self):
+        self.slot, self.h2d_bytes = 0, 0
+
+    def next_chunk(self, g_, t0, t1):
+        torch = self.torch
+        K = GROUP_K[g_]
+        buf, ready, free = self._buf(K, self.slot & 1)
+        self.slot += 1
+        rows = t1 - t0
+        src0 = t0 % self.cycle[g_]
+        if src0 + rows > self.cycle[g_]:
+            src0 = 0
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(free)  # the kernel that last read this buffer is done
+            buf[:rows].copy_(self.host[g_][src0:src0 + rows], non_blocking=True)
+            ready.record(self.copy_stream)
+        torch.cuda.current_stream().wait_event(ready)
+        self.h2d_bytes += rows * K * 2
+        out = buf[:rows]
+        out._feeder_free = free
+        return out
+
+    def release(self, chunk):
+        chunk._feeder_free.record(self.torch.cuda.current_stream())
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    from llm_compressor_b200 import _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path for the product arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    peaks = load_peaks()
+    seqs = args.seqs
+    bench = LayerBench(rank, world, args.tokens_per_call, seqs, dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # L2 is defeated by size: every step streams tens of GB of activations (>> 126 MB)
+    for _ in range(args.warmup):
+        bench.step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = lib.b200q_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    bench.syrk_events = []
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        results = bench.step(record=True)
+    e1.record()
+    barrier()
+    launches = lib.b200q_launch_count() - launches0
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    scale = (SEQS / seqs)  # 1 unless a reduced calibration set was asked for
+    value = ms_per_step / 1e3 * LAYERS
+
+    # dominant kernel: the SYRK; achieved = algorithmic flops / CUDA-event time of its launches
+    syrk_ms = sum(a.elapsed_time(b) for a, b, _, _ in bench.syrk_events)
+    syrk_flops = sum(f_syrk(t, K) for _, _, t, K in bench.syrk_events)
+    achieved = syrk_flops / (syrk_ms * 1e-3) / 1e12 if syrk_ms > 0 else 0.0
+    roofline = {"bound": "tensor", "kernel": "syrk_kernel (tcgen05)", "achieved": achieved, "peak": peaks["tflops"],
+                "unit": "TFLOP/s", "frac": achieved / peaks["tflops"], "traffic": None,
+                "peak_source": peaks["source"] + " bf16_tflops_sustained",
+                "share_of_step": syrk_ms / ms if ms else None,
+                "launches": len(bench.syrk_events)}
+
+    # end to end through the public API with host buffers
+    e2e = None
+    if not args.no_e2e:
+        import psutil
+        avail = psutil.virtual_memory().available
+        budget = int(min(0.25 * avail, 64 * 2**30))
+        feeder = HostFeeder(bench, budget)
+        d2h_bytes = 0
+        host_out = {}
+        barrier()
+        steps_e2e = max(1, min(args.steps, args.e2e_steps))
+        for it in range(1 + steps_e2e):
+            if it == 1:
+                barrier()
+                t0 = torch.cuda.Event(enable_timing=True)
+                t1 = torch.cuda.Event(enable_timing=True)
+                t0.record()
+            feeder.start_step()
+            res = bench.step(from_host=feeder)
+            d2h_bytes = 0
+            for name, (loss, wq, packed) in res.items():
+                for k, v in packed.items():
+                    key = (name, k)
+                    if key not in host_out:
+                        host_out[key] = torch.empty(v.shape, dtype=v.dtype, pin_memory=True)
+                    host_out[key].copy_(v, non_blocking=True)
+                    d2h_bytes += v.numel() * v.element_size()
+        t1.record()
+        barrier()
+        ms_e2e = t0.elapsed_time(t1) / steps_e2e
+        if world > 1:
+            t = torch.tensor([ms_e2e], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_e2e = float(t.item())
+        e2e = {"value": ms_e2e / 1e3 * LAYERS, "unit": "s", "h2d_bytes_per_step": feeder.h2d_bytes,
+               "d2h_bytes_per_step": d2h_bytes, "steps": steps_e2e,
+               "host_pool_fraction": round(feeder.pool_fraction, 3)}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        sec, cores, desc = cpu_reference_step_seconds()
+        cpu = {"value": sec * LAYERS, "unit": "s", "cores": cores, "kind": "port", "sample": desc}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[2]: GPTQ W4A16 g128 (sym int4, block 128, damp 0.01, no act-order), "
+                                   "Llama-3-8B shapes, %d x %d calibration tokens" % (seqs, SEQ_LEN),
+                       "step": "one decoder layer: 4 Hessians over all tokens + 7 modules observe/factor/sweep/pack",
+                       "layers": LAYERS, "tokens_per_syrk_call": bench.tokens_per_call,
+                       "l2": "inputs larger than L2 (tens of GB streamed per step)",
+                       "calibration_scale": scale},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "clocks": clocks,
+            "published_reference": {"value": 745.03, "unit": "s", "note": "whole oneshot incl. model forwards, "
+                                    "GPU not stated (docs/guides/big_models_and_distributed/distributed_oneshot.md:107-111)"},
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--tokens-per-call", type=int, default=32768)
+    ap.add_argument("--seqs", type=int, default=SEQS, help="calibration sequences (512 = the named config)")
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -62,6 +62,9 @@ typedef struct {
 const char* b200q_version(void);
 /* Text of the last CUDA error seen by the calling thread ("" if none). */
 const char* b200q_last_error(void);
+/* Number of kernels this library has launched in the process so far (diagnostic; no
+ * counterpart in the reference). */
+long long b200q_launch_count(void);
 
 /* ------------------------------------------------------------------ observers */
 
@@ -98,8 +101,9 @@ int b200q_qparams(const void* min_vals, const void* max_vals, int stat_dtype, in
 
 /* MSE shrink-grid search over per-group ranges.  Replaces _grid_search_mse /
  * _grid_search_eager / _calculate_error (src/observers/mse_quant.py:19-141,255-284).
- * Writes the best min/max per group (W's dtype).  err_table: float [steps, groups]
- * scratch (b200q_observe_mse_workspace_bytes). */
+ * Writes the best min/max per group (W's dtype).  GROUP / TENSOR_GROUP (group a power of two,
+ * 8..256) and CHANNEL strategies.  scratch: b200q_observe_mse_workspace_bytes (per-candidate
+ * "some group improved" flags that reproduce the reference's global early stop). */
 size_t b200q_observe_mse_workspace_bytes(int64_t N, int64_t K, const b200q_qargs* qa, int steps);
 int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw,
                       const b200q_qargs* qa, float maxshrink, int patience, float grid,
@@ -192,6 +196,10 @@ int b200q_scatter_columns_cast(const float* Wf, int64_t N, int64_t K, int64_t ld
  * W[:,i]=0; then H_ii += percdamp * mean(diag H). */
 int b200q_gptq_prepare(float* H, int64_t K, int64_t ldh, float* Wf, int64_t N, int64_t ldf,
                        float percdamp, void* stream);
+/* W[:, i] = 0 where diag[i * diag_stride] == 0 (gptq_quantize.py:144-146), for modules that
+ * share one Hessian (q/k/v, gate/up): `diag` is the diagonal saved before b200q_gptq_prepare. */
+int b200q_gptq_zero_dead_columns(const float* diag, int64_t diag_stride, int64_t K, float* Wf,
+                                 int64_t N, int64_t ldf, void* stream);
 
 /* In place: H (symmetric positive definite, full storage) -> upper-triangular U with
  * U^T U = H^-1, strictly-lower part zeroed.  Stands in for cholesky -> cholesky_inverse ->

@@ -45,6 +45,7 @@ _qa = C.POINTER(QArgs)
 SIGNATURES = {
     "b200q_version": (C.c_char_p, []),
     "b200q_last_error": (C.c_char_p, []),
+    "b200q_launch_count": (C.c_longlong, []),
     "b200q_observe_minmax_workspace_bytes": (C.c_size_t, [_i64, _i64, _qa]),
     "b200q_observe_minmax": (_i, [_p, _i, _i64, _i64, _i64, _qa, _p, _p, _p, _p]),
     "b200q_absmax_accumulate": (_i, [_p, _p, _i, _i64, _p, _p]),
@@ -65,6 +66,7 @@ SIGNATURES = {
     "b200q_permute_hessian": (_i, [_p, _i64, _i64, _p, _p, _i64, _p]),
     "b200q_scatter_columns_cast": (_i, [_p, _i64, _i64, _i64, _p, _p, _i, _i64, _p]),
     "b200q_gptq_prepare": (_i, [_p, _i64, _i64, _p, _i64, _i64, _f, _p]),
+    "b200q_gptq_zero_dead_columns": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p]),
     "b200q_gptq_factor_workspace_bytes": (C.c_size_t, [_i64]),
     "b200q_gptq_factor": (_i, [_p, _i64, _i64, _p, _p, _p]),
     "b200q_gptq_sweep_workspace_bytes": (C.c_size_t, [_i64, _i64, _i]),

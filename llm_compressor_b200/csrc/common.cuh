@@ -26,7 +26,13 @@ inline int cuda_status(cudaError_t e, const char* what) {
     int _st = b200q::cuda_status((expr), #expr);             \
     if (_st != B200Q_OK) return _st;                         \
   } while (0)
-#define B200Q_LAUNCH_CHECK() B200Q_TRY(cudaGetLastError())
+// every kernel launch is followed by this check; it also feeds b200q_launch_count()
+void count_launch();
+#define B200Q_LAUNCH_CHECK()          \
+  do {                                \
+    b200q::count_launch();            \
+    B200Q_TRY(cudaGetLastError());    \
+  } while (0)
 
 // Grid size for a grid-stride kernel: whole multiples of the SM count, capped by the work.
 inline int grid_for(int64_t blocks_needed, int blocks_per_sm) {

@@ -85,14 +85,14 @@ __global__ void scatter_cols_kernel(const float* __restrict__ Wf, int64_t N, int
 
 // ---------------------------------------------------------------------------------------
 // dead columns and dampening
-__global__ void zero_dead_columns_kernel(const float* __restrict__ H, int64_t K, int64_t ldh,
+__global__ void zero_dead_columns_kernel(const float* __restrict__ H, int64_t K, int64_t diag_stride,
                                          float* __restrict__ W, int64_t N, int64_t ldf) {
   // one warp per column; only dead columns touch W
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   for (int64_t c = warp; c < K; c += nwarps) {
-    if (H[c * ldh + c] == 0.0f)
+    if (H[c * diag_stride] == 0.0f)
       for (int64_t r = lane; r < N; r += 32) W[r * ldf + c] = 0.0f;
   }
 }
@@ -259,10 +259,19 @@ int b200q_gptq_prepare(float* H, int64_t K, int64_t ldh, float* Wf, int64_t N, i
   if (!H || K <= 0 || ldh < K) return B200Q_ERR_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   if (Wf && N > 0) {
-    zero_dead_columns_kernel<<<grid_for((K * 32 + 255) / 256, 4), 256, 0, st>>>(H, K, ldh, Wf, N, ldf);
+    zero_dead_columns_kernel<<<grid_for((K * 32 + 255) / 256, 4), 256, 0, st>>>(H, K, ldh + 1, Wf, N, ldf);
     B200Q_LAUNCH_CHECK();
   }
   damp_kernel<<<1, 1024, 0, st>>>(H, K, ldh, percdamp);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_gptq_zero_dead_columns(const float* diag, int64_t diag_stride, int64_t K, float* Wf, int64_t N,
+                                 int64_t ldf, void* stream) {
+  if (!diag || !Wf || K <= 0 || N <= 0 || ldf < K || diag_stride <= 0) return B200Q_ERR_ARG;
+  zero_dead_columns_kernel<<<grid_for((K * 32 + 255) / 256, 4), 256, 0, (cudaStream_t)stream>>>(diag, K, diag_stride,
+                                                                                                Wf, N, ldf);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

@@ -5,12 +5,15 @@
 // write packed codes with 4..16-byte stores.  Grids are whole multiples of the SM count.
 #include "common.cuh"
 
+#include <atomic>
 #include <mutex>
 #include <string>
 
 namespace b200q {
 
 static thread_local std::string g_last_error;
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 void set_last_error(const char* what, cudaError_t e) {
   g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
 }
@@ -733,6 +736,7 @@ extern "C" {
 
 const char* b200q_version(void) { return "b200q 0.1 (sm_100a)"; }
 const char* b200q_last_error(void) { return g_last_error.c_str(); }
+long long b200q_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 size_t b200q_observe_minmax_workspace_bytes(int64_t, int64_t, const b200q_qargs* qa) {
   return (qa && qa->strategy == B200Q_TENSOR) ? sizeof(float) * 2 * kTensorPartialBlocks : 0;

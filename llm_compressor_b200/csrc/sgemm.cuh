@@ -210,6 +210,7 @@ inline cudaError_t launch(int trans, const float* A, int64_t lda, const float* B
   int grid = grid_for(tiles, 2);
   if (trans == kNT) sgemm_kernel<kNT><<<grid, THREADS, 0, st>>>(a, tiles);
   else sgemm_kernel<kNN><<<grid, THREADS, 0, st>>>(a, tiles);
+  count_launch();
   return cudaGetLastError();
 }
 

@@ -2,11 +2,18 @@
 
 Drop-in for ``make_empty_hessian`` / ``accumulate_hessian`` / ``quantize_weight`` of
 src/llmcompressor/modifiers/gptq/gptq_quantize.py (:19-25, :28-64, :67-264).
+
+Two things go beyond the reference's per-module functions, both without changing results:
+``accumulate_hessian_lower`` / ``finalize_hessian`` keep only the lower triangle current
+between hook calls (the mirror and the division by the sample count happen once), and
+``factor_hessian`` lets modules that see the same input (q/k/v, gate/up, the experts of an
+all-expert calibration) share one permutation and one factor U instead of recomputing them.
 """
 from __future__ import annotations
 
-import math
 import warnings
+from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
@@ -15,9 +22,15 @@ from .observers import Observer
 from .quant_args import QuantizationArgs
 
 __all__ = ["make_empty_hessian", "accumulate_hessian", "accumulate_hessian_lower",
-           "finalize_hessian", "quantize_weight", "GPTQ_PRECISION"]
+           "finalize_hessian", "factor_hessian", "HessianFactor", "quantize_weight",
+           "GPTQ_PRECISION"]
 
 GPTQ_PRECISION = torch.float32
+
+_NOT_PD_MESSAGE = (
+    "Failed to invert hessian due to numerical instability. Consider increasing "
+    "GPTQModifier.dampening_frac, increasing the number of calibration samples, or shuffling "
+    "the calibration dataset. Falling back to round-to-nearest for this module.")
 
 
 def make_empty_hessian(module: torch.nn.Module, device=None) -> torch.Tensor:
@@ -72,22 +85,53 @@ def accumulate_hessian(inp, module, H, num_samples):
     return H, num_samples
 
 
-def quantize_weight(module, quant_args, hessian: torch.Tensor, blocksize: int = 128,
-                    percdamp: float = 0.01):
+@dataclass
+class HessianFactor:
+    """What the sweep needs from one Hessian: the act-order permutation (or None), the
+    diagonal before dead-column patching, and U (upper, U^T U = (H + damp I)^-1) or None
+    when the factorisation failed and the identity stands in for it."""
+    K: int
+    perm: Optional[torch.Tensor]
+    diag: torch.Tensor
+    U: Optional[torch.Tensor]
+    ok: bool
+
+
+def factor_hessian(hessian: torch.Tensor, percdamp: float = 0.01, actorder=None) -> HessianFactor:
+    """Permute (act-order), patch dead columns, dampen and factor ``hessian`` (consumed)."""
+    H = hessian
+    K = H.shape[0]
+    if H.shape != (K, K) or H.dtype != torch.float32:
+        raise ValueError("hessian must be a square float32 matrix")
+    perm = None
+    if actorder:
+        perm = ops.actorder_perm(H)
+        H = ops.permute_hessian(H, perm)
+    diag = H.diagonal().clone()
+    ops.gptq_prepare(H, None, percdamp)
+    status = ops.gptq_factor(H)
+    if status == _lib.NOT_POSITIVE_DEFINITE:
+        warnings.warn(_NOT_PD_MESSAGE)
+        return HessianFactor(K, perm, diag, None, False)
+    return HessianFactor(K, perm, diag, H, True)
+
+
+def quantize_weight(module, quant_args, hessian: Optional[torch.Tensor], blocksize: int = 128,
+                    percdamp: float = 0.01, factor: Optional[HessianFactor] = None):
     """GPTQ-quantise ``module.weight`` given its Hessian (already divided by the sample
     count).  Returns ``(loss, dict)`` with the fake-quantised weight in the original dtype,
     ``weight_scale``, ``weight_zero_point`` and, where they apply, ``weight_global_scale`` and
     ``weight_g_idx``.  ``hessian`` is consumed.  ``module.weight_observer`` must hold
-    statistics unless act-order "group" re-observes; ``module.weight`` is not touched."""
+    statistics unless act-order "group" re-observes; ``module.weight`` is not touched.
+
+    ``factor`` (from ``factor_hessian`` with the same ``percdamp`` and act-order setting) may
+    be passed instead of ``hessian`` when several modules share one Hessian."""
     args = QuantizationArgs.of(quant_args)
     strategy, actorder = args.strategy, args.actorder
     weight = module.weight.data if isinstance(module.weight, torch.nn.Parameter) else module.weight
     final_dtype = weight.dtype
     observer: Observer = module.weight_observer
     N, K = weight.shape
-    H = hessian
-    if H.shape != (K, K) or H.dtype != torch.float32:
-        raise ValueError("hessian must be float32 [in_features, in_features]")
     if strategy not in ("tensor", "channel", "group", "tensor_group", "block"):
         raise ValueError(f"Quantization strategy is not supported for GPTQ: {strategy}")
 
@@ -96,19 +140,22 @@ def quantize_weight(module, quant_args, hessian: torch.Tensor, blocksize: int = 
                       "falling back to actorder=None for this module.")
         actorder = None
 
-    perm = None
-    if actorder:
-        perm = ops.actorder_perm(H)
-        W = ops.gather_columns_f32(weight, perm)
-        H = ops.permute_hessian(H, perm)
-    else:
-        W = ops.gather_columns_f32(weight, None)
+    if factor is None:
+        if hessian is None or hessian.shape != (K, K):
+            raise ValueError("hessian must be float32 [in_features, in_features]")
+        factor = factor_hessian(hessian, percdamp, actorder)
+    elif factor.K != K or (factor.perm is not None) != bool(actorder):
+        raise ValueError("factor does not match this module / act-order setting")
+    perm = factor.perm
+
+    W = ops.gather_columns_f32(weight, perm)
 
     if actorder == "group":
         observer.delete_statistics(check_fused=False)
         observer(W)
 
     col_group = None
+    g_idx = None
     if strategy in ("group", "tensor_group", "block"):
         divisor = args.group_size if strategy != "block" else args.block_structure[1]
         g_idx = torch.arange(K, device=W.device, dtype=torch.int32) // divisor
@@ -119,18 +166,9 @@ def quantize_weight(module, quant_args, hessian: torch.Tensor, blocksize: int = 
     qparams = observer.get_qparams()
     scale, zero_point, global_scale = qparams["scale"], qparams["zero_point"], qparams["global_scale"]
 
-    ops.gptq_prepare(H, W, percdamp)
-    status = ops.gptq_factor(H)
-    U = H
-    if status == _lib.NOT_POSITIVE_DEFINITE:
-        warnings.warn(
-            "Failed to invert hessian due to numerical instability. Consider increasing "
-            "GPTQModifier.dampening_frac, increasing the number of calibration samples, or "
-            "shuffling the calibration dataset. Falling back to round-to-nearest for this module.")
-        U = None
-
-    losses = ops.gptq_sweep(W, U, scale, zero_point, args, blocksize=blocksize, col_group=col_group,
-                            global_scale=global_scale)
+    ops.gptq_zero_dead_columns(factor.diag, W)
+    losses = ops.gptq_sweep(W, factor.U, scale, zero_point, args, blocksize=blocksize,
+                            col_group=col_group, global_scale=global_scale)
 
     Wq = ops.scatter_columns_cast(W, final_dtype, perm)
     loss = float(losses.sum().item())

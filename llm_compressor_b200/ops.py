@@ -275,9 +275,17 @@ def scatter_columns_cast(wf: torch.Tensor, dtype: torch.dtype, perm=None) -> tor
 def gptq_prepare(H: torch.Tensor, wf: torch.Tensor, percdamp: float):
     _need_cuda(H, wf)
     K = H.shape[0]
-    N = wf.shape[0]
-    check(_lib.load().b200q_gptq_prepare(ptr(H), K, H.stride(0), ptr(wf), N, wf.stride(0),
+    N, ldf = (wf.shape[0], wf.stride(0)) if wf is not None else (0, K)
+    check(_lib.load().b200q_gptq_prepare(ptr(H), K, H.stride(0), ptr(wf), N, ldf,
                                          float(percdamp), stream_ptr()), "b200q_gptq_prepare")
+
+
+def gptq_zero_dead_columns(diag: torch.Tensor, wf: torch.Tensor):
+    _need_cuda(diag, wf)
+    assert diag.dtype == torch.float32 and diag.ndim == 1
+    check(_lib.load().b200q_gptq_zero_dead_columns(ptr(diag), diag.stride(0), diag.numel(), ptr(wf),
+                                                   wf.shape[0], wf.stride(0), stream_ptr()),
+          "b200q_gptq_zero_dead_columns")
 
 
 def gptq_factor(H: torch.Tensor) -> int:
