@@ -1,0 +1,500 @@
+"""``GPTQModifier`` and ``QuantizationModifier`` with the reference's fields, lifecycle hooks
+and error behaviour, running on the b200q kernels.
+
+Mirrors src/llmcompressor/modifiers/gptq/base.py:47-400,
+src/llmcompressor/modifiers/quantization/quantization/{base.py:24-110,mixin.py:56-440},
+src/llmcompressor/modifiers/quantization/calibration.py:36-162 and the hook helper
+src/llmcompressor/modifiers/utils/hooks.py:19-110.  Only weight quantisation is on this
+package's path: schemes that also name input activations keep that information for the
+checkpoint format, nothing is calibrated for it.
+"""
+from __future__ import annotations
+
+import contextlib
+import re
+import time
+import warnings
+from typing import Any, Iterable, Optional
+
+import torch
+
+from . import dist as bdist
+from . import gptq
+from .observers import Observer, fuse_weight_observers
+from .quant_args import (PRESET_SCHEMES, QuantizationArgs, QuantizationScheme,
+                         preset_name_to_scheme)
+
+__all__ = ["GPTQModifier", "QuantizationModifier", "match_named_modules", "HooksMixin"]
+
+_STATIC = "static"
+_UNSET = object()
+
+
+# ------------------------------------------------------------------------------------------
+# module matching (compressed-tensors utils/match.py:34-70,344-456)
+def _match_one(name: str, module: torch.nn.Module, target: str) -> bool:
+    if target.startswith("re:"):
+        return re.match(target[3:], name) is not None
+    if name == target:
+        return True
+    return any(cls.__name__ == target for cls in type(module).__mro__)
+
+
+def match_named_modules(model: torch.nn.Module, targets: Iterable[str], ignore: Iterable[str] = ()):
+    """(name, module) pairs selected by ``targets`` and not by ``ignore``, in
+    ``model.named_modules()`` order.  A target selects a module if it equals its name, if a
+    ``re:`` target matches the name from its start, or if it names a class in the module's MRO."""
+    targets, ignore = list(targets or []), list(ignore or [])
+    out = []
+    for name, module in model.named_modules():
+        if not any(_match_one(name, module, t) for t in targets):
+            continue
+        if any(_match_one(name, module, t) for t in ignore):
+            continue
+        out.append((name, module))
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+class HooksMixin:
+    """Forward hooks that can be switched off globally (hooks.py:54-66)."""
+
+    _HOOKS_DISABLED = False
+
+    def __init__(self):
+        self._hooks: list = []
+
+    @classmethod
+    @contextlib.contextmanager
+    def disable_hooks(cls):
+        prev = HooksMixin._HOOKS_DISABLED
+        HooksMixin._HOOKS_DISABLED = True
+        try:
+            yield
+        finally:
+            HooksMixin._HOOKS_DISABLED = prev
+
+    def register_hook(self, module: torch.nn.Module, fn, kind: str = "forward"):
+        def wrapped(*a, **k):
+            if HooksMixin._HOOKS_DISABLED:
+                return None
+            return fn(*a, **k)
+        handle = getattr(module, f"register_{kind}_hook")(wrapped)
+        self._hooks.append(handle)
+        return handle
+
+    def remove_hooks(self):
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+
+
+# ------------------------------------------------------------------------------------------
+class QuantizationMixin(HooksMixin):
+    """Scheme resolution, qparam attachment and observer life cycle (mixin.py:56-440)."""
+
+    def __init__(self, config_groups=None, targets="Linear", ignore=None, scheme=None,
+                 kv_cache_scheme=None, weight_observer=None, input_observer=None,
+                 output_observer=None, observer=None, bypass_divisibility_checks=False):
+        HooksMixin.__init__(self)
+        self.config_groups = config_groups
+        self.targets = [targets] if isinstance(targets, str) else list(targets)
+        self.ignore = list(ignore or [])
+        self.scheme = scheme
+        self.kv_cache_scheme = kv_cache_scheme
+        self.weight_observer = weight_observer
+        self.input_observer = input_observer
+        self.output_observer = output_observer
+        self.observer = observer
+        self.bypass_divisibility_checks = bypass_divisibility_checks
+        if kv_cache_scheme is not None:
+            raise NotImplementedError("kv-cache quantisation is outside this package's path")
+        self._resolved: Optional[dict] = None
+        self._module_names: dict = {}
+
+    # ---- scheme resolution ---------------------------------------------------------------
+    def _apply_observer_overrides(self, scheme: QuantizationScheme) -> QuantizationScheme:
+        has_individual = any(o is not None for o in (self.weight_observer, self.input_observer,
+                                                     self.output_observer))
+        if has_individual and self.observer is not None:
+            raise ValueError(
+                "Cannot specify both individual observer parameters (weight_observer, "
+                "input_observer, output_observer) and observer dict. "
+                "Please use either individual parameters or the observer dict.")
+        weight_obs = self.weight_observer
+        if self.observer is not None:
+            weight_obs = self.observer.get("weights", weight_obs)
+        if weight_obs is not None and scheme.weights is not None:
+            scheme.weights = scheme.weights.model_copy(update={"observer": weight_obs})
+        return scheme
+
+    def resolve_quantization_config(self) -> dict:
+        """``{"group_i": QuantizationScheme}`` (mixin.py:335-386)."""
+        scheme, config_groups = self.scheme, self.config_groups
+        if scheme is not None and config_groups is not None:
+            raise ValueError("Please specify either `scheme` or `config_groups`")
+        groups = {}
+        if scheme is not None:
+            if isinstance(scheme, str):
+                scheme = {scheme: self.targets}
+            for idx, (key, tg) in enumerate(scheme.items()):
+                if key.upper() not in PRESET_SCHEMES:
+                    raise ValueError(f"Unknown preset scheme {key}")
+                tg = [tg] if isinstance(tg, str) else list(tg)
+                groups[f"group_{idx}"] = self._apply_observer_overrides(preset_name_to_scheme(key, tg))
+        elif config_groups:
+            for name, g in config_groups.items():
+                if isinstance(g, dict):
+                    w = g.get("weights")
+                    g = QuantizationScheme(targets=list(g.get("targets", self.targets)),
+                                           weights=None if w is None else QuantizationArgs.of(w),
+                                           input_activations=g.get("input_activations"))
+                elif not isinstance(g, QuantizationScheme):
+                    g = QuantizationScheme(targets=list(g.targets),
+                                           weights=None if g.weights is None else QuantizationArgs.of(g.weights),
+                                           input_activations=getattr(g, "input_activations", None))
+                groups[name] = self._apply_observer_overrides(g)
+        else:
+            groups["group_0"] = self._apply_observer_overrides(
+                QuantizationScheme(targets=list(self.targets), weights=QuantizationArgs(num_bits=8)))
+        return groups
+
+    # ---- attach / detach -------------------------------------------------------------------
+    def initialize_quantization(self, model: torch.nn.Module) -> None:
+        """Attach ``quantization_scheme`` and empty scale / zero-point (/ global scale / g_idx)
+        parameters to every targeted module (CT lifecycle/initialize.py:132-254)."""
+        groups = self.resolve_quantization_config()
+        self._resolved = groups
+        bad = []
+        for scheme in groups.values():
+            for name, module in match_named_modules(model, scheme.targets, self.ignore):
+                if not hasattr(module, "weight") or module.weight is None or module.weight.ndim != 2:
+                    continue
+                if isinstance(module, torch.nn.Embedding):
+                    continue
+                w = scheme.weights
+                if w is None:
+                    continue
+                N, K = module.weight.shape
+                if (w.strategy in ("group", "tensor_group") and K >= w.group_size and K % w.group_size
+                        and not self.bypass_divisibility_checks):
+                    bad.append((name, K, w.group_size))
+                    continue
+                module.quantization_scheme = scheme
+                self._module_names[module] = name
+                dev, dt = module.weight.device, module.weight.dtype
+                shape = w.qparam_shape(N, K)
+
+                def reg(pname, t):
+                    module.register_parameter(pname, torch.nn.Parameter(t, requires_grad=False))
+                if w.strategy == "tensor_group":
+                    reg("weight_global_scale", torch.empty(1, dtype=torch.float32, device=dev))
+                reg("weight_scale", torch.empty(shape, dtype=dt if dt.is_floating_point else torch.float16,
+                                                device=dev))
+                reg("weight_zero_point", torch.zeros(shape, dtype=w.zp_dtype, device=dev))
+                if w.actorder == "group":
+                    reg("weight_g_idx", torch.full((K,), -1, dtype=torch.int32, device=dev))
+        if bad:
+            lines = "\n".join(f"  {n}: columns {k} not divisible by group_size {g}" for n, k, g in bad)
+            raise ValueError(
+                "The following layers have weight column counts that are not divisible by the "
+                f"quantization group size:\n{lines}\nAdd them to `ignore` or set "
+                "bypass_divisibility_checks=True")
+
+    def quantized_modules(self, model: torch.nn.Module):
+        return [(n, m) for n, m in model.named_modules() if hasattr(m, "quantization_scheme")
+                and m in self._module_names]
+
+    def start_calibration(self, model: torch.nn.Module) -> None:
+        for _, module in self.quantized_modules(model):
+            w = module.quantization_scheme.weights
+            module.weight_observer = Observer.load_from_registry(
+                w.observer or "memoryless_minmax", base_name="weight", args=w)
+        fuse_weight_observers(model)
+
+    def end_calibration(self, model: torch.nn.Module) -> None:
+        self.remove_hooks()
+        for _, module in self.quantized_modules(model):
+            if hasattr(module, "weight_observer"):
+                del module.weight_observer
+
+
+def observe(modules: Iterable[torch.nn.Module], base_name: str = "weight") -> None:
+    for m in modules:
+        obs = getattr(m, f"{base_name}_observer", None)
+        if obs is not None:
+            obs(m.weight.data)
+
+
+def update_qparams(modules: Iterable[torch.nn.Module], base_name: str = "weight") -> None:
+    """Copy the observer's scale / zero point / global scale into the module's parameters
+    (calibration.py:109-162)."""
+    for m in modules:
+        obs = getattr(m, f"{base_name}_observer", None)
+        if obs is None:
+            continue
+        if not obs.has_statistics:
+            warnings.warn(f"Observer of {type(m).__name__} has no statistics; qparams not updated")
+            continue
+        qp = obs.get_qparams()
+        getattr(m, f"{base_name}_scale").data.copy_(qp["scale"].reshape(getattr(m, f"{base_name}_scale").shape))
+        getattr(m, f"{base_name}_zero_point").data.copy_(qp["zero_point"].reshape(
+            getattr(m, f"{base_name}_zero_point").shape))
+        if qp["global_scale"] is not None and hasattr(m, f"{base_name}_global_scale"):
+            getattr(m, f"{base_name}_global_scale").data.copy_(qp["global_scale"])
+
+
+# ------------------------------------------------------------------------------------------
+class QuantizationModifier(QuantizationMixin):
+    """Round-to-nearest weight quantisation: observe weights, write qparams; the weight is
+    left as is until it is packed at save time (quantization/base.py:24-110)."""
+
+    requires_calibration_data = False
+
+    def on_initialize(self, model, **_):
+        self.initialize_quantization(model)
+        return True
+
+    def on_calibration_start(self, model, **_):
+        self.start_calibration(model)
+
+    def on_sequential_epoch_end(self, model, modules: Iterable[torch.nn.Module], **_):
+        modules = [m for m in modules if hasattr(m, "weight_observer")]
+        if bdist.is_distributed():
+            # owners by weight size; each rank observes its share, scales are broadcast
+            items, rank_to, to_rank = bdist.greedy_bin_packing(
+                list(modules), bdist.world_size(), item_weight_fn=lambda m: m.weight.numel())
+            mine = rank_to[bdist.rank()]
+            observe(mine)
+            update_qparams(mine)
+            bdist.broadcast_module_params(items, to_rank,
+                                          ("weight_scale", "weight_zero_point", "weight_global_scale"))
+        else:
+            observe(modules)
+            update_qparams(modules)
+
+    def on_calibration_end(self, model, **_):
+        self.end_calibration(model)
+
+    def on_finalize(self, model, **_):
+        return True
+
+
+class GPTQModifier(QuantizationMixin):
+    """GPTQ weight quantisation (gptq/base.py:47-400).
+
+    Forward hooks accumulate H += 2 X^T X per calibration batch; at the end of each sequential
+    epoch the modules of that epoch are observed and quantised column block by column block.
+    Modules that receive the very same input tensor (q/k/v, gate/up, experts under all-expert
+    calibration) share one Hessian accumulation and one factorisation; set
+    ``share_hessians=False`` to keep one per module like the reference.
+    """
+
+    requires_calibration_data = True
+
+    def __init__(self, block_size: int = 128, dampening_frac: Optional[float] = 0.01,
+                 actorder: Any = _UNSET, offload_hessians: bool = False, share_hessians: bool = True,
+                 **quant_kwargs):
+        kw = dict(quant_kwargs)
+        kw.setdefault("targets", "Linear")
+        super().__init__(**kw)
+        self.block_size = block_size
+        self.dampening_frac = dampening_frac
+        self.actorder = actorder
+        self.offload_hessians = offload_hessians
+        self.share_hessians = share_hessians
+        self._groups: dict = {}        # module -> _HessianGroup
+        self._num_samples: dict = {}   # module -> None (membership: modules awaiting compression)
+        self.losses: dict = {}
+
+    # ---- config ------------------------------------------------------------------------------
+    def resolve_quantization_config(self) -> dict:
+        groups = super().resolve_quantization_config()
+
+        def resolve(existing):
+            if self.actorder is _UNSET:  # sentinel default only fills an unset scheme value
+                return "weight" if existing is None else existing
+            mine = QuantizationArgs(num_bits=4, group_size=128, actorder=self.actorder).actorder \
+                if self.actorder not in (None, False) else None
+            if existing is None or mine == existing:
+                return mine
+            raise ValueError(
+                "Cannot resolve activation ordering when both `GPTQModifier.actorder` and "
+                f"`QuantizationScheme.actorder` are provided and differ ({self.actorder}, {existing}). "
+                "Either unset `GPTQModifier.actorder` or remove `actorder` from config groups.")
+
+        for scheme in groups.values():
+            w = scheme.weights
+            if w is None:
+                continue
+            # the modifier-level setting is applied to every strategy, as the reference does by
+            # assigning past the argument validation (base.py:176-192): "weight"/"static" then
+            # permutes the sweep of channel / tensor / block schemes too
+            a = resolve(w.actorder)
+            if a == "group" and w.strategy not in ("group", "tensor_group"):
+                warnings.warn(f"ActivationOrdering.GROUP is not compatible with strategy={w.strategy}; "
+                              "falling back to actorder=None for this scheme.")
+                a = None
+            scheme.weights = _with_actorder(w, a)
+        return groups
+
+    # ---- lifecycle -----------------------------------------------------------------------------
+    def on_initialize(self, model, **_):
+        self.initialize_quantization(model)
+        return True
+
+    def on_calibration_start(self, model, **_):
+        self.start_calibration(model)
+        added = False
+        for _, module in self.quantized_modules(model):
+            if isinstance(module, torch.nn.Embedding):
+                continue
+            if getattr(module, "quantization_scheme", None) is None or module.quantization_scheme.weights is None:
+                continue
+            self.register_hook(module, self.calibrate_module, "forward")
+            added = True
+        if not added:
+            raise ValueError(
+                "GPTQModifier requires a weight quantization config be specified by this modifier or a "
+                "modifier preceding it")
+
+    def calibrate_module(self, module, args, _output):
+        inp = args[0]
+        group = self._groups.get(module)
+        if group is None:
+            group = self._find_shared(inp) if self.share_hessians else None
+            if group is None:
+                group = _HessianGroup(module, offload=self.offload_hessians)
+            else:
+                group.members.append(module)
+            self._groups[module] = group
+            self._num_samples[module] = None
+        group.accumulate(inp)
+
+    def _find_shared(self, inp):
+        for g in {id(g): g for g in self._groups.values()}.values():
+            if g.same_input(inp):
+                return g
+        return None
+
+    def on_sequential_epoch_end(self, model, modules: Iterable[torch.nn.Module], **_):
+        mods = [m for m in modules if m in self._num_samples]
+        observe(mods, "weight")
+        self.compress_modules(mods)
+
+    def compress_modules(self, modules=None):
+        modules = list(self._num_samples.keys()) if modules is None else list(modules)
+        if not bdist.is_distributed():
+            self.compress_module_list(modules)
+            return
+        # owners by Hessian width over the distinct Hessians (base.py:306-318)
+        groups = list({id(self._groups[m]): self._groups[m] for m in modules}.values())
+        items, rank_to, to_rank = bdist.greedy_bin_packing(groups, bdist.world_size(),
+                                                           item_weight_fn=lambda g: g.H.shape[0])
+        bdist.reduce_hessians(items, to_rank)
+        mine = [m for m in modules if to_rank[self._groups[m]] == bdist.rank()]
+        self.compress_module_list(mine)
+        mod_rank = {m: to_rank[self._groups[m]] for m in modules}
+        bdist.broadcast_module_params(modules, mod_rank, ("weight", "weight_scale", "weight_zero_point",
+                                                          "weight_g_idx", "weight_global_scale"))
+        for m in modules:
+            self._num_samples.pop(m, None)
+            self._groups.pop(m, None)
+
+    def compress_module_list(self, module_list):
+        factors = {}
+        # how many distinct act-order settings still need each shared Hessian
+        pending = {}
+        for module in module_list:
+            g = self._groups[module]
+            pending.setdefault(id(g), set()).add(module.quantization_scheme.weights.actorder)
+        for module in module_list:
+            group = self._groups.pop(module)
+            self._num_samples.pop(module, None)
+            qargs = module.quantization_scheme.weights
+            name = self._module_names.get(module, type(module).__name__)
+            t0 = time.perf_counter()
+            key = (id(group), qargs.actorder)
+            if key not in factors:
+                left = pending[id(group)]
+                left.discard(qargs.actorder)
+                H = group.finalized(keep=bool(left))  # factor_hessian consumes its argument
+                factors[key] = gptq.factor_hessian(H, self.dampening_frac, qargs.actorder)
+            with torch.no_grad():
+                loss, out = gptq.quantize_weight(module, qargs, None, blocksize=self.block_size,
+                                                 percdamp=self.dampening_frac, factor=factors[key])
+            self.losses[name] = loss
+            self._log_metric(name, time.perf_counter() - t0, loss)
+            for attr, val in out.items():
+                if attr == "weight":
+                    module.weight.data.copy_(val)
+                elif hasattr(module, attr):
+                    p = getattr(module, attr)
+                    p.data.copy_(val.reshape(p.shape))
+                else:
+                    module.register_parameter(attr, torch.nn.Parameter(val, requires_grad=False))
+
+    @staticmethod
+    def _log_metric(name, seconds, loss):
+        # shape of the reference's METRIC lines (src/llmcompressor/utils/metric_logging.py:42-65)
+        import logging
+        logging.getLogger("llm_compressor_b200").info("METRIC - %s time %.2fs error %.2f", name, seconds, loss)
+
+    def on_calibration_end(self, model, **_):
+        self.end_calibration(model)
+
+    def on_finalize(self, model, **_):
+        if len(self._num_samples) > 0:
+            raise ValueError(f"Failed to compress {len(self._num_samples)} modules")
+        self._groups, self._num_samples = {}, {}
+        return True
+
+
+def _with_actorder(qargs: QuantizationArgs, actorder):
+    a = qargs.model_copy()
+    object.__setattr__(a, "actorder", actorder)
+    return a
+
+
+class _HessianGroup:
+    """One Hessian shared by the modules that see the same input."""
+
+    def __init__(self, module, offload=False):
+        self.members = [module]
+        K = module.weight.shape[1]
+        self.device = module.weight.device
+        self.H = torch.zeros((K, K), dtype=torch.float32, device=self.device)
+        self.n = 0
+        self._last = None  # (tensor kept alive, version) of the batch accumulated last
+        self.offload = offload
+        self._final = None
+
+    def same_input(self, inp: torch.Tensor) -> bool:
+        if self._last is None:
+            return False
+        t, ver = self._last
+        return (t.data_ptr() == inp.data_ptr() and t.shape == inp.shape and t.stride() == inp.stride()
+                and t.dtype == inp.dtype and ver == inp._version)
+
+    def accumulate(self, inp: torch.Tensor) -> None:
+        if self.same_input(inp):
+            return  # another member already added this batch
+        if self.offload and self.H.device != self.device:
+            self.H = self.H.to(self.device)
+        self.H, self.n = gptq.accumulate_hessian_lower(inp, self.H, self.n)
+        self._last = (inp, inp._version)
+        if self.offload:
+            self.H = self.H.to("cpu")
+
+    def finalized(self, keep: bool = False) -> torch.Tensor:
+        """Full symmetric H / n.  The caller's factorisation consumes the matrix it gets;
+        ``keep`` asks for a copy because another act-order setting still needs H."""
+        self._last = None
+        if self._final is None:
+            H = self.H.to(self.device)
+            self.H = None
+            self._final = gptq.finalize_hessian(H, self.n)
+        out = self._final.clone() if keep else self._final
+        if not keep:
+            self._final = None
+        return out

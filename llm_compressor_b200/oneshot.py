@@ -1,0 +1,236 @@
+"""``oneshot`` entry point and the two calibration drivers it needs.
+
+Signature and behaviour follow src/llmcompressor/entrypoints/oneshot.py:316-479.  The
+drivers are this package's own, not the reference's fx tracer: the sequential driver walks the
+model's decoder layers (the modules named by ``sequential_targets``, default the model's
+``_no_split_modules``) in the order of src/llmcompressor/pipelines/sequential/pipeline.py:136-178
+(calibration pass with hooks, epoch end, propagation pass without hooks); the data-free driver is
+src/llmcompressor/pipelines/data_free/pipeline.py:18-38.  Activations stay in HBM between layers.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Iterable, Optional
+
+import torch
+
+from . import dist as bdist
+from .compressors import compress_state_dict, infer_module_format
+from .modifiers import HooksMixin
+
+__all__ = ["oneshot", "save_compressed_model"]
+
+
+class _StopForward(Exception):
+    pass
+
+
+def _as_batches(dataset, num_calibration_samples, max_seq_length, batch_size, device):
+    """Normalise the calibration data to a list of keyword dicts on ``device``."""
+    if dataset is None:
+        return []
+    if isinstance(dataset, torch.Tensor):
+        rows = [dataset[i] for i in range(dataset.shape[0])]
+    else:
+        rows = list(dataset)
+    samples = []
+    for item in rows:
+        if isinstance(item, dict):
+            d = {k: torch.as_tensor(v) for k, v in item.items()}
+        else:
+            d = {"input_ids": torch.as_tensor(item)}
+        d = {k: (v.unsqueeze(0) if v.ndim == 1 else v) for k, v in d.items()}
+        if max_seq_length:
+            d = {k: v[..., :max_seq_length] for k, v in d.items()}
+        samples.append(d)
+    if num_calibration_samples:
+        samples = samples[:num_calibration_samples]
+    if bdist.is_distributed():
+        keep = bdist.partition_samples(len(samples), bdist.rank(), bdist.world_size())
+        samples = [samples[i] for i in keep]
+    batches = []
+    for i in range(0, len(samples), max(1, batch_size)):
+        chunk = samples[i:i + batch_size]
+        batches.append({k: torch.cat([c[k] for c in chunk], 0).to(device) for k in chunk[0]})
+    return batches
+
+
+def _sequential_layers(model, sequential_targets):
+    names = sequential_targets
+    if names is None:
+        names = list(getattr(model, "_no_split_modules", None) or [])
+    if isinstance(names, str):
+        names = [names]
+    layers = [(n, m) for n, m in model.named_modules() if type(m).__name__ in names]
+    # keep outermost matches only
+    out = []
+    for n, m in layers:
+        if not any(n.startswith(p + ".") for p, _ in out):
+            out.append((n, m))
+    if not out:
+        raise ValueError(f"no module of class {names} found for the sequential pipeline")
+    return out
+
+
+def _run_sequential(model, modifiers, batches, sequential_targets):
+    layers = _sequential_layers(model, sequential_targets)
+    first = layers[0][1]
+    captured = []
+
+    def grab(_m, args, kwargs):
+        captured.append((args, kwargs))
+        raise _StopForward()
+
+    handle = first.register_forward_pre_hook(grab, with_kwargs=True)
+    use_cache = getattr(getattr(model, "config", None), "use_cache", None)
+    if use_cache is not None:
+        model.config.use_cache = False
+    try:
+        with torch.no_grad(), HooksMixin.disable_hooks():
+            for b in batches:
+                try:
+                    model(**b)
+                except _StopForward:
+                    pass
+    finally:
+        handle.remove()
+        if use_cache is not None:
+            model.config.use_cache = use_cache
+    for m in modifiers:
+        m.on_calibration_start(model)
+    for _name, layer in layers:
+        with torch.no_grad():
+            for args, kwargs in captured:  # calibration pass: hooks fire
+                layer(*args, **kwargs)
+        members = list(layer.modules())
+        for m in modifiers:
+            m.on_sequential_epoch_end(model, members)
+        nxt = []
+        with torch.no_grad(), HooksMixin.disable_hooks():
+            for args, kwargs in captured:  # propagation pass with the quantised weights
+                out = layer(*args, **kwargs)
+                hidden = out[0] if isinstance(out, (tuple, list)) else out
+                nxt.append(((hidden,) + tuple(args[1:]), kwargs))
+        captured = nxt
+    for m in modifiers:
+        m.on_calibration_end(model)
+
+
+def _run_data_free(model, modifiers):
+    for m in modifiers:
+        m.on_calibration_start(model)
+    members = list(model.modules())
+    for m in modifiers:
+        m.on_sequential_epoch_end(model, members)
+    for m in modifiers:
+        m.on_calibration_end(model)
+
+
+def oneshot(model, recipe=None, dataset=None, num_calibration_samples: int = 512,
+            max_seq_length: Optional[int] = None, batch_size: int = 1, pipeline: str = "independent",
+            sequential_targets=None, moe_calibrate_all_experts: bool = True,
+            output_dir: Optional[str] = None, save_compressed: bool = True, **_ignored):
+    """Apply the recipe's modifiers to ``model`` in one calibration pass and return it.
+
+    ``recipe`` is a modifier or a list of modifiers (GPTQModifier / QuantizationModifier);
+    ``dataset`` is a DataLoader, a list of ``{"input_ids": ...}`` dicts / id tensors, or a
+    [samples, length] tensor of token ids; it may be None for data-free recipes."""
+    if isinstance(model, str):
+        raise NotImplementedError("pass an instantiated model; loading checkpoints is outside this package")
+    if recipe is None:
+        raise ValueError("oneshot needs a recipe")
+    modifiers = list(recipe) if isinstance(recipe, (list, tuple)) else [recipe]
+    if pipeline not in ("independent", "sequential", "datafree", "basic"):
+        raise ValueError(f"unknown pipeline {pipeline}")
+    device = next(model.parameters()).device
+    model.eval()
+    for m in modifiers:
+        m.on_initialize(model)
+    # "independent": each modifier runs alone with the driver it needs (pipelines/independent)
+    for m in modifiers:
+        needs_data = getattr(m, "requires_calibration_data", False) and pipeline != "datafree"
+        if needs_data:
+            batches = _as_batches(dataset, num_calibration_samples, max_seq_length, batch_size, device)
+            if not batches:
+                raise ValueError(f"{type(m).__name__} needs calibration data but no dataset was given")
+            _run_sequential(model, [m], batches, sequential_targets)
+        else:
+            _run_data_free(model, [m])
+    for m in modifiers:
+        m.on_finalize(model)
+    if output_dir is not None:
+        save_compressed_model(model, output_dir, compress=save_compressed)
+    return model
+
+
+def save_compressed_model(model, output_dir: str, compress: bool = True) -> dict:
+    """Write the compressed-tensors checkpoint layout: ``model.safetensors`` with
+    ``<module>.weight_packed`` / ``weight_scale`` / ``weight_shape`` / ... per quantised module,
+    and ``config.json`` carrying ``quantization_config`` (CT model_compressor.py:177-213).
+    Only rank 0 writes.  Returns the state dict that was written."""
+    from safetensors.torch import save_file
+
+    state, formats, groups, ignore = {}, set(), {}, []
+    quantised = {n: m for n, m in model.named_modules() if hasattr(m, "quantization_scheme")}
+    skip = set()
+    for name, mod in quantised.items():
+        scheme = mod.quantization_scheme
+        local = {k: getattr(mod, k).data for k in ("weight", "weight_scale", "weight_zero_point",
+                                                   "weight_global_scale", "weight_g_idx") if hasattr(mod, k)}
+        if "weight_g_idx" in local and bool((local["weight_g_idx"] < 0).any()):
+            local.pop("weight_g_idx")
+        fmt = infer_module_format(scheme)
+        formats.add(fmt)
+        out = compress_state_dict(local, scheme, fmt) if compress else local
+        for k, v in out.items():
+            state[f"{name}.{k}"] = v.detach().contiguous().cpu()
+        for k in ("weight", "weight_scale", "weight_zero_point", "weight_global_scale", "weight_g_idx"):
+            skip.add(f"{name}.{k}")
+        gname = next((g for g, s in groups.items() if s is scheme), None)
+        if gname is None:
+            groups[f"group_{len(groups)}"] = scheme
+    for k, v in model.state_dict().items():
+        if k not in skip and k not in state:
+            state[k] = v.detach().contiguous().cpu()
+    for n, m in model.named_modules():
+        if isinstance(m, torch.nn.Linear) and n not in quantised:
+            ignore.append(n)
+
+    def args_dict(a):
+        if a is None:
+            return None
+        return {"num_bits": a.num_bits, "type": a.type, "symmetric": a.symmetric, "group_size": a.group_size,
+                "strategy": a.strategy, "block_structure": a.block_structure, "dynamic": a.dynamic,
+                "actorder": a.actorder, "scale_dtype": None if a.scale_dtype is None else str(a.scale_dtype),
+                "zp_dtype": None if a.zp_dtype is None else str(a.zp_dtype), "observer": a.observer,
+                "observer_kwargs": a.observer_kwargs}
+
+    fmt = "dense" if not formats else (formats.pop() if len(formats) == 1 else "mixed-precision")
+    qconfig = {
+        "quant_method": "compressed-tensors", "format": fmt,
+        "quantization_status": "compressed" if compress else "frozen",
+        "config_groups": {g: {"targets": s.targets, "weights": args_dict(s.weights),
+                              "input_activations": args_dict(s.input_activations),
+                              "output_activations": None, "format": infer_module_format(s)}
+                          for g, s in groups.items()},
+        "ignore": ignore, "kv_cache_scheme": None, "sparsity_config": {}, "transform_config": {},
+        "global_compression_ratio": None,
+    }
+    if bdist.rank() == 0:
+        os.makedirs(output_dir, exist_ok=True)
+        # tied tensors (embeddings / lm_head) share storage; safetensors wants distinct buffers
+        seen = {}
+        for k in list(state):
+            p = state[k].data_ptr()
+            if p in seen and state[k].numel():
+                state[k] = state[k].clone()
+            seen[p] = k
+        save_file(state, os.path.join(output_dir, "model.safetensors"), metadata={"format": "pt"})
+        cfg = model.config.to_dict() if hasattr(model, "config") and hasattr(model.config, "to_dict") else {}
+        cfg["quantization_config"] = qconfig
+        with open(os.path.join(output_dir, "config.json"), "w") as f:
+            json.dump(cfg, f, indent=2, default=str)
+    if bdist.is_distributed():
+        torch.distributed.barrier()
+    return state

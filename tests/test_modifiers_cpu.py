@@ -1,0 +1,145 @@
+"""Host logic of the modifiers, matching rules and the multi-rank plumbing (gloo, CPU)."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from llm_compressor_b200 import dist as bdist
+from llm_compressor_b200.modifiers import GPTQModifier, QuantizationModifier, match_named_modules
+
+
+class Attn(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.q_proj = torch.nn.Linear(256, 256, bias=False)
+        self.k_proj = torch.nn.Linear(256, 64, bias=False)
+        self.v_proj = torch.nn.Linear(256, 64, bias=False)
+
+
+class Tiny(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.embed = torch.nn.Embedding(10, 256)
+        self.attn = Attn()
+        self.gate = torch.nn.Linear(256, 8, bias=False)
+        self.lm_head = torch.nn.Linear(256, 10, bias=False)
+
+
+def test_match_named_modules_rules():
+    m = Tiny()
+    names = [n for n, _ in match_named_modules(m, ["Linear"], ["lm_head"])]
+    assert names == ["attn.q_proj", "attn.k_proj", "attn.v_proj", "gate"]
+    names = [n for n, _ in match_named_modules(m, ["Linear"], ["lm_head", "re:.*gate$"])]
+    assert "gate" not in names
+    assert [n for n, _ in match_named_modules(m, ["re:attn\\..*"], [])] == ["attn.q_proj", "attn.k_proj", "attn.v_proj"]
+    assert [n for n, _ in match_named_modules(m, ["attn.q_proj"], [])] == ["attn.q_proj"]
+
+
+def test_scheme_resolution_and_actorder_defaults():
+    g = GPTQModifier(targets="Linear", scheme="W4A16", ignore=["lm_head"])
+    groups = g.resolve_quantization_config()
+    assert list(groups) == ["group_0"]
+    assert groups["group_0"].weights.actorder == "weight"  # reference default "static"
+    assert GPTQModifier(scheme="W4A16", actorder=None).resolve_quantization_config()["group_0"].weights.actorder is None
+    assert GPTQModifier(scheme="W4A16", actorder="group").resolve_quantization_config()["group_0"].weights.actorder == "group"
+    # channel strategy: static permutes, group falls back to None
+    assert GPTQModifier(scheme="FP8_DYNAMIC").resolve_quantization_config()["group_0"].weights.actorder == "weight"
+    with pytest.warns(UserWarning):
+        a = GPTQModifier(scheme="W8A16", actorder="group").resolve_quantization_config()["group_0"].weights.actorder
+    assert a is None
+    with pytest.raises(ValueError):
+        GPTQModifier(scheme="W4A16", config_groups={"g": {"targets": ["Linear"]}}).resolve_quantization_config()
+    with pytest.raises(ValueError):
+        QuantizationModifier(scheme="W4A16", weight_observer="mse", observer={"weights": "mse"}).resolve_quantization_config()
+    q = QuantizationModifier(scheme="W4A16", weight_observer="mse").resolve_quantization_config()
+    assert q["group_0"].weights.observer == "mse"
+
+
+def test_initialize_attaches_params_and_checks_divisibility():
+    m = Tiny().to(torch.bfloat16)
+    mod = GPTQModifier(targets="Linear", scheme="W4A16", ignore=["lm_head", "gate"])
+    mod.on_initialize(m)
+    assert m.attn.q_proj.weight_scale.shape == (256, 2) and m.attn.q_proj.weight_scale.dtype == torch.bfloat16
+    assert m.attn.k_proj.weight_zero_point.dtype == torch.int8
+    assert not hasattr(m.lm_head, "weight_scale") and not hasattr(m.embed, "weight_scale")
+    m2 = Tiny()
+    m2.odd = torch.nn.Linear(200, 8, bias=False)
+    with pytest.raises(ValueError, match="not divisible"):
+        GPTQModifier(targets="Linear", scheme="W4A16", ignore=["lm_head"]).on_initialize(m2)
+    m3 = Tiny()
+    nv = QuantizationModifier(targets="Linear", scheme="NVFP4A16", ignore=["lm_head"])
+    nv.on_initialize(m3)
+    assert m3.attn.q_proj.weight_global_scale.dtype == torch.float32
+
+
+def test_gptq_requires_targets():
+    m = Tiny()
+    mod = GPTQModifier(targets="Conv2d", scheme="W4A16")
+    mod.on_initialize(m)
+    with pytest.raises(ValueError):
+        mod.on_calibration_start(m)
+
+
+def test_greedy_bin_packing_and_partition():
+    items = ["a", "b", "c", "d", "e"]
+    w = {"a": 4096, "b": 14336, "c": 4096, "d": 4096, "e": 1024}
+    it, bins, where = bdist.greedy_bin_packing(items, 2, item_weight_fn=lambda k: w[k])
+    assert it[0] == "b" and where["b"] == 0
+    assert sum(w[k] for k in bins[0]) == 14336 and sum(w[k] for k in bins[1]) == 4096 * 3 + 1024
+    assert [len(bdist.partition_samples(10, r, 4)) for r in range(4)] == [2, 3, 2, 3]
+    assert list(bdist.partition_samples(10, 1, 4)) == [2, 3, 4]
+
+
+class _G:
+    def __init__(self, K, val):
+        self.H = torch.full((K, K), float(val))
+        self.n = 3.0
+        self.device = torch.device("cpu")
+
+    def __hash__(self):
+        return id(self)
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.distributed.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        groups = [_G(8, rank + 1), _G(16, 10 * (rank + 1))]
+        items, bins, where = bdist.greedy_bin_packing(list(groups), world, item_weight_fn=lambda g: g.H.shape[0])
+        order = {id(g): i for i, g in enumerate(groups)}
+        bdist.reduce_hessians(items, where)
+        res = {}
+        for g in groups:
+            owner = where[g]
+            if owner == rank:
+                res[order[id(g)]] = (float(g.H[0, 0]), g.n)
+            else:
+                assert g.H is None
+        lin = torch.nn.Linear(4, 4, bias=False)
+        lin.weight.data.fill_(float(rank + 5))
+        lin.weight_scale = torch.nn.Parameter(torch.full((4, 1), float(rank)), requires_grad=False)
+        bdist.broadcast_module_params([lin], {lin: 1}, ("weight", "weight_scale", "weight_g_idx"))
+        q.put((rank, res, float(lin.weight[0, 0]), float(lin.weight_scale[0, 0])))
+    finally:
+        torch.distributed.destroy_process_group()
+
+
+def test_reduce_and_broadcast_world2_gloo():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 1000
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    merged = {}
+    for rank, res, w, s in out:
+        merged.update(res)
+        assert w == 6.0 and s == 1.0  # values of rank 1 everywhere
+    assert merged[0] == (3.0, 6.0)    # 1 + 2, samples 3 + 3
+    assert merged[1] == (30.0, 6.0)   # 10 + 20
