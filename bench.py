@@ -452,8 +452,94 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_micro(args):
+    """Kernel-level figures on small cases (also the cases ncu captures are taken on):
+    Hessian SYRK TFLOP/s and quantize/pack GB/s against their rooflines.  One JSON line."""
+    import torch
+
+    from llm_compressor_b200 import ops
+    from llm_compressor_b200.quant_args import QuantizationArgs, preset_name_to_scheme
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=dev)  # > L2 (126 MB)
+    out = {"micro": args.micro, "peaks": peaks, "results": []}
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    g = torch.Generator(device=dev).manual_seed(0)
+    if args.micro in ("syrk", "all"):
+        for K, T in ((4096, 32768), (14336, 16384)) if args.micro == "all" else ((args.micro_k, args.micro_t),):
+            x = torch.randn(T, K, generator=g, device=dev).to(torch.bfloat16)
+            H = torch.zeros(K, K, device=dev)
+            ms = timed(lambda: ops.hessian_syrk(x, H, 2.0), args.steps)
+            tf = f_syrk(T, K) / (ms * 1e-3) / 1e12
+            out["results"].append({"kernel": "syrk", "K": K, "T": T, "ms": ms, "tflops": tf,
+                                   "frac_of_burst_peak": tf / 1661.0 if peaks["source"] == "measured" else None})
+            del x, H
+    if args.micro in ("pack", "all"):
+        N = K = 8192
+        w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        cases = [("rtn_int4_g128", "W4A16", 2 + 0.5 + 2 / 128), ("rtn_mxfp4", "MXFP4A16", 2 + 0.5 + 1 / 32 + 2 / 32),
+                 ("rtn_mxfp8", "MXFP8A16", 2 + 1 + 1 / 32 + 2 / 32), ("rtn_fp8_channel", "FP8_DYNAMIC", 3.0)]
+        for name, preset, bpe in cases:
+            a = preset_name_to_scheme(preset, ["Linear"]).weights
+            ms = timed(lambda: ops.rtn_quantize_pack(w, a), args.steps)
+            gbs = bpe * N * K / (ms * 1e-3) / 1e9
+            out["results"].append({"kernel": name, "N": N, "K": K, "ms": ms, "gbs": gbs, "bytes_per_elem": bpe,
+                                   "frac_of_hbm_peak": gbs / peaks["hbm"]})
+        a4 = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128)
+        mn, mx = ops.observe_minmax(w, a4)
+        scale, zp = ops.qparams(mn, mx, a4)
+        ms = timed(lambda: ops.quantize_pack(w, scale, zp, a4), args.steps)
+        bpe = 2 + 0.5 + 2 / 128
+        out["results"].append({"kernel": "pack_int4_g128_given_scale", "N": N, "K": K, "ms": ms,
+                               "gbs": bpe * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": bpe,
+                               "frac_of_hbm_peak": bpe * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
+        ms = timed(lambda: ops.observe_minmax(w, a4), args.steps)
+        out["results"].append({"kernel": "observe_minmax_g128", "N": N, "K": K, "ms": ms,
+                               "gbs": 2.0 * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": 2.0,
+                               "frac_of_hbm_peak": 2.0 * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
+        gs = torch.tensor([1000.0], device=dev)
+        ms = timed(lambda: ops.nvfp4_quantize_pack(w, gs), args.steps)
+        bpe = 2 + 0.5 + 1 / 16 + 2 / 16
+        out["results"].append({"kernel": "nvfp4_given_global_scale", "N": N, "K": K, "ms": ms,
+                               "gbs": bpe * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": bpe,
+                               "frac_of_hbm_peak": bpe * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
+    if args.micro in ("factor", "all"):
+        K = args.micro_k if args.micro == "factor" else 4096
+        xx = torch.randn(2 * K, K, generator=g, device=dev)
+        H0 = (xx.t() @ xx) / K + 0.01 * torch.eye(K, device=dev)
+        Hw = H0.clone()
+
+        def f():
+            Hw.copy_(H0)
+            ops.gptq_factor(Hw)
+        ms = timed(f, args.steps)
+        out["results"].append({"kernel": "gptq_factor", "K": K, "ms": ms,
+                               "tflops_fp32": (2.0 / 3.0) * K ** 3 / (ms * 1e-3) / 1e12})
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--micro", default=None, choices=["syrk", "pack", "factor", "all"],
+                    help="kernel-level micro benchmark instead of the layer step")
+    ap.add_argument("--micro-k", type=int, default=4096)
+    ap.add_argument("--micro-t", type=int, default=32768)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
@@ -464,7 +550,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.micro:
+        run_micro(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)
