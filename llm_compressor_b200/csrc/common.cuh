@@ -128,14 +128,39 @@ inline int make_qrange(const b200q_qargs* qa, QRange* r) {
 // both bf16), otherwise float32; intermediate roundings follow torch's bf16 element-wise ops.
 // The zero point is always added (0 for symmetric schemes), as the reference does: that turns
 // a -0.0 quotient into +0.0.
-template <bool CB>
-__device__ __forceinline__ float quant_code(float x, float s, float zp, QRange r) {
-  float v = rnd_if<CB>(__fdiv_rn(x, s));
-  v = rnd_if<CB>(v + zp);
+__device__ __forceinline__ float round_code(float v, QRange r) {
   v = fminf(fmaxf(v, r.qmin), r.qmax);
   if (r.kind == kInt) return rintf(v);
   if (r.kind == kFp8) return e4m3_round(v);
   return e2m1_round(v);
+}
+template <bool CB>
+__device__ __forceinline__ float quant_code(float x, float s, float zp, QRange r) {
+  float v = rnd_if<CB>(__fdiv_rn(x, s));
+  v = rnd_if<CB>(v + zp);
+  return round_code(v, r);
+}
+// Same result as quant_code<CB>(x, s, zp, r) given rs = 1/s to within an ulp.  The quotient is
+// formed as x*rs (a few ulp off); the IEEE division is redone only when that product lies so
+// close to a rounding boundary that those ulps could change the outcome (a few times in 1e4).
+template <bool CB>
+__device__ __forceinline__ float quant_code_fast(float x, float s, float rs, float zp, QRange r) {
+  const float qa = x * rs;
+  const float aq = fabsf(qa);
+  bool safe = (aq < 1e30f) && (aq > 1e-30f || aq == 0.0f);
+  if (CB) {
+    // bf16 rounding midpoints sit at low half-word 0x8000; keep 16 float ulps away from them
+    const uint32_t low = __float_as_uint(qa) & 0xFFFFu;
+    safe = safe && ((low - 0x7FF0u) > 0x20u);
+    if (safe) return round_code(bf16r(bf16r(qa) + zp), r);
+  } else if (safe) {
+    // the code is a monotone function of the quotient: equal codes at both ends of an
+    // interval that contains the exact quotient settle it
+    const float a = round_code(qa * (1.0f - 0x1p-20f) + zp, r);
+    const float b = round_code(qa * (1.0f + 0x1p-20f) + zp, r);
+    if (a == b) return round_code(qa + zp, r);
+  }
+  return quant_code<CB>(x, s, zp, r);
 }
 // (q - zp) * s in the scale's dtype (SB: bf16).
 template <bool SB>
@@ -161,9 +186,9 @@ struct ParamMap {
     switch (strategy) {
       case B200Q_TENSOR: return 0;
       case B200Q_CHANNEL: return row;
-      case B200Q_BLOCK: return (row / block_h) * groups_per_row + col / block_w;
+      case B200Q_BLOCK: return (int64_t)((int)row / block_h) * groups_per_row + (int)col / block_w;
       default: {
-        int64_t g = g_idx ? (int64_t)g_idx[col] : col / group_size;
+        int64_t g = g_idx ? (int64_t)g_idx[col] : (int64_t)((int)col / group_size);
         return row * groups_per_row + g;
       }
     }

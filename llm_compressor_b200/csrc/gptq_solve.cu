@@ -143,59 +143,71 @@ __global__ void reverse_out_kernel(const float* __restrict__ A, int64_t K, int64
 // ---------------------------------------------------------------------------------------
 // Diagonal block: Cholesky of the n x n (n <= 128) block at A[k0,k0] in shared memory, L
 // written back (upper part of the block zeroed), L^-1 written to Dinv (128 x 128, zero padded).
-__global__ void __launch_bounds__(256) chol_diag_kernel(float* __restrict__ A, int64_t lda, int k0, int n,
-                                                        float* __restrict__ Dinv, int* __restrict__ status) {
+// 512 threads: four threads share a row (Cholesky, left-looking dot products) or a column
+// (inverse, forward substitution) and combine partial sums by shuffle.
+constexpr int kDiagThreads = 512;
+constexpr int kDiagLD = NB + 4;  // row stride: rows 4 banks apart, no conflicts inside a quad
+__global__ void __launch_bounds__(kDiagThreads) chol_diag_kernel(float* __restrict__ A, int64_t lda, int k0, int n,
+                                                                 float* __restrict__ Dinv, int* __restrict__ status) {
   extern __shared__ float sm[];
-  float* L = sm;                   // [NB][NB+1]
-  float* X = sm + NB * (NB + 1);   // [NB][NB+1]
+  constexpr int LD = kDiagLD;
+  float* L = sm;              // [NB][LD]
+  float* X = sm + NB * LD;    // [NB][LD]
+  __shared__ float raw[NB];
   const int tid = threadIdx.x;
-  constexpr int LD = NB + 1;
+  const int r = tid >> 2, p = tid & 3;
   for (int idx = tid; idx < NB * NB; idx += blockDim.x) {
-    int r = idx / NB, c = idx - r * NB;
-    L[r * LD + c] = (r < n && c < n && c <= r) ? A[(int64_t)(k0 + r) * lda + (k0 + c)] : 0.0f;
-    X[r * LD + c] = 0.0f;
+    int rr = idx / NB, cc = idx - rr * NB;
+    L[rr * LD + cc] = (rr < n && cc < n && cc <= rr) ? A[(int64_t)(k0 + rr) * lda + (k0 + cc)] : 0.0f;
+    X[rr * LD + cc] = 0.0f;
   }
   __syncthreads();
   for (int j = 0; j < n; ++j) {
-    if (tid == 0) {
-      float d = L[j * LD + j];
-      if (!(d > 0.0f)) {  // also catches NaN
-        if (atomicCAS(status, 0, B200Q_NOT_POSITIVE_DEFINITE) == 0) status[1] = k0 + j + 1;
-        d = 1.0f;
-      }
-      L[j * LD + j] = sqrtf(d);
+    const bool act = (r >= j) && (r < n);
+    float acc = 0.0f;
+    if (act) {
+      const float* lr = L + r * LD;
+      const float* lj = L + j * LD;
+      for (int k = p; k < j; k += 4) acc = fmaf(lr[k], lj[k], acc);
     }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    if (act && p == 0) raw[r] = L[r * LD + j] - acc;
     __syncthreads();
-    const float djj = L[j * LD + j];
-    for (int r = j + 1 + tid; r < n; r += blockDim.x) L[r * LD + j] = __fdiv_rn(L[r * LD + j], djj);
-    __syncthreads();
-    // trailing update of the lower triangle: L[r][c] -= L[r][j] * L[c][j], j < c <= r
-    const int m = n - j - 1;
-    for (int idx = tid; idx < m * m; idx += blockDim.x) {
-      int rr = idx / m, cc = idx - rr * m;
-      if (cc <= rr) {
-        int r = j + 1 + rr, c = j + 1 + cc;
-        L[r * LD + c] = fmaf(-L[r * LD + j], L[c * LD + j], L[r * LD + c]);
-      }
+    float sj = raw[j];
+    const bool ok = sj > 0.0f;  // false for NaN too
+    if (!ok) {
+      if (tid == 0 && atomicCAS(status, 0, B200Q_NOT_POSITIVE_DEFINITE) == 0) status[1] = k0 + j + 1;
+      sj = 1.0f;
     }
+    const float d = sqrtf(sj);
+    if (act && p == 0) L[r * LD + j] = (r == j) ? d : __fdiv_rn(raw[r], d);
     __syncthreads();
   }
-  // inverse by forward substitution: thread c solves L x = e_c
-  if (tid < n) {
-    const int c = tid;
-    for (int r = c; r < n; ++r) {
-      float s = (r == c) ? 1.0f : 0.0f;
-      for (int k = c; k < r; ++k) s = fmaf(-L[r * LD + k], X[k * LD + c], s);
-      X[r * LD + c] = __fdiv_rn(s, L[r * LD + r]);
+  // inverse by forward substitution: the quad of column c solves L x = e_c row by row
+  {
+    const int c = r;
+    for (int row = 0; row < n; ++row) {
+      const bool act = (c < n) && (row >= c);
+      float acc = 0.0f;
+      if (act) {
+        const float* lr = L + row * LD;
+        for (int k = c + p; k < row; k += 4) acc = fmaf(lr[k], X[k * LD + c], acc);
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      if (act && p == 0) X[row * LD + c] = __fdiv_rn(((row == c) ? 1.0f : 0.0f) - acc, L[row * LD + row]);
+      __syncwarp();
     }
   }
   __syncthreads();
   for (int idx = tid; idx < NB * NB; idx += blockDim.x) {
-    int r = idx / NB, c = idx - r * NB;
-    Dinv[idx] = X[r * LD + c];
-    if (r < n && c < n) A[(int64_t)(k0 + r) * lda + (k0 + c)] = L[r * LD + c];
+    int rr = idx / NB, cc = idx - rr * NB;
+    Dinv[idx] = X[rr * LD + cc];
+    if (rr < n && cc < n) A[(int64_t)(k0 + rr) * lda + (k0 + cc)] = L[rr * LD + cc];
   }
 }
+
 
 // X[k,k] = Linv_kk
 __global__ void copy_block_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t ldd, int n) {
@@ -290,7 +302,7 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
   const int nb = (int)((K + NB - 1) / NB);
   float* A = (float*)workspace;
   float* Dinv = A + K * lda;  // nb blocks of 128 x 128
-  const size_t diag_smem = 2 * NB * (NB + 1) * sizeof(float);
+  const size_t diag_smem = 2 * NB * kDiagLD * sizeof(float);
   B200Q_TRY(cudaFuncSetAttribute(chol_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)diag_smem));
 
   reverse_in_kernel<<<grid_for((K * K + 255) / 256, 8), 256, 0, st>>>(H, K, ldh, A, lda);
@@ -301,7 +313,7 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
     const int k0 = k * NB;
     const int n = (int)min((int64_t)NB, K - k0);
     float* Dk = Dinv + (int64_t)k * NB * NB;
-    chol_diag_kernel<<<1, 256, diag_smem, st>>>(A, lda, k0, n, Dk, status);
+    chol_diag_kernel<<<1, kDiagThreads, diag_smem, st>>>(A, lda, k0, n, Dk, status);
     B200Q_LAUNCH_CHECK();
     const int rem = (int)(K - k0 - n);
     if (rem <= 0) break;

@@ -146,6 +146,10 @@ __device__ __forceinline__ void store8(void* base, int64_t off, const float (&v)
   }
 }
 
+}  // namespace b200q
+#include "stream_kernels.cuh"
+namespace b200q {
+
 static bool vec_ok(const void* p, int64_t K, int64_t ld, int elem_bytes) {
   return (K % 8 == 0) && (ld % 8 == 0) && (((uintptr_t)p) % 16 == 0) && elem_bytes > 0;
 }
@@ -322,8 +326,21 @@ static int observe_minmax_impl(const void* W, int64_t N, int64_t K, int64_t ldw,
       int g = qa->group_size;
       if (g <= 0) return B200Q_ERR_ARG;
       if (vec && pow2(g) && g >= 8 && g <= 256 && K % g == 0) {
-        int64_t blocks = (N * (K >> 3) + 255) / 256;
-        minmax_group_vec_kernel<DT><<<grid_for(blocks, 8), 256, 0, st>>>(W, N, K, ldw, g, mn, mx);
+        if constexpr (DT == B200Q_BF16) {
+          const stream::GroupSplit gsp = stream::make_group_split(g);
+          const int64_t slots = (K / g) * gsp.L;
+          int tx2 = 32;
+          while (tx2 < 256 && tx2 < slots) tx2 <<= 1;
+          const int rows2 = stream::kThreads / tx2;
+          const int grid2 = grid_for((N + rows2 - 1) / rows2, 8);
+          const int txl2 = __builtin_ctz(tx2), ll2 = __builtin_ctz(gsp.L);
+          if (gsp.R == 4) stream::minmax_group_bf16_kernel<4><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, mn, mx);
+          else if (gsp.R == 2) stream::minmax_group_bf16_kernel<2><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, mn, mx);
+          else stream::minmax_group_bf16_kernel<1><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, mn, mx);
+        } else {
+          stream::RowTiling t = stream::make_tiling(N, K, 8);
+          stream::minmax_group_kernel<DT><<<t.grid, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, __builtin_ctz(t.tx), mn, mx);
+        }
       } else {
         int64_t total = N * ((K + g - 1) / g);
         minmax_generic_kernel<DT><<<grid_for((total + 127) / 128, 8), 128, 0, st>>>(
@@ -533,10 +550,14 @@ static int quant_launch(const void* W, int64_t N, int64_t K, int64_t ldw, const 
                         const QRange& qr, void* out, int64_t ldo, cudaStream_t st) {
   bool vec = vec_ok(W, K, ldw, 2) && (((uintptr_t)out) % 16 == 0) &&
              (MODE != kPackFake || ldo % 8 == 0);
-  if (vec) {
-    int64_t blocks = (N * (K >> 3) + 255) / 256;
-    quant_vec_kernel<XDT, SDT, GLOBAL, MODE><<<grid_for(blocks, 8), 256, 0, st>>>(
-        W, N, K, ldw, scale, zp, zp_kind, pm, gscale, qr, out, ldo);
+  if (vec && N < (1LL << 31) && K < (1LL << 31)) {
+    const bool uniform = (pm.strategy == B200Q_TENSOR) || (pm.strategy == B200Q_CHANNEL) ||
+                         ((pm.strategy == B200Q_GROUP || pm.strategy == B200Q_TENSOR_GROUP) &&
+                          pm.g_idx == nullptr && (pm.group_size & 7) == 0) ||
+                         (pm.strategy == B200Q_BLOCK && (pm.block_w & 7) == 0);
+    stream::RowTiling t = stream::make_tiling(N, K, 6);
+    stream::quant_rows_kernel<XDT, SDT, GLOBAL, MODE><<<t.grid, stream::kThreads, 0, st>>>(
+        W, (int)N, (int)K, ldw, __builtin_ctz(t.tx), scale, zp, zp_kind, pm, uniform, gscale, qr, out, ldo);
   } else {
     int64_t blocks = (N * K + 255) / 256;
     quant_scalar_kernel<XDT, SDT, GLOBAL, MODE><<<grid_for(blocks, 8), 256, 0, st>>>(
@@ -853,18 +874,44 @@ static int rtn_impl(const void* W, int64_t N, int64_t K, int64_t ldw, const b200
   if (grp) {
     int g = qa->group_size;
     if (!(pow2(g) && g >= 8 && g <= 256 && K % g == 0)) return B200Q_ERR_UNSUPPORTED;
-    int grid = grid_for((N * (K >> 3) + 255) / 256, 8);
+    stream::RowTiling t = stream::make_tiling(N, K, 6);
+    const int txl = __builtin_ctz(t.tx);
+    // bf16 weights: R chunks per lane, L lanes per group
+    const stream::GroupSplit gsp = stream::make_group_split(g);
+    const int64_t slots = (K / g) * gsp.L;
+    int tx2 = 32;
+    while (tx2 < 256 && tx2 < slots) tx2 <<= 1;
+    const int rows2 = stream::kThreads / tx2;
+    const int grid2 = grid_for((N + rows2 - 1) / rows2, 6);
+    const int txl2 = __builtin_ctz(tx2), ll2 = __builtin_ctz(gsp.L);
+#define B200Q_RB3(MODE, GL, RR) stream::rtn_group_bf16_kernel<stream::MODE, GL, RR><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, qc, qr, gscale, scale_out, zp_out, scale_store, out)
+#define B200Q_RB2(MODE, GL)                         \
+  do {                                              \
+    if (gsp.R == 4) B200Q_RB3(MODE, GL, 4);         \
+    else if (gsp.R == 2) B200Q_RB3(MODE, GL, 2);    \
+    else B200Q_RB3(MODE, GL, 1);                    \
+  } while (0)
+#define B200Q_RB(MODE)                              \
+  do {                                              \
+    if (gscale) B200Q_RB2(MODE, true);              \
+    else B200Q_RB2(MODE, false);                    \
+  } while (0)
 #define B200Q_R(MODE)                                                                              \
   do {                                                                                             \
-    if (gscale) rtn_group_kernel<DT, MODE, true><<<grid, 256, 0, st>>>(W, N, K, ldw, g, qc, qr, gscale, scale_out, zp_out, scale_store, out); \
-    else rtn_group_kernel<DT, MODE, false><<<grid, 256, 0, st>>>(W, N, K, ldw, g, qc, qr, gscale, scale_out, zp_out, scale_store, out);      \
+    if constexpr (DT == B200Q_BF16) {                                                              \
+      B200Q_RB(MODE);                                                                               \
+    } else if (gscale) stream::rtn_group_kernel<DT, stream::MODE, true><<<t.grid, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, txl, qc, qr, gscale, scale_out, zp_out, scale_store, out); \
+    else stream::rtn_group_kernel<DT, stream::MODE, false><<<t.grid, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, txl, qc, qr, gscale, scale_out, zp_out, scale_store, out);      \
   } while (0)
-    if (qr.kind == kInt && qa->num_bits == 4) B200Q_R(kPackInt4);
-    else if (qr.kind == kInt && qa->num_bits == 8) B200Q_R(kPackInt8Word);
-    else if (qr.kind == kFp8) B200Q_R(kPackByte);
-    else if (qr.kind == kFp4) B200Q_R(kPackFp4);
+    if (qr.kind == kInt && qa->num_bits == 4) B200Q_R(kInt4);
+    else if (qr.kind == kInt && qa->num_bits == 8) B200Q_R(kInt8Word);
+    else if (qr.kind == kFp8) B200Q_R(kByte);
+    else if (qr.kind == kFp4) B200Q_R(kFp4);
     else return B200Q_ERR_UNSUPPORTED;
 #undef B200Q_R
+#undef B200Q_RB
+#undef B200Q_RB2
+#undef B200Q_RB3
   } else if (qa->strategy == B200Q_CHANNEL) {
     if (gscale) return B200Q_ERR_UNSUPPORTED;
     size_t smem = (size_t)K * (DT == B200Q_BF16 ? 2 : 4);
