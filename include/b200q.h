@@ -110,6 +110,22 @@ int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t l
                       float norm, float expand, void* min_out, void* max_out, void* scratch,
                       void* stream);
 
+/* Same search as b200q_observe_mse for callers that cannot allocate device memory (a process
+ * whose memory is already committed to a cache pool, code inside an allocator callback, a
+ * plain C host with no allocator).  It has no counterpart in the reference.  The scratch lives
+ * in a 4 KiB array inside the library image, which every GPU that loads the library holds
+ * until exit; nothing is allocated or freed by this call.
+ *   - limit: int(maxshrink * grid) <= 1023 candidates, otherwise B200Q_ERR_ARG is returned
+ *     (text in b200q_last_error) and nothing is launched;
+ *   - the first call on each device looks the array's device address up
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture;
+ *   - all calls on a device share the one array: calls that overlap on the GPU (different
+ *     streams) race on it, so issue them on one stream or order them yourself.  The previous
+ *     call's contents are cleared by the search itself. */
+int b200q_observe_mse_noalloc(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw,
+                              const b200q_qargs* qa, float maxshrink, int patience, float grid,
+                              float norm, float expand, void* min_out, void* max_out, void* stream);
+
 /* ------------------------------------------------------------- quantize / pack */
 
 /* Quantize-dequantize.  Replaces fake_quantize (CT/quantization/lifecycle/forward.py:149-181,

@@ -53,6 +53,7 @@ SIGNATURES = {
     "b200q_qparams": (_i, [_p, _p, _i, _i64, _qa, _p, _p, _p, _p]),
     "b200q_observe_mse_workspace_bytes": (C.c_size_t, [_i64, _i64, _qa, _i]),
     "b200q_observe_mse": (_i, [_p, _i, _i64, _i64, _i64, _qa, _f, _i, _f, _f, _f, _p, _p, _p, _p]),
+    "b200q_observe_mse_noalloc": (_i, [_p, _i, _i64, _i64, _i64, _qa, _f, _i, _f, _f, _f, _p, _p, _p]),
     "b200q_fake_quantize": (_i, [_p, _i, _i64, _i64, _i64, _p, _i, _p, _p, _p, _qa, _p, _i64, _p]),
     "b200q_quantize_pack": (_i, [_p, _i, _i64, _i64, _i64, _p, _i, _p, _p, _p, _qa, _i, _p, _p]),
     "b200q_pack_zero_points": (_i, [_p, _i64, _i64, _i, _p, _p]),

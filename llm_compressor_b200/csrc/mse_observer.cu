@@ -13,6 +13,8 @@
 
 #include <string.h>
 
+#include <mutex>
+
 namespace b200q {
 namespace mse {
 
@@ -271,3 +273,61 @@ int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t l
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant of b200q_observe_mse.
+//
+// Some callers cannot obtain device memory at the moment they need an MSE observation: a
+// serving process that has handed its whole memory budget to a KV-cache pool and re-calibrates
+// a layer in place, code running inside a framework callback where the caching allocator must
+// not be re-entered, or a C program that links this library without any allocator of its own.
+// For them the search's scratch (one flag per shrink candidate plus the stop step) lives in a
+// fixed array inside the library image instead of a caller-supplied buffer.
+namespace b200q {
+namespace mse {
+
+constexpr int kStaticMaxSteps = 1023;  // candidates; the array holds kStaticMaxSteps + 1 ints (4 KiB)
+static __device__ __align__(256) int g_static_ctl[kStaticMaxSteps + 1];
+
+constexpr int kMaxDevices = 64;
+static int* g_static_ctl_ptr[kMaxDevices] = {nullptr};
+static std::mutex g_static_mutex;
+
+// Device address of the array on the current device.  In host code the symbol's name is only a
+// handle, not an address, so it is resolved once per device with cudaGetSymbolAddress.
+static int static_ctl_address(int** out) {
+  int dev = -1;
+  B200Q_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return B200Q_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ctl_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    B200Q_TRY(cudaGetSymbolAddress(&p, g_static_ctl));
+    if (p == nullptr) return B200Q_ERR_CUDA;
+    g_static_ctl_ptr[dev] = static_cast<int*>(p);
+  }
+  *out = g_static_ctl_ptr[dev];
+  return B200Q_OK;
+}
+
+}  // namespace mse
+}  // namespace b200q
+
+extern "C" int b200q_observe_mse_noalloc(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw,
+                                         const b200q_qargs* qa, float maxshrink, int patience, float grid,
+                                         float norm, float expand, void* mn_out, void* mx_out, void* stream) {
+  using namespace b200q::mse;
+  const double steps = (double)maxshrink * (double)grid;
+  if (!(steps >= 0.0) || steps > (double)kStaticMaxSteps) {
+    b200q::set_last_error("b200q_observe_mse_noalloc: int(maxshrink*grid) exceeds the built-in scratch (1023 candidates)",
+                          cudaErrorInvalidValue);
+    return B200Q_ERR_ARG;
+  }
+  int* ctl = nullptr;
+  int rc = static_ctl_address(&ctl);
+  if (rc != B200Q_OK) return rc;
+  // the search clears the flags it uses before its first pass, so the contents left by the
+  // previous call do not matter
+  return b200q_observe_mse(W, wdtype, N, K, ldw, qa, maxshrink, patience, grid, norm, expand, mn_out, mx_out,
+                           ctl, stream);
+}

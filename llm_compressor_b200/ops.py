@@ -73,6 +73,32 @@ def observe_mse(w, args, maxshrink=0.20, patience=5, grid=100.0, norm=2.4, expan
     return mn, mx
 
 
+def observe_mse_noalloc(w, args, mn: torch.Tensor, mx: torch.Tensor, maxshrink=0.20, patience=5,
+                        grid=100.0, norm=2.4, expand=1.0):
+    """MSE grid search into caller-provided ``mn`` / ``mx`` without allocating anything on the
+    device: for callers that must not touch an allocator (memory fully committed to a cache
+    pool, allocator callbacks).  The scratch is a fixed array inside the library, so at most
+    1023 shrink candidates are accepted, and calls that overlap on the GPU would race on it:
+    keep them on one stream.  Make the first call on a device outside stream capture."""
+    _need_cuda(w, mn, mx)
+    N, K, ld = _2d(w)
+    if args.strategy == "tensor_group" and args.scale_dtype is not None:
+        args = args.model_copy(update={"scale_dtype": None})
+    shape = tuple(args.qparam_shape(N, K))
+    for t in (mn, mx):
+        if tuple(t.shape) != shape or t.dtype != w.dtype or not t.is_contiguous():
+            raise ValueError(f"min/max outputs must be contiguous {shape} tensors of dtype {w.dtype}")
+    lib = _lib.load()
+    rc = lib.b200q_observe_mse_noalloc(ptr(w), _dt(w), N, K, ld, args.c_struct(), float(maxshrink),
+                                       int(patience), float(grid), float(norm), float(expand), ptr(mn),
+                                       ptr(mx), stream_ptr())
+    if rc == -1 and int(maxshrink * grid) > 1023:
+        raise _lib.B200QError("b200q_observe_mse_noalloc: int(maxshrink*grid) = %d candidates exceed the "
+                              "built-in scratch of 1023; use observe_mse" % int(maxshrink * grid))
+    check(rc, "b200q_observe_mse_noalloc")
+    return mn, mx
+
+
 def absmax_accumulate(mn, mx, absmax: torch.Tensor):
     _need_cuda(mn, mx, absmax)
     assert absmax.dtype == torch.float32
