@@ -219,13 +219,26 @@ int b200q_gptq_zero_dead_columns(const float* diag, int64_t diag_stride, int64_t
 
 /* In place: H (symmetric positive definite, full storage) -> upper-triangular U with
  * U^T U = H^-1, strictly-lower part zeroed.  Stands in for cholesky -> cholesky_inverse ->
- * cholesky(upper=True) (gptq_quantize.py:153-156).  *status (device int) is set to
- * B200Q_NOT_POSITIVE_DEFINITE (and info to the first bad column + 1) if a pivot is <= 0; the
+ * cholesky(upper=True) (gptq_quantize.py:153-156).  status: four device ints, zeroed by the
+ * caller; status[0] is set to B200Q_NOT_POSITIVE_DEFINITE (status[1] to the first bad column
+ * + 1) if a pivot is <= 0, status[2] to B200Q_ERR_DEVICE if a bounded wait expired; the
  * caller then takes the reference's identity fallback (:157-164).  workspace:
  * b200q_gptq_factor_workspace_bytes(K) bytes. */
 size_t b200q_gptq_factor_workspace_bytes(int64_t K);
 int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* status,
                       void* stream);
+
+/* The float32-accurate tensor-core GEMM that the factorisation and the sweep use for their
+ * rank-128 updates (tcgen05 kind::tf32, three MMAs per product on hi/lo splits of the operands):
+ *   C[M,N] = beta*C + alpha * A[M,Kd] * (trans_b ? B[N,Kd]^T : B[Kd,N]),   Kd <= 128.
+ * Stands in for the torch.matmul calls of gptq_quantize.py:236,244 and the cuSOLVER updates
+ * behind :153-155.  lower_tiles != 0 restricts the update to 128x128 tiles with column block <=
+ * row block.  status (device int, may be NULL) receives B200Q_ERR_DEVICE if a bounded wait
+ * expired.  workspace: b200q_gemm_tf32x3_workspace_bytes. */
+size_t b200q_gemm_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t Kd);
+int b200q_gemm_tf32x3(int trans_b, const float* A, int64_t lda, const float* B, int64_t ldb, float* C,
+                      int64_t ldc, int64_t M, int64_t N, int64_t Kd, float alpha, float beta,
+                      int lower_tiles, void* workspace, int* status, void* stream);
 
 /* Blockwise column sweep (gptq_quantize.py:166-245): for each block of `blocksize` columns,
  * column by column: q = fake_quantize(w); loss += (w-q)^2/d^2/2; err = (w-q)/d;

@@ -13,7 +13,7 @@
 //   4. U = J X J written over H, strictly lower part zeroed
 // A pivot <= 0 (or NaN) sets *status; the host then takes the reference's identity fallback.
 #include "common.cuh"
-#include "sgemm.cuh"
+#include "tgemm_tf32.cuh"
 
 namespace b200q {
 namespace solve {
@@ -292,7 +292,9 @@ size_t b200q_gptq_factor_workspace_bytes(int64_t K) {
   if (K <= 0) return 0;
   int64_t lda = round_up(K, 32);
   int64_t nb = (K + NB - 1) / NB;
-  return (size_t)(K * lda + nb * NB * NB) * sizeof(float);
+  // reversed matrix + inverse diagonal blocks + hi/lo copies of the two GEMM operands
+  // (split buffers are whole 128-row tiles: the GEMM's TMA boxes read full tiles)
+  return (size_t)(K * lda + nb * NB * NB + 4 * (nb * NB) * NB) * sizeof(float);
 }
 
 int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* status, void* stream) {
@@ -302,8 +304,16 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
   const int nb = (int)((K + NB - 1) / NB);
   float* A = (float*)workspace;
   float* Dinv = A + K * lda;  // nb blocks of 128 x 128
+  float* sa_hi = Dinv + (int64_t)nb * NB * NB;  // operand A parts: up to [K][128]
+  const int64_t cap = (int64_t)nb * NB * NB;    // floats per split buffer: [roundup(K,128)][128]
+  float* sa_lo = sa_hi + cap;
+  float* sb_hi = sa_lo + cap;                   // operand B parts, K-major: up to [K][128]
+  float* sb_lo = sb_hi + cap;
   const size_t diag_smem = 2 * NB * kDiagLD * sizeof(float);
   B200Q_TRY(cudaFuncSetAttribute(chol_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)diag_smem));
+  using tgemm::Split;
+  int rc;
+#define B200Q_RC(expr) do { rc = (expr); if (rc != B200Q_OK) return rc; } while (0)
 
   reverse_in_kernel<<<grid_for((K * K + 255) / 256, 8), 256, 0, st>>>(H, K, ldh, A, lda);
   B200Q_LAUNCH_CHECK();
@@ -318,11 +328,17 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
     const int rem = (int)(K - k0 - n);
     if (rem <= 0) break;
     float* P = A + (int64_t)(k0 + n) * lda + k0;  // panel below the diagonal block: rem x n
+    const int64_t ldp = tgemm::split_ld(n);
     // P <- P * L_kk^-T   (out[r][c] = sum_m P[r][m] * Linv[c][m])
-    B200Q_TRY(sgemm::launch(sgemm::kNT, P, lda, Dk, NB, P, lda, rem, n, n, 1.0f, 0.0f, sgemm::kAllTiles, st));
+    B200Q_RC(tgemm::split(P, lda, rem, n, sa_hi, sa_lo, st));
+    B200Q_RC(tgemm::split(Dk, NB, n, n, sb_hi, sb_lo, st));
+    B200Q_RC(tgemm::launch(tgemm::kNT, Split{sa_hi, sa_lo, ldp}, Split{sb_hi, sb_lo, ldp}, P, lda, rem, n, n, 1.0f,
+                           0.0f, tgemm::kAllTiles, status + 2, st));
     // trailing: A22 -= P P^T on the lower block triangle
     float* A22 = A + (int64_t)(k0 + n) * lda + (k0 + n);
-    B200Q_TRY(sgemm::launch(sgemm::kNT, P, lda, P, lda, A22, lda, rem, rem, n, -1.0f, 1.0f, sgemm::kLowerTiles, st));
+    B200Q_RC(tgemm::split(P, lda, rem, n, sa_hi, sa_lo, st));
+    B200Q_RC(tgemm::launch(tgemm::kNT, Split{sa_hi, sa_lo, ldp}, Split{sa_hi, sa_lo, ldp}, A22, lda, rem, rem, n,
+                           -1.0f, 1.0f, tgemm::kLowerTiles, status + 2, st));
   }
 
   // ---- inverse in place: X = L^-1 (lower) ----
@@ -331,24 +347,34 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
     const int n = (int)min((int64_t)NB, K - k0);
     float* Dk = Dinv + (int64_t)k * NB * NB;
     float* rowk = A + (int64_t)k0 * lda;  // X[k, 0:k0] accumulators, n x k0
+    const int64_t ldn = tgemm::split_ld(n);
     if (k0 > 0) {
       // X[k, :k0] <- Linv_kk * S[k, :k0]
-      B200Q_TRY(sgemm::launch(sgemm::kNN, Dk, NB, rowk, lda, rowk, lda, n, k0, n, 1.0f, 0.0f, sgemm::kAllTiles, st));
+      B200Q_RC(tgemm::split(Dk, NB, n, n, sa_hi, sa_lo, st));
+      B200Q_RC(tgemm::split_transposed(rowk, lda, n, k0, sb_hi, sb_lo, st));
+      B200Q_RC(tgemm::launch(tgemm::kNT, Split{sa_hi, sa_lo, ldn}, Split{sb_hi, sb_lo, ldn}, rowk, lda,
+                             n, k0, n, 1.0f, 0.0f, tgemm::kAllTiles, status + 2, st));
     }
     const int rem = (int)(K - k0 - n);
     if (rem > 0) {
       float* Lik = A + (int64_t)(k0 + n) * lda + k0;  // L[i,k] for i > k: rem x n
+      B200Q_RC(tgemm::split(Lik, lda, rem, n, sa_hi, sa_lo, st));
       if (k0 > 0) {
         // S[i, :k0] -= L[i,k] * X[k, :k0]
         float* Si = A + (int64_t)(k0 + n) * lda;
-        B200Q_TRY(sgemm::launch(sgemm::kNN, Lik, lda, rowk, lda, Si, lda, rem, k0, n, -1.0f, 1.0f, sgemm::kAllTiles, st));
+        B200Q_RC(tgemm::split_transposed(rowk, lda, n, k0, sb_hi, sb_lo, st));
+        B200Q_RC(tgemm::launch(tgemm::kNT, Split{sa_hi, sa_lo, ldn}, Split{sb_hi, sb_lo, ldn}, Si, lda,
+                               rem, k0, n, -1.0f, 1.0f, tgemm::kAllTiles, status + 2, st));
       }
-      // S[i, k] = -L[i,k] * Linv_kk   (in place on the panel)
-      B200Q_TRY(sgemm::launch(sgemm::kNN, Lik, lda, Dk, NB, Lik, lda, rem, n, n, -1.0f, 0.0f, sgemm::kAllTiles, st));
+      // S[i, k] = -L[i,k] * Linv_kk   (in place on the panel; the operand is read from its split copy)
+      B200Q_RC(tgemm::split_transposed(Dk, NB, n, n, sb_hi, sb_lo, st));
+      B200Q_RC(tgemm::launch(tgemm::kNT, Split{sa_hi, sa_lo, ldn}, Split{sb_hi, sb_lo, ldn}, Lik, lda, rem, n, n, -1.0f,
+                             0.0f, tgemm::kAllTiles, status + 2, st));
     }
     copy_block_kernel<<<16, 256, 0, st>>>(Dk, A + (int64_t)k0 * lda + k0, lda, n);
     B200Q_LAUNCH_CHECK();
   }
+#undef B200Q_RC
 
   reverse_out_kernel<<<grid_for((K * K + 255) / 256, 8), 256, 0, st>>>(A, K, lda, H, ldh);
   B200Q_LAUNCH_CHECK();
@@ -356,3 +382,31 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
 }
 
 }  // extern "C"
+
+// fp32-accurate tile GEMM of the solve, exposed for testing and reuse:
+//   C[M,N] = beta*C + alpha * A[M,Kd] * (trans_b ? B[N,Kd]^T : B[Kd,N]),  Kd <= 128.
+extern "C" size_t b200q_gemm_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t Kd) {
+  if (M <= 0 || N <= 0 || Kd <= 0) return 0;
+  const int64_t kp = tgemm::split_ld(Kd);
+  const int64_t a = (M + 127) / 128 * 128 * kp, b = (N + 127) / 128 * 128 * kp;
+  return (size_t)(2 * a + 2 * b) * sizeof(float);
+}
+extern "C" int b200q_gemm_tf32x3(int trans_b, const float* A, int64_t lda, const float* B, int64_t ldb, float* C,
+                                 int64_t ldc, int64_t M, int64_t N, int64_t Kd, float alpha, float beta,
+                                 int lower_tiles, void* workspace, int* status, void* stream) {
+  if (!A || !B || !C || !workspace || M <= 0 || N <= 0 || Kd <= 0 || Kd > 128) return B200Q_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t kp = tgemm::split_ld(Kd);
+  const int64_t asz = (M + 127) / 128 * 128 * kp, bsz = (N + 127) / 128 * 128 * kp;
+  float* a_hi = (float*)workspace;
+  float* a_lo = a_hi + asz;
+  float* b_hi = a_lo + asz;
+  float* b_lo = b_hi + bsz;
+  int rc = tgemm::split(A, lda, (int)M, (int)Kd, a_hi, a_lo, st);
+  if (rc) return rc;
+  if (trans_b) rc = tgemm::split(B, ldb, (int)N, (int)Kd, b_hi, b_lo, st);
+  else rc = tgemm::split_transposed(B, ldb, (int)Kd, (int)N, b_hi, b_lo, st);
+  if (rc) return rc;
+  return tgemm::launch(tgemm::kNT, tgemm::Split{a_hi, a_lo, kp}, tgemm::Split{b_hi, b_lo, kp}, C, ldc, (int)M, (int)N, (int)Kd, alpha, beta,
+                       lower_tiles ? tgemm::kLowerTiles : tgemm::kAllTiles, status, st);
+}

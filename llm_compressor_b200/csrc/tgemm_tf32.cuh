@@ -1,0 +1,30 @@
+// Interface of the float32-accurate tensor-core GEMM (implementation: tgemm_tf32.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace b200q {
+namespace tgemm {
+
+enum Trans { kNN = 0, kNT = 1 };
+enum TileMask { kAllTiles = 0, kLowerTiles = 1 };
+
+struct Split {       // a split operand: hi / lo arrays with a common leading dimension
+  const float* hi;
+  const float* lo;
+  int64_t ld;
+};
+
+inline int64_t split_ld(int64_t cols) { return (cols + 31) / 32 * 32; }
+
+// src [rows][cols] -> hi/lo [rows][split_ld(cols)]
+int split(const float* src, int64_t ld_src, int rows, int cols, float* hi, float* lo, cudaStream_t st);
+// src [rows][cols] -> hi/lo [cols][split_ld(rows)]
+int split_transposed(const float* src, int64_t ld_src, int rows, int cols, float* hi, float* lo, cudaStream_t st);
+// C[M,N] = beta*C + alpha * A[M,Kd] * B[N,Kd]^T with A, B given as hi/lo splits whose buffers hold
+// whole 128-row tiles (rows beyond M / N may hold anything).
+int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int Kd, float alpha, float beta,
+           int mask, int* status, cudaStream_t st);
+
+}  // namespace tgemm
+}  // namespace b200q

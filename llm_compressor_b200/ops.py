@@ -321,10 +321,13 @@ def gptq_factor(H: torch.Tensor) -> int:
     K = H.shape[0]
     ws = torch.empty(max(lib.b200q_gptq_factor_workspace_bytes(K), 4), dtype=torch.uint8,
                      device=H.device)
-    status = torch.zeros(2, dtype=torch.int32, device=H.device)
+    status = torch.zeros(4, dtype=torch.int32, device=H.device)
     check(lib.b200q_gptq_factor(ptr(H), K, H.stride(0), ptr(ws), ptr(status), stream_ptr()),
           "b200q_gptq_factor")
-    return int(status[0].item())
+    st = status.tolist()
+    if st[2] != 0:
+        raise _lib.B200QError("b200q_gptq_factor: a bounded wait inside the GEMM kernel expired")
+    return int(st[0])
 
 
 def gptq_sweep(wf, U, scale, zp, args: QuantizationArgs, blocksize=128, col_group=None,
@@ -340,10 +343,28 @@ def gptq_sweep(wf, U, scale, zp, args: QuantizationArgs, blocksize=128, col_grou
     if global_scale is not None:
         global_scale = global_scale.to(torch.float32).contiguous()
     losses = torch.empty(N, dtype=torch.float32, device=wf.device)
-    ws = torch.empty(max(lib.b200q_gptq_sweep_workspace_bytes(N, K, blocksize), 4),
+    ws = torch.empty(max(lib.b200q_gptq_sweep_workspace_bytes(N, K, blocksize), 4) + 16,
                      dtype=torch.uint8, device=wf.device)
     check(lib.b200q_gptq_sweep(ptr(wf), N, K, ld, ptr(U), 0 if U is None else U.stride(0),
                                ptr(scale), _dt(scale), ptr(zp), ptr(col_group), ptr(global_scale),
                                args.c_struct(), int(blocksize), ptr(losses), ptr(ws), stream_ptr()),
           "b200q_gptq_sweep")
     return losses
+
+
+def gemm_tf32x3(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, trans_b: bool, alpha=1.0, beta=0.0,
+                lower_tiles=False) -> torch.Tensor:
+    """c = beta*c + alpha * a @ (b.T if trans_b else b) on the tensor cores with float32 accuracy;
+    a [M,Kd], Kd <= 128."""
+    _need_cuda(a, b, c)
+    lib = _lib.load()
+    M, Kd = a.shape
+    N = b.shape[0] if trans_b else b.shape[1]
+    ws = torch.empty(lib.b200q_gemm_tf32x3_workspace_bytes(M, N, Kd) + 16, dtype=torch.uint8, device=a.device)
+    status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    check(lib.b200q_gemm_tf32x3(int(trans_b), ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(c), c.stride(0), M, N, Kd,
+                                float(alpha), float(beta), int(lower_tiles), ptr(ws), ptr(status), stream_ptr()),
+          "b200q_gemm_tf32x3")
+    if int(status.item()) != 0:
+        raise _lib.B200QError("b200q_gemm_tf32x3: a bounded wait inside the kernel expired")
+    return c

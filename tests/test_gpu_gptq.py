@@ -201,3 +201,38 @@ def test_mse_golden(golden):
         rel = ((s - s_ref).abs() / s_ref.abs().clamp_min(1e-30))
         assert float((rel > 1e-3).float().mean()) <= 0.02, (name, float(rel.max()))
     assert worst <= 0.05, worst
+
+
+# ------------------------------------------------------------------------------- tensor-core GEMM
+@pytest.mark.parametrize("trans_b", [True, False])
+@pytest.mark.parametrize("M,N,Kd", [(128, 128, 32), (256, 384, 128), (2, 128, 128), (128, 2, 128), (130, 70, 2),
+                                    (300, 260, 100), (1000, 129, 128)])
+def test_gemm_tf32x3_is_float32_accurate(trans_b, M, N, Kd):
+    g = torch.Generator().manual_seed(M + N + Kd)
+    a = torch.randn(M, Kd, generator=g)
+    b = torch.randn(N, Kd, generator=g) if trans_b else torch.randn(Kd, N, generator=g)
+    c0 = torch.randn(M, N, generator=g)
+    ref = 0.5 * c0.double() - a.double() @ (b.double().t() if trans_b else b.double())
+    c = c0.clone().to(DEV)
+    ops.gemm_tf32x3(a.to(DEV), b.to(DEV), c, trans_b, alpha=-1.0, beta=0.5)
+    err = float((c.cpu().double() - ref).norm() / ref.norm())
+    ref32 = 0.5 * c0 - a @ (b.t() if trans_b else b)
+    err32 = float((ref32.double() - ref).norm() / ref.norm())
+    assert err < max(3e-6, 20 * err32), (err, err32)
+
+
+def test_gemm_tf32x3_lower_tiles_only():
+    g = torch.Generator().manual_seed(0)
+    p = torch.randn(384, 128, generator=g)
+    c = torch.zeros(384, 384, device=DEV)
+    ops.gemm_tf32x3(p.to(DEV), p.to(DEV), c, True, alpha=1.0, beta=1.0, lower_tiles=True)
+    ref = (p.double() @ p.double().t())
+    out = c.cpu().double()
+    for bi in range(3):
+        for bj in range(3):
+            blk = out[bi * 128:(bi + 1) * 128, bj * 128:(bj + 1) * 128]
+            if bj <= bi:
+                r = ref[bi * 128:(bi + 1) * 128, bj * 128:(bj + 1) * 128]
+                assert float((blk - r).norm() / r.norm()) < 3e-6
+            else:
+                assert float(blk.abs().max()) == 0.0
