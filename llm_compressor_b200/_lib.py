@@ -10,7 +10,7 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libb200q.so")
+LIB_PATH = os.environ.get("B200Q_LIBRARY") or os.path.join(_PKG, "libb200q.so")
 
 # enums of include/b200q.h
 BF16, F32, F16 = 0, 1, 2

@@ -168,7 +168,17 @@ __global__ void __launch_bounds__(kDiagThreads) chol_diag_kernel(float* __restri
     if (act) {
       const float* lr = L + r * LD;
       const float* lj = L + j * LD;
-      for (int k = p; k < j; k += 4) acc = fmaf(lr[k], lj[k], acc);
+      // four independent partial sums keep the shared-memory loads in flight
+      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+      int k = p;
+      for (; k + 12 < j; k += 16) {
+        a0 = fmaf(lr[k], lj[k], a0);
+        a1 = fmaf(lr[k + 4], lj[k + 4], a1);
+        a2 = fmaf(lr[k + 8], lj[k + 8], a2);
+        a3 = fmaf(lr[k + 12], lj[k + 12], a3);
+      }
+      for (; k < j; k += 4) a0 = fmaf(lr[k], lj[k], a0);
+      acc = (a0 + a1) + (a2 + a3);
     }
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
@@ -192,7 +202,16 @@ __global__ void __launch_bounds__(kDiagThreads) chol_diag_kernel(float* __restri
       float acc = 0.0f;
       if (act) {
         const float* lr = L + row * LD;
-        for (int k = c + p; k < row; k += 4) acc = fmaf(lr[k], X[k * LD + c], acc);
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        int k = c + p;
+        for (; k + 12 < row; k += 16) {
+          a0 = fmaf(lr[k], X[k * LD + c], a0);
+          a1 = fmaf(lr[k + 4], X[(k + 4) * LD + c], a1);
+          a2 = fmaf(lr[k + 8], X[(k + 8) * LD + c], a2);
+          a3 = fmaf(lr[k + 12], X[(k + 12) * LD + c], a3);
+        }
+        for (; k < row; k += 4) a0 = fmaf(lr[k], X[k * LD + c], a0);
+        acc = (a0 + a1) + (a2 + a3);
       }
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);

@@ -30,7 +30,8 @@ constexpr int kChunkBytes = kChunk * kBlockT * 2;            // 8 KiB
 constexpr int kABytes = (kTileM / kChunk) * kChunkBytes;     // 16 KiB
 constexpr int kBBytes = (kTileN / kChunk) * kChunkBytes;     // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;               // 48 KiB
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kEpiBytes = 4 * 32 * 33 * 4;  // per-warp staging tiles of the epilogue
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kEpiBytes;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
@@ -269,6 +270,8 @@ syrk_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    float* stage = reinterpret_cast<float*>(aligned + kStages * kStageBytes + 256) + (warp - 2) * (32 * 33);
+    const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;  // 4 rows x 8 float4 per instruction
     int local = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++local) {
@@ -282,7 +285,7 @@ syrk_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       if (!mbar_wait(accf_bar(buf), acc_phase, &s_abort, p.status, 4)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = bi * kTileM + q * 32 + lane;
+      const int row0 = bi * kTileM + q * 32;
       const int col_base = bj * kTileN;
       const int row_blk_end = bi * kTileM + kTileM;  // columns >= this belong to the upper part
 #pragma unroll 1
@@ -292,23 +295,42 @@ syrk_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTileN + c * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < p.K) {
-          float* dst = p.H + (int64_t)row * p.ldh + col0;
+        // TMEM hands out one accumulator row per lane; transposing the 32x32 chunk through shared
+        // memory makes every global access a whole 128-byte row segment (8 lanes x 16 bytes)
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            if (col0 + v * 4 < p.K) {
-              float a = __uint_as_float(r[4 * v]) * p.alpha, b = __uint_as_float(r[4 * v + 1]) * p.alpha;
-              float cc = __uint_as_float(r[4 * v + 2]) * p.alpha, d = __uint_as_float(r[4 * v + 3]) * p.alpha;
-              if (p.splits > 1) {
-                red_add_v4(dst + 4 * v, a, b, cc, d);
-              } else {
-                float4 h = *reinterpret_cast<float4*>(dst + 4 * v);
-                h.x += a; h.y += b; h.z += cc; h.w += d;
-                *reinterpret_cast<float4*>(dst + 4 * v) = h;
+        for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]) * p.alpha;
+        __syncwarp();
+        const int cc = col0 + sub_col;
+        if (cc < p.K) {  // K % 8 == 0, so a float4 is inside or outside as a whole
+          if (p.splits > 1) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int lr = i * 4 + sub_row, row = row0 + lr;
+              if (row < p.K) {
+                const float* sp = stage + lr * 33 + sub_col;
+                red_add_v4(p.H + (int64_t)row * p.ldh + cc, sp[0], sp[1], sp[2], sp[3]);
+              }
+            }
+          } else {
+            float4 h[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int row = row0 + i * 4 + sub_row;
+              h[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (row < p.K) h[i] = *reinterpret_cast<const float4*>(p.H + (int64_t)row * p.ldh + cc);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int lr = i * 4 + sub_row, row = row0 + lr;
+              if (row < p.K) {
+                const float* sp = stage + lr * 33 + sub_col;
+                h[i].x += sp[0]; h[i].y += sp[1]; h[i].z += sp[2]; h[i].w += sp[3];
+                *reinterpret_cast<float4*>(p.H + (int64_t)row * p.ldh + cc) = h[i];
               }
             }
           }
         }
+        __syncwarp();
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();

@@ -27,7 +27,8 @@ constexpr int kChunkK = 32;         // fp32 elements per 128-byte row
 constexpr int kStages = 3;
 constexpr int kOpBytes = kTile * kChunkK * 4;    // one operand part of one stage: 16 KiB
 constexpr int kStageBytes = 4 * kOpBytes;        // A_hi, A_lo, B_hi, B_lo: 64 KiB
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kEpiBytes = 4 * 32 * 33 * 4;        // per-warp staging tiles of the epilogue
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kEpiBytes;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 256;
 constexpr long long kWaitCycles = 4000000000LL;
@@ -248,6 +249,10 @@ tgemm_kernel(const __grid_constant__ CUtensorMap a_hi, const __grid_constant__ C
     int local = 0;
     bool ok = true;
     const bool vec = ((p.ldc & 3) == 0) && ((((uintptr_t)p.C) & 15) == 0);
+    // per-warp staging tile [32 rows][33]: accumulator rows come out of TMEM one row per lane;
+    // going through shared memory lets every global access cover whole 128-byte row segments
+    float* stage = reinterpret_cast<float*>(aligned + kStages * kStageBytes + 256) + (warp - 2) * (32 * 33);
+    const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;  // 4 rows x 8 float4 per instruction
     for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, ++local) {
       int tm, tn;
       tile_from_index(p, t, tm, tn);
@@ -255,7 +260,7 @@ tgemm_kernel(const __grid_constant__ CUtensorMap a_hi, const __grid_constant__ C
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       if (!mbar_wait(accf_bar(buf), acc_phase, &s_abort)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = tm * kTile + q * 32 + lane;
+      const int row0 = tm * kTile + q * 32;
 #pragma unroll 1
       for (int c = 0; c < kTile / 32; ++c) {
         const int col0 = tn * kTile + c * 32;
@@ -263,29 +268,43 @@ tgemm_kernel(const __grid_constant__ CUtensorMap a_hi, const __grid_constant__ C
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTile + c * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < p.M) {
-          float* dst = p.C + (int64_t)row * p.ldc + col0;
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            const int cc = col0 + 4 * v;
-            if (cc >= p.N) break;
-            const float a0 = __uint_as_float(r[4 * v]) * p.alpha, a1 = __uint_as_float(r[4 * v + 1]) * p.alpha;
-            const float a2 = __uint_as_float(r[4 * v + 2]) * p.alpha, a3 = __uint_as_float(r[4 * v + 3]) * p.alpha;
-            if (vec && cc + 3 < p.N) {
-              float4 h = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (p.beta != 0.0f) h = *reinterpret_cast<const float4*>(dst + 4 * v);
-              h.x = p.beta * h.x + a0; h.y = p.beta * h.y + a1; h.z = p.beta * h.z + a2; h.w = p.beta * h.w + a3;
-              *reinterpret_cast<float4*>(dst + 4 * v) = h;
-            } else {
-              const float av[4] = {a0, a1, a2, a3};
-              for (int j = 0; j < 4; ++j)
-                if (cc + j < p.N) {
-                  const float old = (p.beta != 0.0f) ? dst[4 * v + j] : 0.0f;
-                  dst[4 * v + j] = p.beta * old + av[j];
-                }
+        for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]) * p.alpha;
+        __syncwarp();
+        const int cc = col0 + sub_col;
+        if (vec && col0 + 31 < p.N) {
+          float4 h[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row = row0 + i * 4 + sub_row;
+            h[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p.beta != 0.0f && row < p.M)
+              h[i] = *reinterpret_cast<const float4*>(p.C + (int64_t)row * p.ldc + cc);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int lr = i * 4 + sub_row, row = row0 + lr;
+            if (row < p.M) {
+              const float* sp = stage + lr * 33 + sub_col;
+              float4 o;
+              o.x = p.beta * h[i].x + sp[0]; o.y = p.beta * h[i].y + sp[1];
+              o.z = p.beta * h[i].z + sp[2]; o.w = p.beta * h[i].w + sp[3];
+              *reinterpret_cast<float4*>(p.C + (int64_t)row * p.ldc + cc) = o;
             }
           }
+        } else {
+          for (int i = 0; i < 8; ++i) {
+            const int lr = i * 4 + sub_row, row = row0 + lr;
+            if (row >= p.M) continue;
+            for (int j = 0; j < 4; ++j)
+              if (cc + j < p.N) {
+                float* d = p.C + (int64_t)row * p.ldc + cc + j;
+                const float old = (p.beta != 0.0f) ? *d : 0.0f;
+                *d = p.beta * old + stage[lr * 33 + sub_col + j];
+              }
+          }
         }
+        __syncwarp();
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
