@@ -436,13 +436,16 @@ struct MapCache {
   MapKey key[kSlots];
   CUtensorMap map[kSlots];
   int used = 0, next = 0;
-  const CUtensorMap* get(const float* base, int64_t ld) {
+  // Copies the map out: a later get() may evict the slot it came from.
+  bool get(const float* base, int64_t ld, CUtensorMap* out) {
     for (int i = 0; i < used; ++i)
-      if (key[i].base == base && key[i].ld == ld) return &map[i];
+      if (key[i].base == base && key[i].ld == ld) { *out = map[i]; return true; }
     int slot = (used < kSlots) ? used++ : (next++ % kSlots);
-    if (!make_map(&map[slot], base, (int64_t)1 << 30, ld, ld, kTile)) return nullptr;
+    key[slot] = MapKey{nullptr, 0};
+    if (!make_map(&map[slot], base, (int64_t)1 << 30, ld, ld, kTile)) return false;
     key[slot] = MapKey{base, ld};
-    return &map[slot];
+    *out = map[slot];
+    return true;
   }
 };
 inline MapCache& map_cache() {
@@ -457,11 +460,9 @@ int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int
   if (Kd > 128 || (A.ld & 31) || (B.ld & 31) || A.ld < Kd || B.ld < Kd) return B200Q_ERR_ARG;
   if (trans != kNT) return B200Q_ERR_UNSUPPORTED;
   MapCache& mc = map_cache();
-  const CUtensorMap* mah = mc.get(A.hi, A.ld);
-  const CUtensorMap* mal = mc.get(A.lo, A.ld);
-  const CUtensorMap* mbh = mc.get(B.hi, B.ld);
-  const CUtensorMap* mbl = mc.get(B.lo, B.ld);
-  if (!mah || !mal || !mbh || !mbl) {
+  CUtensorMap mah, mal, mbh, mbl;
+  if (!mc.get(A.hi, A.ld, &mah) || !mc.get(A.lo, A.ld, &mal) || !mc.get(B.hi, B.ld, &mbh) ||
+      !mc.get(B.lo, B.ld, &mbl)) {
     set_last_error("cuTensorMapEncodeTiled (tgemm)", cudaErrorInvalidValue);
     return B200Q_ERR_CUDA;
   }
@@ -478,13 +479,13 @@ int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int
     attr_device = dev;
   }
   // map of C for the L2 prefetch (needs 16-byte aligned rows); any valid map when unused
-  CUtensorMap mc_c = *mah;
+  CUtensorMap mc_c = mah;
   p.prefetch_c = 0;
   if (beta != 0.0f && (ldc & 3) == 0 && (((uintptr_t)C) & 15) == 0 &&
       make_map(&mc_c, C, M, N, ldc, kTile))
     p.prefetch_c = 1;
   const int grid = (int)(p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs);
-  tgemm_kernel<<<grid, kThreads, kSmemBytes, st>>>(*mah, *mal, *mbh, *mbl, mc_c, p);
+  tgemm_kernel<<<grid, kThreads, kSmemBytes, st>>>(mah, mal, mbh, mbl, mc_c, p);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
