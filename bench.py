@@ -213,14 +213,24 @@ class LayerBench:
             self.owner[g_] = r
             loads[r] += GROUP_K[g_] ** 3
         self.syrk_events = []
+        self.phase_events = []
+        self.streams = 4
 
     def step(self, from_host=None, record=False):
         """One decoder layer.  `from_host`: HostFeeder supplying activation chunks from pinned
         host memory (end-to-end arm); otherwise activations are resident in HBM."""
         torch = self.torch
         from llm_compressor_b200 import compressors, gptq
+        from llm_compressor_b200.streams import run_concurrent
         import torch.distributed as dist
 
+        def mark():
+            if record:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                self.phase_events.append(ev)
+
+        mark()
         for g_, H in self.H.items():
             H.zero_()
         n = {g_: 0 for g_ in self.H}
@@ -240,13 +250,14 @@ class LayerBench:
                 if from_host is not None:
                     from_host.release(chunk)
                 n[g_] += seqs
+        mark()
         if self.world > 1:
             for g_ in self.H:
                 dist.reduce(self.H[g_], dst=self.owner[g_], op=dist.ReduceOp.SUM)
+        mark()
         results = {}
-        for g_, K in GROUP_K.items():
-            if self.owner[g_] != self.rank:
-                continue
+
+        def solve(g_):
             gptq.finalize_hessian(self.H[g_], self.total_seqs)
             factor = gptq.factor_hessian(self.H[g_], percdamp=0.01, actorder=None)
             self.H[g_] = factor.U if factor.U is not None else self.H[g_]
@@ -260,6 +271,11 @@ class LayerBench:
                     {"weight": out["weight"], "weight_scale": out["weight_scale"],
                      "weight_zero_point": out["weight_zero_point"]}, self.qargs)
                 results[name] = (loss, out["weight"], packed)
+
+        # the solves of different Hessians are independent chains of small launches: they run
+        # concurrently on side streams (widest Hessian first), as GPTQModifier runs them
+        mine = sorted((g_ for g_ in GROUP_K if self.owner[g_] == self.rank), key=lambda g_: -GROUP_K[g_])
+        run_concurrent([lambda g_=g_: solve(g_) for g_ in mine], self.dev, max_streams=self.streams)
         if self.world > 1:
             # every rank needs the fake-quantised weights to propagate activations
             # (src/llmcompressor/utils/dist.py:55-88)
@@ -269,6 +285,7 @@ class LayerBench:
                 else:
                     buf = torch.empty_like(lin.weight.data)
                 dist.broadcast(buf, src=self.owner[grp])
+        mark()
         return results
 
 
@@ -346,6 +363,7 @@ def run_b200(args):
     peaks = load_peaks()
     seqs = args.seqs
     bench = LayerBench(rank, world, args.tokens_per_call, seqs, dev)
+    bench.streams = args.solve_streams
 
     def barrier():
         if world > 1:
@@ -361,6 +379,7 @@ def run_b200(args):
     launches0 = lib.b200q_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     bench.syrk_events = []
+    bench.phase_events = []
     barrier()
     e0.record()
     for _ in range(args.steps):
@@ -387,6 +406,15 @@ def run_b200(args):
                 "peak_source": peaks["source"] + " bf16_tflops_sustained",
                 "share_of_step": syrk_ms / ms if ms else None,
                 "launches": len(bench.syrk_events)}
+
+    # device time of the step's phases (mean per step): Hessian accumulation, the reduce to the
+    # owners, and the solve (factorise, sweep, pack, broadcast)
+    pe = bench.phase_events
+    phases = {"hessian": 0.0, "reduce": 0.0, "solve": 0.0}
+    for i in range(0, len(pe) - 3, 4):
+        phases["hessian"] += pe[i].elapsed_time(pe[i + 1]) / args.steps
+        phases["reduce"] += pe[i + 1].elapsed_time(pe[i + 2]) / args.steps
+        phases["solve"] += pe[i + 2].elapsed_time(pe[i + 3]) / args.steps
 
     # end to end through the public API with host buffers
     e2e = None
@@ -442,7 +470,7 @@ def run_b200(args):
                        "layers": LAYERS, "tokens_per_syrk_call": bench.tokens_per_call,
                        "l2": "inputs larger than L2 (tens of GB streamed per step)",
                        "calibration_scale": scale},
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "phases_ms": phases, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks,
             "published_reference": {"value": 745.03, "unit": "s", "note": "whole oneshot incl. model forwards, "
                                     "GPU not stated (docs/guides/big_models_and_distributed/distributed_oneshot.md:107-111)"},
@@ -560,6 +588,8 @@ def main():
     ap.add_argument("--tokens-per-call", type=int, default=32768)
     ap.add_argument("--seqs", type=int, default=SEQS, help="calibration sequences (512 = the named config)")
     ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--solve-streams", type=int, default=4,
+                    help="CUDA streams the factorisations / sweeps of one layer are spread over")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -141,89 +141,128 @@ __global__ void reverse_out_kernel(const float* __restrict__ A, int64_t K, int64
 }
 
 // ---------------------------------------------------------------------------------------
-// Diagonal block: Cholesky of the n x n (n <= 128) block at A[k0,k0] in shared memory, L
-// written back (upper part of the block zeroed), L^-1 written to Dinv (128 x 128, zero padded).
-// 512 threads: four threads share a row (Cholesky, left-looking dot products) or a column
-// (inverse, forward substitution) and combine partial sums by shuffle.
-constexpr int kDiagThreads = 512;
-constexpr int kDiagLD = NB + 4;  // row stride: rows 4 banks apart, no conflicts inside a quad
-__global__ void __launch_bounds__(kDiagThreads) chol_diag_kernel(float* __restrict__ A, int64_t lda, int k0, int n,
-                                                                 float* __restrict__ Dinv, int* __restrict__ status) {
-  extern __shared__ float sm[];
-  constexpr int LD = kDiagLD;
-  float* L = sm;              // [NB][LD]
-  float* X = sm + NB * LD;    // [NB][LD]
-  __shared__ float raw[NB];
-  const int tid = threadIdx.x;
-  const int r = tid >> 2, p = tid & 3;
-  for (int idx = tid; idx < NB * NB; idx += blockDim.x) {
-    int rr = idx / NB, cc = idx - rr * NB;
-    L[rr * LD + cc] = (rr < n && cc < n && cc <= rr) ? A[(int64_t)(k0 + rr) * lda + (k0 + cc)] : 0.0f;
-    X[rr * LD + cc] = 0.0f;
-  }
-  __syncthreads();
-  for (int j = 0; j < n; ++j) {
-    const bool act = (r >= j) && (r < n);
-    float acc = 0.0f;
-    if (act) {
-      const float* lr = L + r * LD;
-      const float* lj = L + j * LD;
-      // four independent partial sums keep the shared-memory loads in flight
-      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-      int k = p;
-      for (; k + 12 < j; k += 16) {
-        a0 = fmaf(lr[k], lj[k], a0);
-        a1 = fmaf(lr[k + 4], lj[k + 4], a1);
-        a2 = fmaf(lr[k + 8], lj[k + 8], a2);
-        a3 = fmaf(lr[k + 12], lj[k + 12], a3);
+// Diagonal block: Cholesky of the n x n (n <= 128) block at A[k0,k0], L written back (upper
+// part of the block zeroed), L^-1 written to Dinv (128 x 128, zero above the diagonal).
+//
+// The block lives in registers: 256 threads as a 16 x 16 grid, thread (ty,tx) holding the 64
+// elements (ty + 16a, tx + 16b).  The cyclic layout keeps every thread busy while the active
+// part shrinks.  Right-looking elimination, one barrier per column: the owners of column j
+// publish it (unscaled) to shared memory, the owners of row j publish that row of the inverse
+// under construction, and every thread then applies the rank-1 update to the rows below j that
+// it holds.  Column c of the block is dead once step c has exported it, and column c of the
+// inverse is born at step c, so the same register holds first A[i][c] and then Linv[i][c]:
+//     c > j:  A[i][c]    -= l_i * l_c            (l = column j / pivot root)
+//     c = j:  Linv[i][j]  = -l_i / root          (Linv[j][j] = 1 / root)
+//     c < j:  Linv[i][c] -= l_i * Linv[j][c]     (row j of the inverse, scaled by 1 / root)
+// The column-block index of j is a compile-time constant inside the unrolled outer loop, which
+// keeps every register index static and drops finished register rows at compile time.
+constexpr int kDiagThreads = 256;
+constexpr int kDiagLD = NB + 1;  // stride of the published columns
+constexpr int kDiagSmemFloats = NB * kDiagLD + 2 * NB + NB;
+
+template <int JA>
+__device__ __forceinline__ void chol_diag_steps(float (&v)[8][8], float* __restrict__ Lt, float* __restrict__ rowbuf,
+                                                float* __restrict__ rinvs, int n, int k0, int* __restrict__ status,
+                                                int tx, int ty) {
+  for (int jr = 0; jr < 16; ++jr) {
+    const int j = JA * 16 + jr;
+    if (j >= n) break;   // uniform
+    float* col = Lt + j * kDiagLD;
+    float* row = rowbuf + (j & 1) * NB;
+    if (tx == jr) {
+#pragma unroll
+      for (int a = JA; a < 8; ++a) {
+        const int i = ty + 16 * a;
+        if (i >= j) col[i] = v[a][JA];
       }
-      for (; k < j; k += 4) a0 = fmaf(lr[k], lj[k], a0);
-      acc = (a0 + a1) + (a2 + a3);
     }
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    if (act && p == 0) raw[r] = L[r * LD + j] - acc;
-    __syncthreads();
-    float sj = raw[j];
-    const bool ok = sj > 0.0f;  // false for NaN too
-    if (!ok) {
-      if (tid == 0 && atomicCAS(status, 0, B200Q_NOT_POSITIVE_DEFINITE) == 0) status[1] = k0 + j + 1;
-      sj = 1.0f;
+    if (ty == jr) {
+#pragma unroll
+      for (int b = 0; b <= JA; ++b) {
+        const int c = tx + 16 * b;
+        if (c < j) row[c] = v[JA][b];
+      }
     }
-    const float d = sqrtf(sj);
-    if (act && p == 0) L[r * LD + j] = (r == j) ? d : __fdiv_rn(raw[r], d);
     __syncthreads();
-  }
-  // inverse by forward substitution: the quad of column c solves L x = e_c row by row
-  {
-    const int c = r;
-    for (int row = 0; row < n; ++row) {
-      const bool act = (c < n) && (row >= c);
-      float acc = 0.0f;
-      if (act) {
-        const float* lr = L + row * LD;
-        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-        int k = c + p;
-        for (; k + 12 < row; k += 16) {
-          a0 = fmaf(lr[k], X[k * LD + c], a0);
-          a1 = fmaf(lr[k + 4], X[(k + 4) * LD + c], a1);
-          a2 = fmaf(lr[k + 8], X[(k + 8) * LD + c], a2);
-          a3 = fmaf(lr[k + 12], X[(k + 12) * LD + c], a3);
+    float piv = col[j];
+    if (!(piv > 0.0f)) {  // also true for NaN
+      if (threadIdx.x == 0 && atomicCAS(status, 0, B200Q_NOT_POSITIVE_DEFINITE) == 0) status[1] = k0 + j + 1;
+      piv = 1.0f;
+    }
+    const float rinv = __fdiv_rn(1.0f, sqrtf(piv));
+    if (threadIdx.x == 0) rinvs[j] = rinv;
+    // multipliers of the columns this thread holds
+    float m[8];
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const int c = tx + 16 * b;
+      float x;
+      if (b > JA) x = col[c];
+      else if (b < JA) x = row[c];
+      else x = (tx > jr) ? col[c] : ((tx < jr) ? row[c] : 0.0f);
+      m[b] = x * rinv;
+    }
+#pragma unroll
+    for (int a = JA; a < 8; ++a) {
+      const int i = ty + 16 * a;
+      if (a == JA && ty <= jr) {
+        if (ty == jr) {
+          // row j of the inverse takes its final value
+#pragma unroll
+          for (int b = 0; b <= JA; ++b) {
+            const int c = tx + 16 * b;
+            if (c < j) v[a][b] = m[b];
+            else if (c == j) v[a][b] = rinv;
+          }
         }
-        for (; k < row; k += 4) a0 = fmaf(lr[k], X[k * LD + c], a0);
-        acc = (a0 + a1) + (a2 + a3);
+        continue;
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      if (act && p == 0) X[row * LD + c] = __fdiv_rn(((row == c) ? 1.0f : 0.0f) - acc, L[row * LD + row]);
-      __syncwarp();
+      const float li = col[i] * rinv;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) v[a][b] = fmaf(-li, m[b], v[a][b]);
+      if (tx == jr) v[a][JA] = -li * rinv;
     }
   }
+}
+
+__global__ void __launch_bounds__(kDiagThreads, 1) chol_diag_kernel(float* __restrict__ A, int64_t lda, int k0, int n,
+                                                                    float* __restrict__ Dinv, int* __restrict__ status) {
+  extern __shared__ float sm[];
+  float* Lt = sm;                      // [NB][kDiagLD]: Lt[j][i] = column j as published at step j
+  float* rowbuf = Lt + NB * kDiagLD;   // [2][NB]
+  float* rinvs = rowbuf + 2 * NB;      // [NB] 1 / L[j][j]
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  float v[8][8];
+#pragma unroll
+  for (int a = 0; a < 8; ++a)
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const int i = ty + 16 * a, c = tx + 16 * b;
+      float x = (i == c) ? 1.0f : 0.0f;   // identity padding beyond n
+      if (i < n && c < n) x = (c <= i) ? A[(int64_t)(k0 + i) * lda + (k0 + c)] : 0.0f;
+      v[a][b] = x;
+    }
+  chol_diag_steps<0>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+  chol_diag_steps<1>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+  chol_diag_steps<2>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+  chol_diag_steps<3>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+  chol_diag_steps<4>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+  chol_diag_steps<5>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+  chol_diag_steps<6>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+  chol_diag_steps<7>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
   __syncthreads();
-  for (int idx = tid; idx < NB * NB; idx += blockDim.x) {
-    int rr = idx / NB, cc = idx - rr * NB;
-    Dinv[idx] = X[rr * LD + cc];
-    if (rr < n && cc < n) A[(int64_t)(k0 + rr) * lda + (k0 + cc)] = L[rr * LD + cc];
+  // inverse: registers -> Dinv
+#pragma unroll
+  for (int a = 0; a < 8; ++a)
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const int i = ty + 16 * a, c = tx + 16 * b;
+      Dinv[i * NB + c] = (c <= i && i < n) ? v[a][b] : 0.0f;
+    }
+  // L: published columns, scaled -> A (coalesced along the row)
+  for (int idx = tid; idx < n * NB; idx += kDiagThreads) {
+    const int i = idx / NB, c = idx - i * NB;
+    if (c < n) A[(int64_t)(k0 + i) * lda + (k0 + c)] = (c <= i) ? Lt[c * kDiagLD + i] * rinvs[c] : 0.0f;
   }
 }
 
@@ -328,7 +367,7 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
   float* sa_lo = sa_hi + cap;
   float* sb_hi = sa_lo + cap;                   // operand B parts, K-major: up to [K][128]
   float* sb_lo = sb_hi + cap;
-  const size_t diag_smem = 2 * NB * kDiagLD * sizeof(float);
+  const size_t diag_smem = kDiagSmemFloats * sizeof(float);
   B200Q_TRY(cudaFuncSetAttribute(chol_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)diag_smem));
   using tgemm::Split;
   int rc;

@@ -21,6 +21,7 @@ import torch
 from . import dist as bdist
 from . import gptq
 from .observers import Observer, fuse_weight_observers
+from .streams import run_concurrent
 from .quant_args import (PRESET_SCHEMES, QuantizationArgs, QuantizationScheme,
                          preset_name_to_scheme)
 
@@ -287,14 +288,16 @@ class GPTQModifier(QuantizationMixin):
     epoch the modules of that epoch are observed and quantised column block by column block.
     Modules that receive the very same input tensor (q/k/v, gate/up, experts under all-expert
     calibration) share one Hessian accumulation and one factorisation; set
-    ``share_hessians=False`` to keep one per module like the reference.
+    ``share_hessians=False`` to keep one per module like the reference.  The solves of different
+    Hessians run concurrently on up to ``parallel_streams`` CUDA streams (1: one after another
+    on the current stream, like the reference).
     """
 
     requires_calibration_data = True
 
     def __init__(self, block_size: int = 128, dampening_frac: Optional[float] = 0.01,
                  actorder: Any = _UNSET, offload_hessians: bool = False, share_hessians: bool = True,
-                 **quant_kwargs):
+                 parallel_streams: int = 4, **quant_kwargs):
         kw = dict(quant_kwargs)
         kw.setdefault("targets", "Linear")
         super().__init__(**kw)
@@ -303,6 +306,7 @@ class GPTQModifier(QuantizationMixin):
         self.actorder = actorder
         self.offload_hessians = offload_hessians
         self.share_hessians = share_hessians
+        self.parallel_streams = parallel_streams
         self._groups: dict = {}        # module -> _HessianGroup
         self._num_samples: dict = {}   # module -> None (membership: modules awaiting compression)
         self.losses: dict = {}
@@ -402,27 +406,35 @@ class GPTQModifier(QuantizationMixin):
             self._groups.pop(m, None)
 
     def compress_module_list(self, module_list):
-        factors = {}
-        # how many distinct act-order settings still need each shared Hessian
-        pending = {}
+        """Quantise the modules; the modules of one Hessian form a job (one factorisation per
+        act-order setting, then their sweeps) and jobs run concurrently on side streams."""
+        by_group: dict = {}
         for module in module_list:
-            g = self._groups[module]
-            pending.setdefault(id(g), set()).add(module.quantization_scheme.weights.actorder)
+            by_group.setdefault(id(self._groups[module]), []).append(module)
+        jobs = sorted(by_group.values(), key=lambda mods: -mods[0].weight.shape[1])
+        if not jobs:
+            return
+        device = jobs[0][0].weight.device
+        run_concurrent([lambda mods=mods: self._compress_group(mods) for mods in jobs], device,
+                       max_streams=self.parallel_streams)
+
+    def _compress_group(self, module_list):
+        factors = {}
+        # the distinct act-order settings that still need this Hessian
+        left = {module.quantization_scheme.weights.actorder for module in module_list}
         for module in module_list:
             group = self._groups.pop(module)
             self._num_samples.pop(module, None)
             qargs = module.quantization_scheme.weights
             name = self._module_names.get(module, type(module).__name__)
             t0 = time.perf_counter()
-            key = (id(group), qargs.actorder)
-            if key not in factors:
-                left = pending[id(group)]
+            if qargs.actorder not in factors:
                 left.discard(qargs.actorder)
                 H = group.finalized(keep=bool(left))  # factor_hessian consumes its argument
-                factors[key] = gptq.factor_hessian(H, self.dampening_frac, qargs.actorder)
+                factors[qargs.actorder] = gptq.factor_hessian(H, self.dampening_frac, qargs.actorder)
             with torch.no_grad():
                 loss, out = gptq.quantize_weight(module, qargs, None, blocksize=self.block_size,
-                                                 percdamp=self.dampening_frac, factor=factors[key])
+                                                 percdamp=self.dampening_frac, factor=factors[qargs.actorder])
             self.losses[name] = loss
             self._log_metric(name, time.perf_counter() - t0, loss)
             for attr, val in out.items():

@@ -353,14 +353,17 @@ def gptq_sweep(wf, U, scale, zp, args: QuantizationArgs, blocksize=128, col_grou
 
 
 def gemm_tf32x3(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, trans_b: bool, alpha=1.0, beta=0.0,
-                lower_tiles=False) -> torch.Tensor:
+                lower_tiles=False, workspace: "torch.Tensor | None" = None) -> torch.Tensor:
     """c = beta*c + alpha * a @ (b.T if trans_b else b) on the tensor cores with float32 accuracy;
-    a [M,Kd], Kd <= 128."""
+    a [M,Kd], Kd <= 128.  ``workspace`` (uint8, 16-byte aligned) is allocated when not given."""
     _need_cuda(a, b, c)
     lib = _lib.load()
     M, Kd = a.shape
     N = b.shape[0] if trans_b else b.shape[1]
-    ws = torch.empty(lib.b200q_gemm_tf32x3_workspace_bytes(M, N, Kd) + 16, dtype=torch.uint8, device=a.device)
+    need = lib.b200q_gemm_tf32x3_workspace_bytes(M, N, Kd)
+    ws = workspace if workspace is not None else torch.empty(need + 16, dtype=torch.uint8, device=a.device)
+    if ws.numel() < need:
+        raise ValueError(f"workspace holds {ws.numel()} bytes, {need} needed")
     status = torch.zeros(1, dtype=torch.int32, device=a.device)
     check(lib.b200q_gemm_tf32x3(int(trans_b), ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(c), c.stride(0), M, N, Kd,
                                 float(alpha), float(beta), int(lower_tiles), ptr(ws), ptr(status), stream_ptr()),

@@ -221,6 +221,21 @@ def test_gemm_tf32x3_is_float32_accurate(trans_b, M, N, Kd):
     assert err < max(3e-6, 20 * err32), (err, err32)
 
 
+def test_gemm_tf32x3_many_operand_buffers():
+    """More distinct operand buffers than the library caches tensor maps for, with one buffer
+    (the start of the workspace) recurring in every call."""
+    g = torch.Generator().manual_seed(5)
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device=DEV)
+    b = torch.randn(128, 128, generator=g)
+    for _ in range(2):
+        for k in range(1, 13):
+            a = torch.randn(128 * k, 128, generator=g)
+            c = torch.zeros(128 * k, 128, device=DEV)
+            ops.gemm_tf32x3(a.to(DEV), b.to(DEV), c, True, workspace=ws)
+            ref = a.double() @ b.double().t()
+            assert float((c.cpu().double() - ref).norm() / ref.norm()) < 3e-6, k
+
+
 def test_gemm_tf32x3_lower_tiles_only():
     g = torch.Generator().manual_seed(0)
     p = torch.randn(384, 128, generator=g)

@@ -143,6 +143,21 @@ def test_shared_hessians_equal_per_module_hessians():
         assert torch.equal(out[0][n], out[1][n]), n
 
 
+def test_concurrent_solves_equal_serial_solves():
+    base = tiny_llama(seed=4)
+    data = calib(8, 64)
+    out = []
+    for streams in (4, 1):
+        recipe = GPTQModifier(targets="Linear", scheme="W4A16", ignore=["lm_head"], actorder="static",
+                              parallel_streams=streams)
+        m = oneshot(copy.deepcopy(base), recipe=recipe, dataset=data)
+        out.append(({n: p.data.clone() for n, p in m.named_parameters() if "proj.weight" in n}, dict(recipe.losses)))
+    assert len(out[0][0]) >= 28
+    for n in out[0][0]:
+        assert torch.equal(out[0][0][n], out[1][0][n]), n
+    assert out[0][1] == out[1][1]
+
+
 @pytest.mark.parametrize("scheme", ["NVFP4A16", "MXFP4A16", "W4A16", "FP8_DYNAMIC"])
 def test_oneshot_rtn_data_free(scheme, tmp_path):
     base = tiny_llama(seed=5)
