@@ -258,19 +258,26 @@ class LayerBench:
         results = {}
 
         def solve(g_):
+            # queued without waiting for the device; status and losses are read at the end
             gptq.finalize_hessian(self.H[g_], self.total_seqs)
-            factor = gptq.factor_hessian(self.H[g_], percdamp=0.01, actorder=None)
-            self.H[g_] = factor.U if factor.U is not None else self.H[g_]
+            factor = gptq.factor_hessian(self.H[g_], percdamp=0.01, actorder=None, defer=True)
+            queued = []
             for name, lin, grp in self.mods:
                 if grp != g_:
                     continue
                 lin.weight_observer = self.Observer("weight", self.qargs)
                 lin.weight_observer(lin.weight.data)
-                loss, out = gptq.quantize_weight(lin, self.qargs, None, blocksize=128, percdamp=0.01, factor=factor)
+                loss, out = gptq.quantize_weight(lin, self.qargs, None, blocksize=128, percdamp=0.01, factor=factor,
+                                                 defer=True)
                 packed = compressors.compress_state_dict(
                     {"weight": out["weight"], "weight_scale": out["weight_scale"],
                      "weight_zero_point": out["weight_zero_point"]}, self.qargs)
-                results[name] = (loss, out["weight"], packed)
+                queued.append((name, loss, out["weight"], packed))
+            if not factor.resolve().ok:
+                raise RuntimeError("synthetic Hessian of %s is not positive definite" % g_)
+            self.H[g_] = factor.U
+            for name, loss, w, packed in queued:
+                results[name] = (float(loss), w, packed)
 
         # the solves of different Hessians are independent chains of small launches: they run
         # concurrently on side streams (widest Hessian first), as GPTQModifier runs them
@@ -411,6 +418,7 @@ def run_b200(args):
     # owners, and the solve (factorise, sweep, pack, broadcast)
     pe = bench.phase_events
     phases = {"hessian": 0.0, "reduce": 0.0, "solve": 0.0}
+    solve_steps = [round(pe[i + 2].elapsed_time(pe[i + 3]), 1) for i in range(0, len(pe) - 3, 4)]
     for i in range(0, len(pe) - 3, 4):
         phases["hessian"] += pe[i].elapsed_time(pe[i + 1]) / args.steps
         phases["reduce"] += pe[i + 1].elapsed_time(pe[i + 2]) / args.steps
@@ -470,7 +478,7 @@ def run_b200(args):
                        "layers": LAYERS, "tokens_per_syrk_call": bench.tokens_per_call,
                        "l2": "inputs larger than L2 (tens of GB streamed per step)",
                        "calibration_scale": scale},
-            "phases_ms": phases, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "phases_ms": phases, "solve_ms_per_step": solve_steps, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks,
             "published_reference": {"value": 745.03, "unit": "s", "note": "whole oneshot incl. model forwards, "
                                     "GPU not stated (docs/guides/big_models_and_distributed/distributed_oneshot.md:107-111)"},

@@ -89,16 +89,31 @@ def accumulate_hessian(inp, module, H, num_samples):
 class HessianFactor:
     """What the sweep needs from one Hessian: the act-order permutation (or None), the
     diagonal before dead-column patching, and U (upper, U^T U = (H + damp I)^-1) or None
-    when the factorisation failed and the identity stands in for it."""
+    when the factorisation failed and the identity stands in for it.
+
+    A deferred factor (``factor_hessian(..., defer=True)``) has ``ok is None`` until
+    ``resolve()`` has waited for the device status; its U must not be trusted before that."""
     K: int
     perm: Optional[torch.Tensor]
     diag: torch.Tensor
     U: Optional[torch.Tensor]
-    ok: bool
+    ok: Optional[bool]
+    status: Optional[torch.Tensor] = None
+
+    def resolve(self) -> "HessianFactor":
+        if self.ok is None:
+            st = ops.gptq_factor_status(self.status)
+            self.ok = st != _lib.NOT_POSITIVE_DEFINITE
+            if not self.ok:
+                warnings.warn(_NOT_PD_MESSAGE)
+                self.U = None
+        return self
 
 
-def factor_hessian(hessian: torch.Tensor, percdamp: float = 0.01, actorder=None) -> HessianFactor:
-    """Permute (act-order), patch dead columns, dampen and factor ``hessian`` (consumed)."""
+def factor_hessian(hessian: torch.Tensor, percdamp: float = 0.01, actorder=None,
+                   defer: bool = False) -> HessianFactor:
+    """Permute (act-order), patch dead columns, dampen and factor ``hessian`` (consumed).
+    ``defer``: do not wait for the factorisation's status (see ``HessianFactor.resolve``)."""
     H = hessian
     K = H.shape[0]
     if H.shape != (K, K) or H.dtype != torch.float32:
@@ -109,15 +124,12 @@ def factor_hessian(hessian: torch.Tensor, percdamp: float = 0.01, actorder=None)
         H = ops.permute_hessian(H, perm)
     diag = H.diagonal().clone()
     ops.gptq_prepare(H, None, percdamp)
-    status = ops.gptq_factor(H)
-    if status == _lib.NOT_POSITIVE_DEFINITE:
-        warnings.warn(_NOT_PD_MESSAGE)
-        return HessianFactor(K, perm, diag, None, False)
-    return HessianFactor(K, perm, diag, H, True)
+    factor = HessianFactor(K, perm, diag, H, None, ops.gptq_factor_async(H))
+    return factor if defer else factor.resolve()
 
 
 def quantize_weight(module, quant_args, hessian: Optional[torch.Tensor], blocksize: int = 128,
-                    percdamp: float = 0.01, factor: Optional[HessianFactor] = None):
+                    percdamp: float = 0.01, factor: Optional[HessianFactor] = None, defer: bool = False):
     """GPTQ-quantise ``module.weight`` given its Hessian (already divided by the sample
     count).  Returns ``(loss, dict)`` with the fake-quantised weight in the original dtype,
     ``weight_scale``, ``weight_zero_point`` and, where they apply, ``weight_global_scale`` and
@@ -125,7 +137,11 @@ def quantize_weight(module, quant_args, hessian: Optional[torch.Tensor], blocksi
     statistics unless act-order "group" re-observes; ``module.weight`` is not touched.
 
     ``factor`` (from ``factor_hessian`` with the same ``percdamp`` and act-order setting) may
-    be passed instead of ``hessian`` when several modules share one Hessian."""
+    be passed instead of ``hessian`` when several modules share one Hessian.
+
+    ``defer``: nothing waits for the device; the loss comes back as a 0-dim device tensor and
+    a deferred ``factor`` is used as it is.  The caller must ``factor.resolve()`` afterwards
+    and repeat the call without ``defer`` if the factorisation turned out to have failed."""
     args = QuantizationArgs.of(quant_args)
     strategy, actorder = args.strategy, args.actorder
     weight = module.weight.data if isinstance(module.weight, torch.nn.Parameter) else module.weight
@@ -171,7 +187,7 @@ def quantize_weight(module, quant_args, hessian: Optional[torch.Tensor], blocksi
                             col_group=col_group, global_scale=global_scale)
 
     Wq = ops.scatter_columns_cast(W, final_dtype, perm)
-    loss = float(losses.sum().item())
+    loss = losses.sum() if defer else float(losses.sum().item())
     out = {
         "weight": Wq,
         "weight_scale": scale.to(final_dtype),

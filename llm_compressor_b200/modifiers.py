@@ -419,22 +419,35 @@ class GPTQModifier(QuantizationMixin):
                        max_streams=self.parallel_streams)
 
     def _compress_group(self, module_list):
+        """Everything is queued on the current stream without waiting for the device; the
+        factorisation status and the losses are read once at the end.  A Hessian that turned
+        out not to be positive definite gets its modules redone with the identity, as the
+        reference falls back (gptq_quantize.py:157-164)."""
         factors = {}
         # the distinct act-order settings that still need this Hessian
         left = {module.quantization_scheme.weights.actorder for module in module_list}
+        queued = []
+        t0 = time.perf_counter()
         for module in module_list:
             group = self._groups.pop(module)
             self._num_samples.pop(module, None)
             qargs = module.quantization_scheme.weights
-            name = self._module_names.get(module, type(module).__name__)
-            t0 = time.perf_counter()
             if qargs.actorder not in factors:
                 left.discard(qargs.actorder)
                 H = group.finalized(keep=bool(left))  # factor_hessian consumes its argument
-                factors[qargs.actorder] = gptq.factor_hessian(H, self.dampening_frac, qargs.actorder)
+                factors[qargs.actorder] = gptq.factor_hessian(H, self.dampening_frac, qargs.actorder, defer=True)
+            factor = factors[qargs.actorder]
             with torch.no_grad():
                 loss, out = gptq.quantize_weight(module, qargs, None, blocksize=self.block_size,
-                                                 percdamp=self.dampening_frac, factor=factors[qargs.actorder])
+                                                 percdamp=self.dampening_frac, factor=factor, defer=True)
+            queued.append((module, qargs, factor, loss, out))
+        for module, qargs, factor, loss, out in queued:
+            if not factor.resolve().ok:
+                with torch.no_grad():
+                    loss, out = gptq.quantize_weight(module, qargs, None, blocksize=self.block_size,
+                                                     percdamp=self.dampening_frac, factor=factor)
+            loss = float(loss)
+            name = self._module_names.get(module, type(module).__name__)
             self.losses[name] = loss
             self._log_metric(name, time.perf_counter() - t0, loss)
             for attr, val in out.items():

@@ -314,8 +314,9 @@ def gptq_zero_dead_columns(diag: torch.Tensor, wf: torch.Tensor):
           "b200q_gptq_zero_dead_columns")
 
 
-def gptq_factor(H: torch.Tensor) -> int:
-    """In place H -> U (upper, U^T U = H^-1).  Returns 0, or NOT_POSITIVE_DEFINITE."""
+def gptq_factor_async(H: torch.Tensor) -> torch.Tensor:
+    """In place H -> U (upper, U^T U = H^-1) without waiting for the result.  Returns the device
+    status words for ``gptq_factor_status``; U is meaningless when the status is not 0."""
     _need_cuda(H)
     lib = _lib.load()
     K = H.shape[0]
@@ -324,10 +325,20 @@ def gptq_factor(H: torch.Tensor) -> int:
     status = torch.zeros(4, dtype=torch.int32, device=H.device)
     check(lib.b200q_gptq_factor(ptr(H), K, H.stride(0), ptr(ws), ptr(status), stream_ptr()),
           "b200q_gptq_factor")
+    return status
+
+
+def gptq_factor_status(status: torch.Tensor) -> int:
+    """Waits for a factorisation: 0, or NOT_POSITIVE_DEFINITE; raises on a device error."""
     st = status.tolist()
     if st[2] != 0:
         raise _lib.B200QError("b200q_gptq_factor: a bounded wait inside the GEMM kernel expired")
     return int(st[0])
+
+
+def gptq_factor(H: torch.Tensor) -> int:
+    """In place H -> U (upper, U^T U = H^-1).  Returns 0, or NOT_POSITIVE_DEFINITE."""
+    return gptq_factor_status(gptq_factor_async(H))
 
 
 def gptq_sweep(wf, U, scale, zp, args: QuantizationArgs, blocksize=128, col_group=None,

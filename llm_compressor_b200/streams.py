@@ -13,6 +13,7 @@ allocated in a job and consumed by the caller afterwards.
 """
 from __future__ import annotations
 
+import os as _os
 import queue
 import threading
 from typing import Callable, List, Sequence
@@ -27,7 +28,8 @@ def _side_streams(device: torch.device, n: int) -> List["torch.cuda.Stream"]:
     with _LOCK:
         have = _STREAMS.setdefault((device.type, device.index), [])
         while len(have) < n:
-            have.append(torch.cuda.Stream(device=device))
+            # the first stream runs the longest job: give it priority over the others
+            have.append(torch.cuda.Stream(device=device, priority=(-1 if not have and _os.environ.get('B200Q_STREAM_PRIORITY', '1') == '1' else 0)))
         return have[:n]
 
 
@@ -46,29 +48,31 @@ def run_concurrent(jobs: Sequence[Callable[[], object]], device, max_streams: in
     main = torch.cuda.current_stream(device)
     ready = torch.cuda.Event()
     ready.record(main)
+    # worker i starts with job i (so the first job gets the priority stream), the rest queue up
     todo: "queue.SimpleQueue[int]" = queue.SimpleQueue()
-    for i in range(len(jobs)):
+    for i in range(n, len(jobs)):
         todo.put(i)
     results: list = [None] * len(jobs)
     errors: list = []
     grad = torch.is_grad_enabled()
 
-    def worker(stream):
+    def worker(first, stream):
         torch.cuda.set_device(device)
         with torch.cuda.stream(stream), torch.set_grad_enabled(grad):
             stream.wait_event(ready)
+            i = first
             while True:
-                try:
-                    i = todo.get_nowait()
-                except queue.Empty:
-                    return
                 try:
                     results[i] = jobs[i]()
                 except BaseException as e:  # noqa: BLE001 - re-raised by the caller below
                     errors.append(e)
                     return
+                try:
+                    i = todo.get_nowait()
+                except queue.Empty:
+                    return
 
-    threads = [threading.Thread(target=worker, args=(s,), daemon=True) for s in streams]
+    threads = [threading.Thread(target=worker, args=(i, s), daemon=True) for i, s in enumerate(streams)]
     for t in threads:
         t.start()
     for t in threads:

@@ -68,3 +68,15 @@ def test_accepts_compressed_tensors_args():
     assert (a.num_bits, a.strategy, a.group_size, a.actorder) == (4, "group", 128, "weight")
     c = a.c_struct()
     assert (c.num_bits, c.strategy, c.group_size) == (4, _lib.GROUP, 128)
+
+
+def test_run_concurrent_keeps_order_and_raises():
+    from llm_compressor_b200.streams import run_concurrent
+
+    assert run_concurrent([lambda i=i: i * i for i in range(6)], "cpu", 4) == [0, 1, 4, 9, 16, 25]
+    assert run_concurrent([], "cpu") == []
+
+    def bad():
+        raise RuntimeError("boom")
+    with pytest.raises(RuntimeError, match="boom"):
+        run_concurrent([lambda: 1, bad], "cpu")
