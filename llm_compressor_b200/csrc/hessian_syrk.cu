@@ -16,6 +16,9 @@
 // flight land, frees TMEM and returns.
 #include <cuda.h>
 
+#include <cstdlib>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200q {
@@ -354,6 +357,277 @@ syrk_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
   }
 }
 
+// =========================================================================================
+// CTA-pair version: two CTAs on neighbouring SMs (a cluster of 2) share one 256 x 256 tile.
+// One tcgen05.mma.cta_group::2 (M=256, N=256, K=16) is issued by the even CTA and runs on both
+// SMs' tensor cores; each CTA stages only ITS 128 rows of A and ITS 128 columns of B, so every
+// SM moves 8 KiB of operands through shared memory per MMA instead of 12 KiB and the ring
+// holds 6 stages.  The accumulator rows of a CTA's half tile land in that CTA's own TMEM and
+// its own epilogue warps add them into H.
+//
+// Barriers: full[stage] lives in the even CTA and counts the bytes of both CTAs' loads (each
+// TMA names the even CTA's barrier); empty[stage] and acc_full[buf] exist in both CTAs and are
+// signalled together by one tcgen05.commit; acc_empty[buf] lives in the even CTA and collects
+// the eight epilogue warps of the pair.  Loads carry no multicast: every CTA fetches its own
+// boxes.
+constexpr int kPairTile = 256;
+constexpr int kPairStages = 6;
+constexpr int kPairHalfBytes = (128 / kChunk) * kChunkBytes;          // 16 KiB: 128 columns x 64 tokens
+constexpr int kPairStageBytes = 2 * kPairHalfBytes;                   // A half + B half
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256 + kEpiBytes;
+constexpr uint32_t kPairInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16)
+                                    | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion bytes go to a barrier that may live in the peer CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair once all MMAs
+// issued so far have completed
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(both)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                      uint32_t idesc, uint32_t accumulate) {
+  const uint32_t z = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
+      : "memory");
+}
+
+// Tile list of the pair kernel: 256-row block bi pairs with 256-column blocks bj <= bi.
+__device__ __forceinline__ void decode_pair_tile(int idx, int& bi, int& bj) {
+  int b = (int)((sqrtf(8.0f * (float)idx + 1.0f) - 1.0f) * 0.5f);
+  while (b * (b + 1) / 2 > idx) --b;
+  while ((b + 1) * (b + 2) / 2 <= idx) ++b;
+  bi = b;
+  bj = idx - b * (b + 1) / 2;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+syrk_pair_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* aligned = smem_raw + (base - raw);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + kPairStages * kPairStageBytes);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kPairStages + s); };
+  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * kPairStages + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * kPairStages + 2 + b); };
+  __shared__ uint32_t s_tmem_base;
+  __shared__ volatile int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();       // 0: issues the MMAs, 1: its peer
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 8); }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&s_tmem_base)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers are initialised before anything signals them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = s_tmem_base;
+
+  const int total_units = p.tiles * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = pair; u < total_units && ok; u += num_pairs) {
+        int bi, bj;
+        decode_pair_tile(u % p.tiles, bi, bj);
+        const int split = u / p.tiles;
+        const int64_t t_begin = (int64_t)split * p.tokens_per_split;
+        const int64_t t_end = min(p.T, t_begin + p.tokens_per_split);
+        const int iters = (int)((t_end - t_begin + kBlockT - 1) / kBlockT);
+        const int a_col = bi * kPairTile + (int)rank * 128, b_col = bj * kPairTile + (int)rank * 128;
+        for (int it = 0; it < iters; ++it) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, &s_abort, p.status, 1)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * kPairStageBytes);
+          const uint32_t full0 = map_to_cta(full_bar(stage), 0);
+          const uint32_t sa = base + stage * kPairStageBytes;
+          const int t0 = (int)(t_begin + (int64_t)it * kBlockT);
+#pragma unroll
+          for (int c = 0; c < 128 / kChunk; ++c) {
+            tma_load_2d_pair(sa + c * kChunkBytes, &xmap, full0, a_col + c * kChunk, t0);
+            tma_load_2d_pair(sa + kPairHalfBytes + c * kChunkBytes, &xmap, full0, b_col + c * kChunk, t0);
+          }
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (even CTA only)
+    if (rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int u = pair; u < total_units && ok; u += num_pairs, ++local) {
+        const int split = u / p.tiles;
+        const int64_t t_begin = (int64_t)split * p.tokens_per_split;
+        const int64_t t_end = min(p.T, t_begin + p.tokens_per_split);
+        const int iters = (int)((t_end - t_begin + kBlockT - 1) / kBlockT);
+        if (iters <= 0) continue;
+        const int buf = local & 1;
+        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        if (!mbar_wait(acce_bar(buf), acc_phase ^ 1u, &s_abort, p.status, 2)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kPairTile);
+        for (int it = 0; it < iters; ++it) {
+          if (!mbar_wait(full_bar(stage), phase, &s_abort, p.status, 3)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (lane == 0) {
+            const uint32_t sa = base + stage * kPairStageBytes;
+#pragma unroll
+            for (int kk = 0; kk < kBlockT / 16; ++kk) {
+              const uint64_t da = make_desc(sa + kk * 2048, kChunkBytes, 1024);
+              const uint64_t db = make_desc(sa + kPairHalfBytes + kk * 2048, kChunkBytes, 1024);
+              tcgen05_mma_bf16_pair(d_tmem, da, db, kPairInstrDesc, (it | kk) ? 1u : 0u);
+            }
+            tcgen05_commit_pair(empty_bar(stage));
+            if (it == iters - 1) tcgen05_commit_pair(accf_bar(buf));
+          }
+          __syncwarp();
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int q = warp & 3;
+    float* stage = reinterpret_cast<float*>(aligned + kPairStages * kPairStageBytes + 256) + (warp - 2) * (32 * 33);
+    const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;
+    int local = 0;
+    bool ok = true;
+    for (int u = pair; u < total_units && ok; u += num_pairs, ++local) {
+      int bi, bj;
+      decode_pair_tile(u % p.tiles, bi, bj);
+      const int split = u / p.tiles;
+      const int64_t t_begin = (int64_t)split * p.tokens_per_split;
+      const int64_t t_end = min(p.T, t_begin + p.tokens_per_split);
+      if (t_end <= t_begin) continue;
+      const int buf = local & 1;
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      if (!mbar_wait(accf_bar(buf), acc_phase, &s_abort, p.status, 4)) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row_blk = bi * kPairTile + (int)rank * 128;   // this CTA's 128 rows of the tile
+      const int row0 = row_blk + q * 32;
+      const int col_base = bj * kPairTile;
+      const int row_blk_end = row_blk + 128;  // columns >= this belong to the upper part
+#pragma unroll 1
+      for (int c = 0; c < kPairTile / 32; ++c) {
+        const int col0 = col_base + c * 32;
+        if (col0 >= row_blk_end || col0 >= p.K || row_blk >= p.K) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kPairTile + c * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]) * p.alpha;
+        __syncwarp();
+        const int cc = col0 + sub_col;
+        if (cc < p.K) {
+          if (p.splits > 1) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int lr = i * 4 + sub_row, row = row0 + lr;
+              if (row < p.K) {
+                const float* sp = stage + lr * 33 + sub_col;
+                red_add_v4(p.H + (int64_t)row * p.ldh + cc, sp[0], sp[1], sp[2], sp[3]);
+              }
+            }
+          } else {
+            float4 h[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int row = row0 + i * 4 + sub_row;
+              h[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (row < p.K) h[i] = *reinterpret_cast<const float4*>(p.H + (int64_t)row * p.ldh + cc);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int lr = i * 4 + sub_row, row = row0 + lr;
+              if (row < p.K) {
+                const float* sp = stage + lr * 33 + sub_col;
+                h[i].x += sp[0]; h[i].y += sp[1]; h[i].z += sp[2]; h[i].w += sp[3];
+                *reinterpret_cast<float4*>(p.H + (int64_t)row * p.ldh + cc) = h[i];
+              }
+            }
+          }
+        }
+        __syncwarp();
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(acce_bar(buf));
+        else mbar_arrive_cluster(map_to_cta(acce_bar(buf), 0));
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  if (s_abort) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();   // neither CTA gives up shared memory or TMEM while the other may still use it
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+}
+
 // H[i][j] = H[j][i] = scale * H[i][j] for j <= i, by 32x32 blocks through shared memory.
 __global__ void __launch_bounds__(256) finalize_kernel(float* __restrict__ H, int64_t K, int64_t ldh,
                                                        float scale) {
@@ -405,6 +679,41 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Number of CTA pairs that can be resident at once on the current device (one CTA per SM), or 0
+// when the pair kernel is switched off (B200Q_SYRK_SINGLE_CTA=1) or cannot be launched.
+static int pair_capacity() {
+  static std::mutex mu;
+  static int cached[64];
+  static bool have[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (have[dev]) return cached[dev];
+  int pairs = 0;
+  const char* off = getenv("B200Q_SYRK_SINGLE_CTA");
+  if (!(off && off[0] == '1')) {
+    if (cudaFuncSetAttribute(syrk_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) ==
+        cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * kNumSMs, 1, 1);
+      cfg.blockDim = dim3(kThreads, 1, 1);
+      cfg.dynamicSmemBytes = kPairSmemBytes;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, syrk_pair_kernel, &cfg) == cudaSuccess && n > 0)
+        pairs = n < kNumSMs / 2 ? n : kNumSMs / 2;
+    }
+    (void)cudaGetLastError();
+  }
+  cached[dev] = pairs;
+  have[dev] = true;
+  return pairs;
+}
+
 }  // namespace syrk
 }  // namespace b200q
 
@@ -434,6 +743,39 @@ int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* 
 
   Params p;
   p.H = H; p.ldh = ldh; p.K = (int)K; p.T = T; p.alpha = alpha; p.status = status;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int pairs = pair_capacity();
+  if (pairs > 0) {
+    // CTA pairs on 256 x 256 tiles
+    const int nb2 = (int)((K + kPairTile - 1) / kPairTile);
+    p.tiles = nb2 * (nb2 + 1) / 2;
+    const int64_t max_splits = (T + 511) / 512;
+    int best = 1;
+    double best_eff = 0.0;
+    for (int s = 1; s <= (int)(max_splits < 64 ? max_splits : 64); ++s) {
+      const int64_t units = (int64_t)p.tiles * s;
+      const int64_t waves = (units + pairs - 1) / pairs;
+      const double eff = (double)units / (double)(waves * pairs);
+      if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    }
+    p.splits = best;
+    const int64_t tps = (T + p.splits - 1) / p.splits;
+    p.tokens_per_split = ((tps + kBlockT - 1) / kBlockT) * kBlockT;
+    const int64_t units = (int64_t)p.tiles * p.splits;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * (units < pairs ? units : pairs)), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200Q_TRY(cudaLaunchKernelEx(&cfg, syrk_pair_kernel, map, p));
+    B200Q_LAUNCH_CHECK();
+    return B200Q_OK;
+  }
   const int nb = (int)((K + kTileM - 1) / kTileM);
   p.tiles = num_tiles(nb);
   // token splits: enough units to fill the machine several times over, each split long enough
@@ -452,7 +794,6 @@ int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* 
   int64_t tps = (T + p.splits - 1) / p.splits;
   p.tokens_per_split = ((tps + kBlockT - 1) / kBlockT) * kBlockT;
 
-  cudaStream_t st = (cudaStream_t)stream;
   B200Q_TRY(cudaFuncSetAttribute(syrk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
   int64_t units = (int64_t)p.tiles * p.splits;
   int grid = (int)(units < kNumSMs ? units : kNumSMs);
