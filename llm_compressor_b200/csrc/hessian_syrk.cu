@@ -2,6 +2,11 @@
 //
 //   H_lower += alpha * X^T X        X: [T, K] bf16 row-major, H: [K, K] fp32
 //
+// Two kernels.  syrk_pair_kernel (further down) is the one that runs: CTA pairs on 256 x 256
+// tiles with tcgen05.mma.cta_group::2.  syrk_kernel, described next, is the single-CTA version
+// it grew out of; it is used when a cluster of two cannot be launched or when
+// B200Q_SYRK_SINGLE_CTA=1 asks for it (A/B measurements).
+//
 // Persistent, warp-specialised kernel, one CTA per SM:
 //   warp 0      TMA producer: 64-token x 64-column boxes of X into a 4-stage shared-memory
 //               ring (128-byte swizzle).  The contraction runs over tokens, so both operands
@@ -162,6 +167,7 @@ struct Params {
   int K;
   int64_t T;
   int tiles;
+  int nb;                    // block rows of the tile grid
   int splits;
   int64_t tokens_per_split;  // multiple of kBlockT
   float alpha;
@@ -425,12 +431,27 @@ __device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t d_tmem, uint64_t 
 }
 
 // Tile list of the pair kernel: 256-row block bi pairs with 256-column blocks bj <= bi.
-__device__ __forceinline__ void decode_pair_tile(int idx, int& bi, int& bj) {
-  int b = (int)((sqrtf(8.0f * (float)idx + 1.0f) - 1.0f) * 0.5f);
-  while (b * (b + 1) / 2 > idx) --b;
-  while ((b + 1) * (b + 2) / 2 <= idx) ++b;
-  bi = b;
-  bj = idx - b * (b + 1) / 2;
+// Order: bands of kBand block rows, column by column inside a band.  The ~74 tiles in flight
+// then cover about kBand row panels and 74 / kBand column panels of X, which L2 holds, instead of
+// one row panel and every column panel.
+constexpr int kBand = 8;
+__device__ __forceinline__ void decode_pair_tile(int idx, int nb, int& bi, int& bj) {
+  int r0 = 0;
+  while (true) {
+    const int r1 = min(nb, r0 + kBand) - 1;            // last row of this band
+    const int rows = r1 - r0 + 1;
+    const int full = (r0 + 1) * rows;                  // columns 0..r0 hold every row of the band
+    const int tri = rows * (rows - 1) / 2;             // columns r0+1..r1 hold the rows >= column
+    if (idx < full) { bj = idx / rows; bi = r0 + idx - bj * rows; return; }
+    if (idx < full + tri) {
+      int rem = idx - full, c = r0 + 1;
+      while (rem >= r1 - c + 1) { rem -= r1 - c + 1; ++c; }
+      bj = c; bi = c + rem;
+      return;
+    }
+    idx -= full + tri;
+    r0 += kBand;
+  }
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -481,7 +502,7 @@ syrk_pair_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
       bool ok = true;
       for (int u = pair; u < total_units && ok; u += num_pairs) {
         int bi, bj;
-        decode_pair_tile(u % p.tiles, bi, bj);
+        decode_pair_tile(u % p.tiles, p.nb, bi, bj);
         const int split = u / p.tiles;
         const int64_t t_begin = (int64_t)split * p.tokens_per_split;
         const int64_t t_end = min(p.T, t_begin + p.tokens_per_split);
@@ -548,7 +569,7 @@ syrk_pair_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
     bool ok = true;
     for (int u = pair; u < total_units && ok; u += num_pairs, ++local) {
       int bi, bj;
-      decode_pair_tile(u % p.tiles, bi, bj);
+      decode_pair_tile(u % p.tiles, p.nb, bi, bj);
       const int split = u / p.tiles;
       const int64_t t_begin = (int64_t)split * p.tokens_per_split;
       const int64_t t_end = min(p.T, t_begin + p.tokens_per_split);
@@ -749,6 +770,7 @@ int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* 
     // CTA pairs on 256 x 256 tiles
     const int nb2 = (int)((K + kPairTile - 1) / kPairTile);
     p.tiles = nb2 * (nb2 + 1) / 2;
+    p.nb = nb2;
     const int64_t max_splits = (T + 511) / 512;
     int best = 1;
     double best_eff = 0.0;
@@ -778,6 +800,7 @@ int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* 
   }
   const int nb = (int)((K + kTileM - 1) / kTileM);
   p.tiles = num_tiles(nb);
+  p.nb = nb;
   // token splits: enough units to fill the machine several times over, each split long enough
   // (>= 512 tokens) to hide its epilogue behind the next unit's main loop
   const int64_t max_splits = (T + 511) / 512;
