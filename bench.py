@@ -408,11 +408,11 @@ def run_b200(args):
     syrk_ms = sum(a.elapsed_time(b) for a, b, _, _ in bench.syrk_events)
     syrk_flops = sum(f_syrk(t, K) for _, _, t, K in bench.syrk_events)
     achieved = syrk_flops / (syrk_ms * 1e-3) / 1e12 if syrk_ms > 0 else 0.0
-    roofline = {"bound": "tensor", "kernel": "syrk_kernel (tcgen05)", "achieved": achieved, "peak": peaks["tflops"],
+    roofline = {"bound": "tensor", "kernel": "syrk_pair_kernel (tcgen05 cta_group::2)", "achieved": achieved, "peak": peaks["tflops"],
                 "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                 # dram__bytes_read.sum + dram__bytes_write.sum of one ncu-captured launch (K=4096, T=32768;
-                # profiles/syrk_kernel_K4096_T32768.md); the K=14336 launches were not captured
-                "traffic": 640.0e6, "traffic_note": "bytes per K=4096 launch of 32768 tokens, from the ncu capture; "
+                # profiles/syrk_pair_kernel_K4096_T32768.md); the K=14336 launches were not captured
+                "traffic": 620.0e6, "traffic_note": "bytes per K=4096 launch of 32768 tokens, from the ncu capture; "
                                                     "algorithmic 2TK + 4K(K+1) = 336e6",
                 "peak_source": peaks["source"] + " bf16_tflops_sustained",
                 "share_of_step": syrk_ms / ms if ms else None,
