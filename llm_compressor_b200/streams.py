@@ -14,7 +14,6 @@ allocated in a job and consumed by the caller afterwards.
 from __future__ import annotations
 
 import os as _os
-import queue
 import threading
 from typing import Callable, List, Sequence
 
@@ -48,10 +47,8 @@ def run_concurrent(jobs: Sequence[Callable[[], object]], device, max_streams: in
     main = torch.cuda.current_stream(device)
     ready = torch.cuda.Event()
     ready.record(main)
-    # worker i starts with job i (so the first job gets the priority stream), the rest queue up
-    todo: "queue.SimpleQueue[int]" = queue.SimpleQueue()
-    for i in range(n, len(jobs)):
-        todo.put(i)
+    # static assignment, worker i runs jobs i, i + n, ...: the first job gets the priority stream and
+    # every job meets the same stream (and its allocator pool) on every call
     results: list = [None] * len(jobs)
     errors: list = []
     grad = torch.is_grad_enabled()
@@ -60,16 +57,11 @@ def run_concurrent(jobs: Sequence[Callable[[], object]], device, max_streams: in
         torch.cuda.set_device(device)
         with torch.cuda.stream(stream), torch.set_grad_enabled(grad):
             stream.wait_event(ready)
-            i = first
-            while True:
+            for i in range(first, len(jobs), n):
                 try:
                     results[i] = jobs[i]()
                 except BaseException as e:  # noqa: BLE001 - re-raised by the caller below
                     errors.append(e)
-                    return
-                try:
-                    i = todo.get_nowait()
-                except queue.Empty:
                     return
 
     threads = [threading.Thread(target=worker, args=(i, s), daemon=True) for i, s in enumerate(streams)]
