@@ -214,6 +214,7 @@ class LayerBench:
             loads[r] += GROUP_K[g_] ** 3
         self.syrk_events = []
         self.phase_events = []
+        self.job_events = []
         self.streams = 4
 
     def step(self, from_host=None, record=False):
@@ -257,10 +258,18 @@ class LayerBench:
         mark()
         results = {}
 
+        def stamp(g_, what):
+            if record:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                self.job_events.append((g_, what, ev))
+
         def solve(g_):
             # queued without waiting for the device; status and losses are read at the end
+            stamp(g_, "start")
             gptq.finalize_hessian(self.H[g_], self.total_seqs)
             factor = gptq.factor_hessian(self.H[g_], percdamp=0.01, actorder=None, defer=True)
+            stamp(g_, "factored")
             queued = []
             for name, lin, grp in self.mods:
                 if grp != g_:
@@ -273,6 +282,7 @@ class LayerBench:
                     {"weight": out["weight"], "weight_scale": out["weight_scale"],
                      "weight_zero_point": out["weight_zero_point"]}, self.qargs)
                 queued.append((name, loss, out["weight"], packed))
+            stamp(g_, "swept")
             if not factor.resolve().ok:
                 raise RuntimeError("synthetic Hessian of %s is not positive definite" % g_)
             self.H[g_] = factor.U
@@ -387,6 +397,7 @@ def run_b200(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     bench.syrk_events = []
     bench.phase_events = []
+    bench.job_events = []
     barrier()
     e0.record()
     for _ in range(args.steps):
@@ -427,6 +438,14 @@ def run_b200(args):
         phases["hessian"] += pe[i].elapsed_time(pe[i + 1]) / args.steps
         phases["reduce"] += pe[i + 1].elapsed_time(pe[i + 2]) / args.steps
         phases["solve"] += pe[i + 2].elapsed_time(pe[i + 3]) / args.steps
+
+    # device time line of the last timed step's solve jobs, ms after the solve phase began:
+    # {group: [start, factored, swept]}
+    jobs = {}
+    if len(pe) >= 4:
+        t0 = pe[len(pe) - 2]
+        for g_, what, ev in bench.job_events[-3 * len(GROUP_K):]:
+            jobs.setdefault(g_, []).append(round(t0.elapsed_time(ev), 1))
 
     # end to end through the public API with host buffers
     e2e = None
@@ -482,7 +501,7 @@ def run_b200(args):
                        "layers": LAYERS, "tokens_per_syrk_call": bench.tokens_per_call,
                        "l2": "inputs larger than L2 (tens of GB streamed per step)",
                        "calibration_scale": scale},
-            "phases_ms": phases, "solve_ms_per_step": solve_steps, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "phases_ms": phases, "solve_ms_per_step": solve_steps, "solve_jobs_ms": jobs, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks,
             "published_reference": {"value": 745.03, "unit": "s", "note": "whole oneshot incl. model forwards, "
                                     "GPU not stated (docs/guides/big_models_and_distributed/distributed_oneshot.md:107-111)"},

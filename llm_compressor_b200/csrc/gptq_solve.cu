@@ -7,10 +7,12 @@
 // factor of H^-1).  That is one Cholesky and one triangular inverse (2/3 K^3 flops) instead
 // of Cholesky, Cholesky-inverse and a second Cholesky (4/3 K^3).
 //   1. A = J H J                                   (reverse copy into the workspace)
-//   2. blocked right-looking Cholesky of A, 128-column blocks: diagonal block factored and
-//      inverted in shared memory by one CTA; panel and trailing updates are tile GEMMs
-//   3. blocked right-looking inverse X = L^-1 in place (rank-128 GEMM updates)
-//   4. U = J X J written over H, strictly lower part zeroed
+//   2. one pass over the 128-column blocks does the right-looking Cholesky of A and the
+//      forward substitution for X = L^-1 together (see b200q_gptq_factor): the diagonal block is
+//      factored and inverted in registers by one CTA, and all rows below it take their updates,
+//      of the substitution's accumulators left of the block and of the Schur complement right
+//      of it, from one rank-128 tensor-core GEMM launch
+//   3. U = J X J written over H, strictly lower part zeroed
 // A pivot <= 0 (or NaN) sets *status; the host then takes the reference's identity fallback.
 #include "common.cuh"
 #include "tgemm_tf32.cuh"
@@ -141,8 +143,8 @@ __global__ void reverse_out_kernel(const float* __restrict__ A, int64_t K, int64
 }
 
 // ---------------------------------------------------------------------------------------
-// Diagonal block: Cholesky of the n x n (n <= 128) block at A[k0,k0], L written back (upper
-// part of the block zeroed), L^-1 written to Dinv (128 x 128, zero above the diagonal).
+// Diagonal block: Cholesky L of the n x n (n <= 128) block at A[k0,k0]; L^-1 is written both to
+// Dinv (128 x 128, zero above the diagonal) and over the block itself (L is not needed again).
 //
 // The block lives in registers: 256 threads as a 16 x 16 grid, thread (ty,tx) holding the 64
 // elements (ty + 16a, tx + 16b).  The cyclic layout keeps every thread busy while the active
@@ -259,13 +261,13 @@ __global__ void __launch_bounds__(kDiagThreads, 1) chol_diag_kernel(float* __res
       const int i = ty + 16 * a, c = tx + 16 * b;
       Dinv[i * NB + c] = (c <= i && i < n) ? v[a][b] : 0.0f;
     }
-  // L: published columns, scaled -> A (coalesced along the row)
-  for (int idx = tid; idx < n * NB; idx += kDiagThreads) {
-    const int i = idx / NB, c = idx - i * NB;
-    if (c < n) A[(int64_t)(k0 + i) * lda + (k0 + c)] = (c <= i) ? Lt[c * kDiagLD + i] * rinvs[c] : 0.0f;
-  }
+  // the diagonal block of A takes the inverse as well: L_kk itself is not needed again
+  for (int a = 0; a < 8; ++a)
+    for (int b = 0; b < 8; ++b) {
+      const int i = ty + 16 * a, c = tx + 16 * b;
+      if (i < n && c < n) A[(int64_t)(k0 + i) * lda + (k0 + c)] = (c <= i) ? v[a][b] : 0.0f;
+    }
 }
-
 
 // X[k,k] = Linv_kk
 __global__ void copy_block_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t ldd, int n) {
@@ -352,7 +354,7 @@ size_t b200q_gptq_factor_workspace_bytes(int64_t K) {
   int64_t nb = (K + NB - 1) / NB;
   // reversed matrix + inverse diagonal blocks + hi/lo copies of the two GEMM operands
   // (split buffers are whole 128-row tiles: the GEMM's TMA boxes read full tiles)
-  return (size_t)(K * lda + nb * NB * NB + 4 * (nb * NB) * NB) * sizeof(float);
+  return (size_t)(K * lda + nb * NB * NB + 4 * (nb * NB) * NB + 4 * NB * NB) * sizeof(float);
 }
 
 int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* status, void* stream) {
@@ -361,12 +363,16 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
   const int64_t lda = round_up(K, 32);
   const int nb = (int)((K + NB - 1) / NB);
   float* A = (float*)workspace;
-  float* Dinv = A + K * lda;  // nb blocks of 128 x 128
-  float* sa_hi = Dinv + (int64_t)nb * NB * NB;  // operand A parts: up to [K][128]
-  const int64_t cap = (int64_t)nb * NB * NB;    // floats per split buffer: [roundup(K,128)][128]
+  float* Dinv = A + K * lda;                      // nb blocks of 128 x 128
+  const int64_t cap = (int64_t)nb * NB * NB;      // floats per split buffer: [roundup(K,128)][128]
+  float* sa_hi = Dinv + cap;                      // panel before its update: [rem][128]
   float* sa_lo = sa_hi + cap;
-  float* sb_hi = sa_lo + cap;                   // operand B parts, K-major: up to [K][128]
+  float* sb_hi = sa_lo + cap;                     // operand rows by absolute column: [roundup(K,128)][128]
   float* sb_lo = sb_hi + cap;
+  float* d_hi = sb_lo + cap;                      // Linv_kk and its transpose, split
+  float* d_lo = d_hi + NB * NB;
+  float* dt_hi = d_lo + NB * NB;
+  float* dt_lo = dt_hi + NB * NB;
   const size_t diag_smem = kDiagSmemFloats * sizeof(float);
   B200Q_TRY(cudaFuncSetAttribute(chol_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)diag_smem));
   using tgemm::Split;
@@ -376,61 +382,51 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
   reverse_in_kernel<<<grid_for((K * K + 255) / 256, 8), 256, 0, st>>>(H, K, ldh, A, lda);
   B200Q_LAUNCH_CHECK();
 
-  // ---- Cholesky: A = L L^T (lower) ----
+  // One pass over the block columns does the Cholesky factorisation A = L L^T and the inverse
+  // X = L^-1 together.  Before step k, in the rows below block row k: block columns < k hold the
+  // accumulators S[i,j] = -sum_{m<k} L[i,m] X[m,j] of the forward substitution, block columns
+  // >= k hold the Schur complement of the factorisation.  Step k:
+  //   diagonal block        -> L_kk, X[k,k] = L_kk^-1
+  //   X[k,:k]  = X[k,k] S[k,:k]
+  //   P        = A[k+1:,k] X[k,k]^T                       (= L[k+1:,k])
+  //   S[i,k]   = -P X[k,k]                                (in place of P)
+  //   S[i,:k] -= P X[k,:k]   and   A[i,j] -= P P^T (j > k, lower tiles)      one GEMM launch
   for (int k = 0; k < nb; ++k) {
     const int k0 = k * NB;
     const int n = (int)min((int64_t)NB, K - k0);
+    const int rem = (int)(K - k0 - n);
     float* Dk = Dinv + (int64_t)k * NB * NB;
+    float* rowk = A + (int64_t)k0 * lda;        // block row k, columns < k0: n x k0
+    const int64_t ldn = tgemm::split_ld(n);
     chol_diag_kernel<<<1, kDiagThreads, diag_smem, st>>>(A, lda, k0, n, Dk, status);
     B200Q_LAUNCH_CHECK();
-    const int rem = (int)(K - k0 - n);
-    if (rem <= 0) break;
-    float* P = A + (int64_t)(k0 + n) * lda + k0;  // panel below the diagonal block: rem x n
-    const int64_t ldp = tgemm::split_ld(n);
-    // P <- P * L_kk^-T   (out[r][c] = sum_m P[r][m] * Linv[c][m])
-    B200Q_RC(tgemm::split(P, lda, rem, n, sa_hi, sa_lo, st));
-    B200Q_RC(tgemm::split(Dk, NB, n, n, sb_hi, sb_lo, st));
-    B200Q_RC(tgemm::launch(tgemm::kNT, Split{sa_hi, sa_lo, ldp}, Split{sb_hi, sb_lo, ldp}, P, lda, rem, n, n, 1.0f,
-                           0.0f, tgemm::kAllTiles, status + 2, st));
-    // trailing: A22 -= P P^T on the lower block triangle
-    float* A22 = A + (int64_t)(k0 + n) * lda + (k0 + n);
-    B200Q_RC(tgemm::split(P, lda, rem, n, sa_hi, sa_lo, st));
-    B200Q_RC(tgemm::launch(tgemm::kNT, Split{sa_hi, sa_lo, ldp}, Split{sa_hi, sa_lo, ldp}, A22, lda, rem, rem, n,
-                           -1.0f, 1.0f, tgemm::kLowerTiles, status + 2, st));
-  }
-
-  // ---- inverse in place: X = L^-1 (lower) ----
-  for (int k = 0; k < nb; ++k) {
-    const int k0 = k * NB;
-    const int n = (int)min((int64_t)NB, K - k0);
-    float* Dk = Dinv + (int64_t)k * NB * NB;
-    float* rowk = A + (int64_t)k0 * lda;  // X[k, 0:k0] accumulators, n x k0
-    const int64_t ldn = tgemm::split_ld(n);
+    if (k0 == 0 && rem <= 0) break;
+    B200Q_RC(tgemm::split(Dk, NB, n, n, d_hi, d_lo, st));
     if (k0 > 0) {
-      // X[k, :k0] <- Linv_kk * S[k, :k0]
-      B200Q_RC(tgemm::split(Dk, NB, n, n, sa_hi, sa_lo, st));
+      // X[k,:k0] <- X[k,k] * S[k,:k0]
       B200Q_RC(tgemm::split_transposed(rowk, lda, n, k0, sb_hi, sb_lo, st));
-      B200Q_RC(tgemm::launch(tgemm::kNT, Split{sa_hi, sa_lo, ldn}, Split{sb_hi, sb_lo, ldn}, rowk, lda,
-                             n, k0, n, 1.0f, 0.0f, tgemm::kAllTiles, status + 2, st));
-    }
-    const int rem = (int)(K - k0 - n);
-    if (rem > 0) {
-      float* Lik = A + (int64_t)(k0 + n) * lda + k0;  // L[i,k] for i > k: rem x n
-      B200Q_RC(tgemm::split(Lik, lda, rem, n, sa_hi, sa_lo, st));
-      if (k0 > 0) {
-        // S[i, :k0] -= L[i,k] * X[k, :k0]
-        float* Si = A + (int64_t)(k0 + n) * lda;
-        B200Q_RC(tgemm::split_transposed(rowk, lda, n, k0, sb_hi, sb_lo, st));
-        B200Q_RC(tgemm::launch(tgemm::kNT, Split{sa_hi, sa_lo, ldn}, Split{sb_hi, sb_lo, ldn}, Si, lda,
-                               rem, k0, n, -1.0f, 1.0f, tgemm::kAllTiles, status + 2, st));
-      }
-      // S[i, k] = -L[i,k] * Linv_kk   (in place on the panel; the operand is read from its split copy)
-      B200Q_RC(tgemm::split_transposed(Dk, NB, n, n, sb_hi, sb_lo, st));
-      B200Q_RC(tgemm::launch(tgemm::kNT, Split{sa_hi, sa_lo, ldn}, Split{sb_hi, sb_lo, ldn}, Lik, lda, rem, n, n, -1.0f,
+      B200Q_RC(tgemm::launch(tgemm::kNT, Split{d_hi, d_lo, ldn}, Split{sb_hi, sb_lo, ldn}, rowk, lda, n, k0, n, 1.0f,
                              0.0f, tgemm::kAllTiles, status + 2, st));
     }
-    copy_block_kernel<<<16, 256, 0, st>>>(Dk, A + (int64_t)k0 * lda + k0, lda, n);
-    B200Q_LAUNCH_CHECK();
+    if (rem <= 0) break;
+    float* P = A + (int64_t)(k0 + n) * lda + k0;  // panel below the diagonal block: rem x n
+    // P <- P * X[k,k]^T   (out[r][c] = sum_m P[r][m] * X[c][m])
+    B200Q_RC(tgemm::split(P, lda, rem, n, sa_hi, sa_lo, st));
+    B200Q_RC(tgemm::launch(tgemm::kNT, Split{sa_hi, sa_lo, ldn}, Split{d_hi, d_lo, ldn}, P, lda, rem, n, n, 1.0f, 0.0f,
+                           tgemm::kAllTiles, status + 2, st));
+    // operand rows of the update, indexed by absolute column: X[k,:k0]^T, then (after the gap of
+    // block k) the new panel
+    float* ph = sb_hi + (int64_t)(k0 + n) * NB;
+    float* pl = sb_lo + (int64_t)(k0 + n) * NB;
+    B200Q_RC(tgemm::split(P, lda, rem, n, ph, pl, st));
+    if (k0 > 0) B200Q_RC(tgemm::split_transposed(rowk, lda, n, k0, sb_hi, sb_lo, st));
+    // S[i,k] = -P * X[k,k]  (in place on the panel; the operand is read from its split copy)
+    B200Q_RC(tgemm::split_transposed(Dk, NB, n, n, dt_hi, dt_lo, st));
+    B200Q_RC(tgemm::launch(tgemm::kNT, Split{ph, pl, ldn}, Split{dt_hi, dt_lo, ldn}, P, lda, rem, n, n, -1.0f, 0.0f,
+                           tgemm::kAllTiles, status + 2, st));
+    // rows below block k: columns < k0 take -P X[k,:k0], columns > block k take -P P^T
+    B200Q_RC(tgemm::launch(tgemm::kNT, Split{ph, pl, ldn}, Split{sb_hi, sb_lo, ldn}, A + (int64_t)(k0 + n) * lda, lda,
+                           rem, (int)K, n, -1.0f, 1.0f, tgemm::kSkipBlockTiles, status + 2, st, k));
   }
 #undef B200Q_RC
 

@@ -109,6 +109,7 @@ struct Params {
   int M, N, Kd;
   float alpha, beta;
   int tiles_m, tiles_n, mask;
+  int skip;   // kSkipBlockTiles: index of the skipped column block
   int64_t num_tiles;
   int trans;
   int prefetch_c;
@@ -122,6 +123,19 @@ __device__ __forceinline__ void tile_from_index(const Params& p, int64_t t, int&
     while ((int64_t)(i + 1) * (i + 2) / 2 <= t) ++i;
     tm = i;
     tn = (int)(t - (int64_t)i * (i + 1) / 2);
+  } else if (p.mask == kSkipBlockTiles) {
+    const int64_t left = (int64_t)p.tiles_m * p.skip;
+    if (t < left) {
+      tm = (int)(t / p.skip);
+      tn = (int)(t - (int64_t)tm * p.skip);
+    } else {
+      const int64_t u = t - left;
+      int i = (int)((sqrt(8.0 * (double)u + 1.0) - 1.0) * 0.5);
+      while ((int64_t)i * (i + 1) / 2 > u) --i;
+      while ((int64_t)(i + 1) * (i + 2) / 2 <= u) ++i;
+      tm = i;
+      tn = p.skip + 1 + (int)(u - (int64_t)i * (i + 1) / 2);
+    }
   } else {
     tm = (int)(t / p.tiles_n);
     tn = (int)(t - (int64_t)tm * p.tiles_n);
@@ -455,7 +469,7 @@ inline MapCache& map_cache() {
 
 // A: [M][Kd] split;  B: [N][Kd] split (K-major; [Kd][N] operands go through split_transposed).
 int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int Kd, float alpha, float beta,
-                  int mask, int* status, cudaStream_t st) {
+           int mask, int* status, cudaStream_t st, int mask_arg) {
   if (M <= 0 || N <= 0 || Kd <= 0) return B200Q_OK;
   if (Kd > 128 || (A.ld & 31) || (B.ld & 31) || A.ld < Kd || B.ld < Kd) return B200Q_ERR_ARG;
   if (trans != kNT) return B200Q_ERR_UNSUPPORTED;
@@ -469,7 +483,10 @@ int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int
   Params p;
   p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.Kd = Kd; p.alpha = alpha; p.beta = beta; p.mask = mask; p.trans = trans;
   p.tiles_m = (M + kTile - 1) / kTile; p.tiles_n = (N + kTile - 1) / kTile;
-  p.num_tiles = (mask == kLowerTiles) ? (int64_t)p.tiles_m * (p.tiles_m + 1) / 2 : (int64_t)p.tiles_m * p.tiles_n;
+  p.skip = mask_arg;
+  p.num_tiles = (mask == kLowerTiles) ? (int64_t)p.tiles_m * (p.tiles_m + 1) / 2
+              : (mask == kSkipBlockTiles) ? (int64_t)p.tiles_m * mask_arg + (int64_t)p.tiles_m * (p.tiles_m + 1) / 2
+              : (int64_t)p.tiles_m * p.tiles_n;
   p.status = status;
   static thread_local int attr_device = -1;
   int dev = 0;

@@ -7,7 +7,10 @@ namespace b200q {
 namespace tgemm {
 
 enum Trans { kNN = 0, kNT = 1 };
-enum TileMask { kAllTiles = 0, kLowerTiles = 1 };
+// kSkipBlockTiles (argument kb): C spans all columns of a matrix whose row 0 is the first row below
+// block row kb; tiles in column blocks < kb are all computed, column block kb is skipped, and
+// column blocks > kb only on and below the diagonal of the matrix (tile (tm, kb + 1 + j), j <= tm).
+enum TileMask { kAllTiles = 0, kLowerTiles = 1, kSkipBlockTiles = 2 };
 
 struct Split {       // a split operand: hi / lo arrays with a common leading dimension
   const float* hi;
@@ -24,7 +27,7 @@ int split_transposed(const float* src, int64_t ld_src, int rows, int cols, float
 // C[M,N] = beta*C + alpha * A[M,Kd] * B[N,Kd]^T with A, B given as hi/lo splits whose buffers hold
 // whole 128-row tiles (rows beyond M / N may hold anything).
 int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int Kd, float alpha, float beta,
-           int mask, int* status, cudaStream_t st);
+           int mask, int* status, cudaStream_t st, int mask_arg = 0);
 
 }  // namespace tgemm
 }  // namespace b200q
