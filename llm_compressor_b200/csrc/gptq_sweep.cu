@@ -1,11 +1,9 @@
 // GPTQ solve, part 2: the blockwise column sweep.
 //
-// Rows of W are independent, so they are spread over warps: one warp owns one row of the
-// current 128-column block, lane l holding columns l, l+32, l+64, l+96 in registers.  The
-// 128x128 diagonal block of U sits in shared memory.  Column by column the owning lane's
-// value is broadcast by shuffle, every lane computes the same quantised value, and each
-// lane applies the rank-1 correction to the columns it holds.  The quantisation error of the
-// block goes to a [N,128] scratch panel and the update of all later columns is one fp32
+// Rows of W are independent, so they are spread over lanes: a warp owns 32 rows of the current
+// 128-column block and each lane sweeps its own row (see sweep_block_kernel).  The 128x128
+// diagonal block of U sits in shared memory.  The quantisation error of the block goes to a
+// [N,128] scratch panel and the update of all later columns is one fp32-accurate tensor-core
 // tile GEMM  W[:, after] -= Err * U[block, after].
 //
 // Rounding follows the reference's sequence of separate float32 operations (product, then
@@ -17,7 +15,6 @@ namespace b200q {
 namespace sweep {
 
 constexpr int kMaxBlock = 128;
-constexpr int kWarps = 16;
 
 struct Params {
   float* W; int64_t ldw; int64_t N; int64_t K;
@@ -33,41 +30,109 @@ struct Params {
 };
 
 // SB: scale tensor is bf16 (and no global scale) -> dequantised value rounded to bf16.
+//
+// Lane-per-row version.  A warp owns 32 rows; lane r keeps row r of the current 16-column
+// sub-block in registers, so the quantisation of a column is done once per row (not once per
+// lane) and the rank-1 corrections inside the sub-block are plain register arithmetic with the
+// row of U broadcast from shared memory.  The other columns of the 128-column block sit in a
+// shared-memory tile (column-major, one word per row and column: lanes hit distinct banks) and
+// take the 16 corrections of a finished sub-block in one pass, column by column, in the same
+// order of operations as the column-at-a-time formulation (product, then subtraction), so the
+// results are bit-identical to it.
+constexpr int kMaxWarps = 8;      // warps of a CTA that own row batches
+constexpr int kCtaThreads = 256;  // all threads help with the loads of the U block
+constexpr int kSub = 16;          // columns kept in registers at a time (code size grows with its square)
+
+__host__ __device__ inline size_t sweep_smem_bytes(int warps) {
+  return ((size_t)kMaxBlock * kMaxBlock + (size_t)kMaxBlock * (32 * warps + 1) + (size_t)warps * kSub * 33 + 64) *
+         sizeof(float);
+}
+
+// One column of one row: fake-quantised value.  Kept out of line: the column loop is unrolled and
+// the kernel has to stay inside the instruction cache (a single warp per SM runs it for small N).
+template <bool SB>
+__device__ __noinline__ float sweep_quant(float wi, float s, float rs, float z, const QRange qr) {
+  // w is float32, so the quantise arithmetic is float32 (quant_code_fast gives the same code as the
+  // true division); only the dequantised value takes the scale's dtype
+  const float q = quant_code_fast<false>(wi, s, rs, z, qr);
+  return dequant_code<SB>(q, s, z);
+}
+
 template <int SDT, bool GLOBAL>
-__global__ void __launch_bounds__(kWarps * 32) sweep_block_kernel(Params p) {
+__global__ void __launch_bounds__(kCtaThreads) sweep_block_kernel(Params p, int warps) {
   constexpr bool SB = Elem<SDT>::is_bf16 && !GLOBAL;
-  extern __shared__ float sU[];  // [bs][kMaxBlock + 1] row i, local col c; identity when U is null
-  constexpr int LD = kMaxBlock + 1;
-  __shared__ float s_rd[kMaxBlock];   // 1 / U[i][i]
-  __shared__ int s_grp[kMaxBlock];    // parameter column (group / block column) of each column
+  extern __shared__ float sm[];
+  const int WLD = 32 * warps + 1;
+  float* sU = sm;                                   // [128][128] row i, local column c (identity when U is null)
+  float* sW = sU + kMaxBlock * kMaxBlock;           // [128][WLD] column c, row slot
+  float* sEall = sW + kMaxBlock * WLD;              // [warps][kSub][33]
+  __shared__ float s_rd[kMaxBlock];                 // 1 / U[i][i]
+  __shared__ int s_grp[kMaxBlock];                  // parameter column (group / block column) of each column
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bs = p.bs;
-  for (int idx = threadIdx.x; idx < bs * kMaxBlock; idx += blockDim.x) {
-    int r = idx / kMaxBlock, c = idx - r * kMaxBlock;
-    float v = 0.0f;
-    if (c < bs) v = p.U ? p.U[(int64_t)(p.i1 + r) * p.ldu + (p.i1 + c)] : (r == c ? 1.0f : 0.0f);
-    sU[r * LD + c] = v;
+  // U block (only c >= r is ever read): 16-byte loads when the layout allows, several in flight
+  {
+    const bool vec = p.U && ((p.ldu & 3) == 0) && ((((uintptr_t)p.U) & 15) == 0) && ((p.i1 & 3) == 0);
+    constexpr int kQuads = kMaxBlock * kMaxBlock / 4;
+#pragma unroll 4
+    for (int idx = threadIdx.x; idx < kQuads; idx += blockDim.x) {
+      const int r = idx >> 5, c = (idx & 31) << 2;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < bs && c + 3 >= r) {
+        if (!p.U) {
+          v.x = (r == c) ? 1.0f : 0.0f; v.y = (r == c + 1) ? 1.0f : 0.0f;
+          v.z = (r == c + 2) ? 1.0f : 0.0f; v.w = (r == c + 3) ? 1.0f : 0.0f;
+        } else {
+          const float* src = p.U + (int64_t)(p.i1 + r) * p.ldu + (p.i1 + c);
+          if (vec && c + 3 < bs) {
+            v = *reinterpret_cast<const float4*>(src);
+          } else {
+            if (c < bs) v.x = src[0];
+            if (c + 1 < bs) v.y = src[1];
+            if (c + 2 < bs) v.z = src[2];
+            if (c + 3 < bs) v.w = src[3];
+          }
+        }
+      }
+      *reinterpret_cast<float4*>(sU + idx * 4) = v;
+    }
   }
-  for (int i = threadIdx.x; i < bs; i += blockDim.x) {
-    const float d = p.U ? p.U[(int64_t)(p.i1 + i) * p.ldu + (p.i1 + i)] : 1.0f;
+  for (int i = threadIdx.x; i < kMaxBlock; i += blockDim.x) {
+    float d = 1.0f;
+    int grp = 0;
+    if (i < bs) {
+      if (p.U) d = p.U[(int64_t)(p.i1 + i) * p.ldu + (p.i1 + i)];
+      const int col = p.i1 + i;
+      grp = (p.strategy == B200Q_TENSOR || p.strategy == B200Q_CHANNEL)
+                ? 0 : (p.col_group ? p.col_group[col] : col / p.group_size);
+    }
     s_rd[i] = __frcp_rn(d);
-    const int col = p.i1 + i;
-    s_grp[i] = (p.strategy == B200Q_TENSOR || p.strategy == B200Q_CHANNEL)
-                   ? 0 : (p.col_group ? p.col_group[col] : col / p.group_size);
+    s_grp[i] = grp;
   }
   __syncthreads();
   const float g = GLOBAL ? *p.gscale : 1.0f;
   const bool has_zp = p.zp != nullptr;
+  float* sE = sEall + warp * (kSub * 33);
+  float* myW = sW + warp * 32;   // this warp's 32 row slots
+  const int64_t batches = (p.N + 31) / 32;
+  if (warp >= warps) return;   // no CTA-wide barrier below this point
 
-  for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < p.N; row += (int64_t)gridDim.x * kWarps) {
-    float w[4], qv[4], ev[4];
+  for (int64_t batch = (int64_t)blockIdx.x * warps + warp; batch < batches; batch += (int64_t)gridDim.x * warps) {
+    const int64_t row0 = batch * 32, row = row0 + lane;
+    const bool live = row < p.N;
+    // tile in: coalesced rows, transposed into the column-major tile
+#pragma unroll 8
+    for (int r = 0; r < 32; ++r) {
+      const int64_t rr = row0 + r;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      int c = lane + 32 * j;
-      w[j] = (c < bs) ? p.W[row * p.ldw + p.i1 + c] : 0.0f;
-      qv[j] = 0.0f; ev[j] = 0.0f;
+      for (int k = 0; k < 4; ++k) {
+        const int c = lane + 32 * k;
+        float v = 0.0f;
+        if (rr < p.N && c < bs) v = p.W[rr * p.ldw + p.i1 + c];
+        myW[c * WLD + r] = v;
+      }
     }
-    // base index of this row's parameters; the column's group is added per column
+    __syncwarp();
     int64_t pbase;
     switch (p.strategy) {
       case B200Q_TENSOR: pbase = 0; break;
@@ -76,52 +141,101 @@ __global__ void __launch_bounds__(kWarps * 32) sweep_block_kernel(Params p) {
       default: pbase = row * p.groups_per_row; break;
     }
     float loss = 0.0f;
-    int64_t cur_pi = -1;
+    int cur_grp = -1;
     float s = 1.0f, z = 0.0f, rs = 1.0f;
+#pragma unroll 1
+    for (int sub = 0; sub * kSub < bs; ++sub) {
+      const int c0 = sub * kSub;
+      float w[kSub], e[kSub];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int lim = min(32, bs - 32 * j);
-      for (int l = 0; l < lim; ++l) {
-        const int i = 32 * j + l;
-        const float wi = __shfl_sync(0xffffffffu, w[j], l);
-        const int64_t pi = pbase + s_grp[i];
-        if (pi != cur_pi) {
-          cur_pi = pi;
-          s = Elem<SDT>::load((const typename Elem<SDT>::type*)p.scale + pi);
-          if (GLOBAL) s = __fdiv_rn(s, g);
-          rs = __frcp_rn(s);
-          if (has_zp) z = load_zp(p.zp, p.zp_kind, pi);
-        }
-        // w is float32, so the quantise arithmetic is float32 (quant_code_fast gives the same code
-        // as the true division); only the dequantised value takes the scale's dtype
-        float q = quant_code_fast<false>(wi, s, rs, z, p.qr);
-        q = dequant_code<SB>(q, s, z);
-        const float diff = __fsub_rn(wi, q);
-        const float rd = s_rd[i];
-        // loss and error use the reciprocal of the pivot (an ulp from the reference's divisions)
-        const float t = __fmul_rn(diff, rd);
-        loss = fmaf(t, t, loss);
-        const float e = t;
-        if (lane == l) { qv[j] = q; ev[j] = e; }
+      for (int t = 0; t < kSub; ++t) w[t] = myW[(c0 + t) * WLD + lane];
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          const int c = lane + 32 * jj;
-          if (jj >= j && c >= i && c < bs) w[jj] = __fsub_rn(w[jj], __fmul_rn(e, sU[i * LD + c]));
+      for (int t = 0; t < kSub; ++t) {
+        const int i = c0 + t;
+        e[t] = 0.0f;
+        if (i < bs) {   // uniform
+          const int grp = s_grp[i];
+          if (grp != cur_grp) {   // uniform
+            cur_grp = grp;
+            if (live) {
+              const int64_t pi = pbase + grp;
+              s = Elem<SDT>::load((const typename Elem<SDT>::type*)p.scale + pi);
+              if (GLOBAL) s = __fdiv_rn(s, g);
+              rs = __frcp_rn(s);
+              if (has_zp) z = load_zp(p.zp, p.zp_kind, pi);
+            }
+          }
+          const float wi = w[t];
+          const float q = sweep_quant<SB>(wi, s, rs, z, p.qr);
+          const float diff = __fsub_rn(wi, q);
+          // loss and error use the reciprocal of the pivot (an ulp from the reference's divisions)
+          const float tt = __fmul_rn(diff, s_rd[i]);
+          loss = fmaf(tt, tt, loss);
+          e[t] = tt;
+          w[t] = q;
+          const float4* urow = reinterpret_cast<const float4*>(sU + i * kMaxBlock + c0);
+#pragma unroll
+          for (int k4 = (t + 1) / 4; k4 < kSub / 4; ++k4) {
+            const float4 u = urow[k4];
+            if (4 * k4 + 0 > t) w[4 * k4 + 0] = __fsub_rn(w[4 * k4 + 0], __fmul_rn(tt, u.x));
+            if (4 * k4 + 1 > t) w[4 * k4 + 1] = __fsub_rn(w[4 * k4 + 1], __fmul_rn(tt, u.y));
+            if (4 * k4 + 2 > t) w[4 * k4 + 2] = __fsub_rn(w[4 * k4 + 2], __fmul_rn(tt, u.z));
+            if (4 * k4 + 3 > t) w[4 * k4 + 3] = __fsub_rn(w[4 * k4 + 3], __fmul_rn(tt, u.w));
+          }
         }
       }
-    }
+      // quantised values back into the tile, errors to the staging tile
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      int c = lane + 32 * j;
-      if (c < bs) {
-        p.W[row * p.ldw + p.i1 + c] = qv[j];
-        p.err[row * p.lde + c] = ev[j];
+      for (int t = 0; t < kSub; ++t) {
+        myW[(c0 + t) * WLD + lane] = w[t];
+        sE[t * 33 + lane] = e[t];
+      }
+      __syncwarp();
+      {
+        // kSub columns x 32 rows out, two rows per instruction
+        const int ec = lane & (kSub - 1), er = lane / kSub;
+        if (c0 + ec < bs) {
+#pragma unroll 4
+          for (int r = er; r < 32; r += 32 / kSub) {
+            const int64_t rr = row0 + r;
+            if (rr < p.N) p.err[rr * p.lde + c0 + ec] = sE[ec * 33 + r];
+          }
+        }
+      }
+      __syncwarp();
+      // the later columns of the block take this sub-block's corrections
+#pragma unroll 1
+      for (int c = c0 + kSub; c < bs; c += 4) {
+        float v0 = myW[(c + 0) * WLD + lane], v1 = myW[(c + 1) * WLD + lane];
+        float v2 = myW[(c + 2) * WLD + lane], v3 = myW[(c + 3) * WLD + lane];
+#pragma unroll
+        for (int t = 0; t < kSub; ++t) {
+          const float4 u = *reinterpret_cast<const float4*>(sU + (c0 + t) * kMaxBlock + c);
+          v0 = __fsub_rn(v0, __fmul_rn(e[t], u.x));
+          v1 = __fsub_rn(v1, __fmul_rn(e[t], u.y));
+          v2 = __fsub_rn(v2, __fmul_rn(e[t], u.z));
+          v3 = __fsub_rn(v3, __fmul_rn(e[t], u.w));
+        }
+        myW[(c + 0) * WLD + lane] = v0; myW[(c + 1) * WLD + lane] = v1;
+        myW[(c + 2) * WLD + lane] = v2; myW[(c + 3) * WLD + lane] = v3;
       }
     }
-    if (lane == 0) {
+    __syncwarp();
+    // tile out
+    for (int r = 0; r < 32; ++r) {
+      const int64_t rr = row0 + r;
+      if (rr >= p.N) break;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = lane + 32 * k;
+        if (c < bs) p.W[rr * p.ldw + p.i1 + c] = myW[c * WLD + r];
+      }
+    }
+    if (live) {
       const float half = loss * 0.5f;
       p.losses[row] = p.first ? half : p.losses[row] + half;
     }
+    __syncwarp();
   }
 }
 
@@ -167,17 +281,24 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
   int* gemm_status = nullptr;
   p.losses = losses;
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = (size_t)kMaxBlock * (kMaxBlock + 1) * sizeof(float);
-  void (*kern)(Params) = nullptr;
+  // warps per CTA: one 32-row batch per warp; few rows -> small CTAs so that every SM gets work
+  const int64_t batches = (N + 31) / 32;
+  int warps = (int)((batches + kNumSMs - 1) / kNumSMs);
+  warps = warps < 1 ? 1 : (warps > kMaxWarps ? kMaxWarps : warps);
+  const size_t smem = sweep_smem_bytes(warps);
+  void (*kern)(Params, int) = nullptr;
   if (sdtype == B200Q_BF16) kern = gscale ? sweep_block_kernel<B200Q_BF16, true> : sweep_block_kernel<B200Q_BF16, false>;
   else if (sdtype == B200Q_F32) kern = gscale ? sweep_block_kernel<B200Q_F32, true> : sweep_block_kernel<B200Q_F32, false>;
   else return B200Q_ERR_UNSUPPORTED;
-  B200Q_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const int grid = grid_for((N + kWarps - 1) / kWarps, 3);
+  // always the largest size: host threads on other streams launch the same kernel with other sizes
+  B200Q_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)sweep_smem_bytes(kMaxWarps)));
+  int64_t ctas = (batches + warps - 1) / warps;
+  const int grid = (int)(ctas < 2 * kNumSMs ? ctas : 2 * kNumSMs);
   for (int64_t i1 = 0; i1 < K; i1 += blocksize) {
     const int bs = (int)((K - i1) < blocksize ? (K - i1) : blocksize);
     p.i1 = (int)i1; p.bs = bs; p.first = (i1 == 0);
-    kern<<<grid, kWarps * 32, smem, st>>>(p);
+    kern<<<grid, kCtaThreads, smem, st>>>(p, warps);
     B200Q_LAUNCH_CHECK();
     const int64_t i2 = i1 + bs;
     if (i2 < K && U) {
