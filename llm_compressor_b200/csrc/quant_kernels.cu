@@ -914,6 +914,30 @@ static int rtn_impl(const void* W, int64_t N, int64_t K, int64_t ldw, const b200
 #undef B200Q_RB3
   } else if (qa->strategy == B200Q_CHANNEL) {
     if (gscale) return B200Q_ERR_UNSUPPORTED;
+    if constexpr (DT == B200Q_BF16) {
+      const int64_t cpr = K >> 3;
+      if ((K & 7) == 0 && cpr <= 16 * stream::kThreads && N < (1 << 30)) {
+        const int r = cpr <= 2 * stream::kThreads ? 2 : cpr <= 4 * stream::kThreads ? 4
+                    : cpr <= 8 * stream::kThreads ? 8 : 16;
+        const int gridc = grid_for(N, r <= 4 ? 4 : 2);
+#define B200Q_CB2(MODE, RR) stream::rtn_channel_bf16_kernel<stream::MODE, RR><<<gridc, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, qc, qr, scale_out, zp_out, out)
+#define B200Q_CB(MODE)                       \
+  do {                                       \
+    if (r == 2) B200Q_CB2(MODE, 2);          \
+    else if (r == 4) B200Q_CB2(MODE, 4);     \
+    else if (r == 8) B200Q_CB2(MODE, 8);     \
+    else B200Q_CB2(MODE, 16);                \
+  } while (0)
+        if (qr.kind == kInt && qa->num_bits == 4) B200Q_CB(kInt4);
+        else if (qr.kind == kInt && qa->num_bits == 8) B200Q_CB(kInt8Word);
+        else if (qr.kind == kFp8) B200Q_CB(kByte);
+        else return B200Q_ERR_UNSUPPORTED;
+#undef B200Q_CB
+#undef B200Q_CB2
+        B200Q_LAUNCH_CHECK();
+        return B200Q_OK;
+      }
+    }
     size_t smem = (size_t)K * (DT == B200Q_BF16 ? 2 : 4);
     if (smem > 200 * 1024) return B200Q_ERR_UNSUPPORTED;
     int grid = grid_for(N, smem > 100 * 1024 ? 1 : 2);

@@ -578,5 +578,65 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// CHANNEL strategy, bf16 weights: one CTA per row, the row held in registers between the
+// statistics pass and the quantisation (R chunks of 8 elements per thread, K <= 2048 * R), so the
+// row is read from HBM once.  Same packed fast paths as the group kernels.
+template <int MODE, int R>
+__global__ void __launch_bounds__(kThreads) rtn_channel_bf16_kernel(
+    const void* __restrict__ W, int N, int K, int64_t ldw, QParamCfg qc, QRange qr,
+    void* __restrict__ scale_out, void* __restrict__ zp_out, void* __restrict__ out) {
+  using T = __nv_bfloat16;
+  __shared__ float s_lo[2][kThreads / 32], s_hi[2][kThreads / 32];
+  const int cpr = K >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool pow2_scale = qc.scale_kind == B200Q_SCALE_E8M0;
+  int par = 0;
+  for (int row = blockIdx.x; row < N; row += gridDim.x, par ^= 1) {
+    const T* wrow = (const T*)W + (int64_t)row * ldw;
+    uint4 raw[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const int c = threadIdx.x + k * kThreads;
+      raw[k] = (c < cpr) ? ldg_stream(wrow + (int64_t)c * 8) : make_uint4(0, 0, 0, 0);
+    }
+    float lo = INFINITY, hi = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      if (threadIdx.x + k * kThreads < cpr) {
+        float a, b;
+        minmax8_bf16(raw[k], a, b);
+        lo = fminf(lo, a); hi = fmaxf(hi, b);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    if (lane == 0) { s_lo[par][warp] = lo; s_hi[par][warp] = hi; }
+    __syncthreads();   // one barrier per row: the buffers alternate
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) { lo = fminf(lo, s_lo[par][w]); hi = fmaxf(hi, s_hi[par][w]); }
+    float s, z;
+    qparams_one<true>(lo, hi, qc, 1.0f, s, z);
+    if (threadIdx.x == 0) {
+      ((T*)scale_out)[row] = __float2bfloat16_rn(s);
+      if (zp_out) store_zp(zp_out, qc.zp_kind, row, z);
+    }
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const int c = threadIdx.x + k * kThreads;
+      if (c < cpr) {
+        uint32_t w0 = 0, w1 = 0;
+        chunk_codes_bf16<MODE, false, true>(raw[k], s, z, pow2_scale, qr, w0, w1);
+        const int64_t wi = (int64_t)row * cpr + c;
+        if (MODE == kInt4 || MODE == kFp4) ((uint32_t*)out)[wi] = w0;
+        else reinterpret_cast<uint2*>(out)[wi] = make_uint2(w0, w1);
+      }
+    }
+  }
+}
+
 }  // namespace stream
 }  // namespace b200q

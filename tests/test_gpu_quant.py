@@ -105,6 +105,28 @@ def test_fused_rtn_matches_unfused(golden, name):
         assert bits_equal(r["scale_store"], ref["weight_scale"])
 
 
+@pytest.mark.parametrize("name", ["fp8_channel", "w4_channel", "w8a16_channel"])
+@pytest.mark.parametrize("N,K", [(3, 8), (5, 2056), (33, 14336), (3, 28672), (4, 40960)])
+def test_fused_rtn_channel_row_lengths(golden, name, N, K):
+    """Rows from one chunk to more than the register-resident kernel holds (which falls back)."""
+    args = args_from(golden["ct_cases"][name]["args"])
+    spec = spec_from(golden["ct_cases"][name]["args"])
+    w = synth_weight(N, K, seed=N + K)
+    oqp = oracle.WeightObserver(spec)(w).get_qparams()
+    ref = oracle.compress_weight({"weight": w, "weight_scale": oqp["scale"].to(w.dtype),
+                                  "weight_zero_point": oqp["zero_point"]}, spec)
+    r = ops.rtn_quantize_pack(w.to(DEV), args)
+    assert bits_equal(r["scale"], oqp["scale"].to(w.dtype))
+    assert bits_equal(r["zero_point"], oqp["zero_point"])
+    if "weight_packed" in ref:
+        assert bits_equal(r["codes"], ref["weight_packed"])
+    else:
+        exp = ref["weight"]
+        if exp.dtype == torch.int8:
+            exp = oracle.pack_int32(exp, 8)
+        assert bits_equal(r["codes"], exp)
+
+
 def test_fused_nvfp4_and_shared_global_scale(golden):
     c = golden["ct_cases"]["nvfp4_fused3"]
     args = args_from(c["args"])
