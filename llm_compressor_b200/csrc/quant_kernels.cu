@@ -84,9 +84,11 @@ __device__ __forceinline__ void qparams_one(float mn, float mx, const QParamCfg&
     s = __uint_as_float(e >= 1.0f ? ((uint32_t)e << 23) : 0x00400000u);  // 2^(e-127)
   }
   if (s == 0.0f) s = c.eps;
-  if (c.zp_kind == B200Q_ZP_INT8) zp = rintf(fminf(fmaxf(zp, -128.0f), 127.0f));
-  else if (c.zp_kind == B200Q_ZP_UINT8) zp = rintf(fminf(fmaxf(zp, 0.0f), 255.0f));
-  else zp = e4m3_round(fminf(fmaxf(zp, -448.0f), 448.0f));
+  if (!c.symmetric) {   // a symmetric zero point is exactly 0 in every storage type
+    if (c.zp_kind == B200Q_ZP_INT8) zp = rintf(fminf(fmaxf(zp, -128.0f), 127.0f));
+    else if (c.zp_kind == B200Q_ZP_UINT8) zp = rintf(fminf(fmaxf(zp, 0.0f), 255.0f));
+    else zp = e4m3_round(fminf(fmaxf(zp, -448.0f), 448.0f));
+  }
   scale = s;
 }
 

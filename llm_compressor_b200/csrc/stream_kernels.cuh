@@ -133,20 +133,31 @@ __device__ __forceinline__ bool near_bf16_midpoint(float q) {
 }
 
 // common front end: 4 words of bf16 pairs -> 4 words of clamped bf16 pairs bf16(bf16(x/s)+zp)
+//
+// Midpoint test, two quotients at a time: the low half-words of both products are packed into
+// one word and 0x8004 is added to each (one 32-bit add; a carry out of the low half only widens
+// the window of the high half by one), which maps "within 3 ulps of the bf16 midpoint 0x8000" to
+// half-words 1..8.  The four words of a chunk are reduced with the packed 16-bit minimum and one
+// test "some half-word below 16" decides; false alarms only cost the exact path.
 template <bool EXACT, bool ADD_ZP>
 __device__ __forceinline__ void front8_bf16(const uint4& raw, float rs, uint32_t zp2, uint32_t lo2, uint32_t hi2,
                                             uint32_t (&v)[4], bool& unsafe) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  bool bad = false;
+  uint32_t m[4];
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
     const float q0 = __uint_as_float(w[p] << 16) * rs;
     const float q1 = __uint_as_float(w[p] & 0xFFFF0000u) * rs;
-    if (!EXACT) bad = bad || near_bf16_midpoint(q0) || near_bf16_midpoint(q1);
+    if (!EXACT) m[p] = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x5410) + 0x80048004u;
     const uint32_t c = cvt_bf16x2(q1, q0);
     v[p] = bf2_clamp(ADD_ZP ? bf2_add(c, zp2) : c, lo2, hi2);
   }
-  unsafe = bad;
+  if (!EXACT) {
+    const uint32_t mm = __vimin3_u16x2(__vimin3_u16x2(m[0], m[1], m[2]), m[3], m[3]) & 0xFFF0FFF0u;
+    unsafe = ((mm & 0xFFFFu) == 0u) || ((mm >> 16) == 0u);
+  } else {
+    unsafe = false;
+  }
 }
 // int4: 8 nibbles (value + 8) in one word
 __device__ __forceinline__ uint32_t tail8_int4(const uint32_t (&v)[4]) {
@@ -197,17 +208,19 @@ __device__ __forceinline__ uint32_t tail8_fp4(const uint32_t (&v)[4]) {
 // around x*(1/s) settle it; otherwise `unsafe`.
 __device__ __forceinline__ uint32_t nvfp4_8(const uint4& raw, float rs, bool& unsafe) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  float q[8], lo[8], hi[8];
+  // both ends of an interval that holds the exact quotient (reciprocal, its scaling and the
+  // product each round by 2^-24 or less; the margin is 2^-21).  The fused "+ 0" turns a -0.0
+  // weight into +0 like the reference's "+ zero_point".
+  const float rlo = rs * (1.0f - 0x1p-21f), rhi = rs * (1.0f + 0x1p-21f);
+  float lo[8], hi[8];
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
-    // x + 0 first: a -0.0 weight must give +0 like the reference's "+ zero_point"
-    q[2 * p] = __fadd_rn(__uint_as_float(w[p] << 16), 0.0f) * rs;
-    q[2 * p + 1] = __fadd_rn(__uint_as_float(w[p] & 0xFFFF0000u), 0.0f) * rs;
+    const float x0 = __uint_as_float(w[p] << 16), x1 = __uint_as_float(w[p] & 0xFFFF0000u);
+    lo[2 * p] = __fmaf_rn(x0, rlo, 0.0f); hi[2 * p] = __fmaf_rn(x0, rhi, 0.0f);
+    lo[2 * p + 1] = __fmaf_rn(x1, rlo, 0.0f); hi[2 * p + 1] = __fmaf_rn(x1, rhi, 0.0f);
   }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) { lo[i] = q[i] * (1.0f - 0x1p-21f); hi[i] = q[i] * (1.0f + 0x1p-21f); }
-  const uint32_t c = cvt_e2m1x8(q);
-  unsafe = (cvt_e2m1x8(lo) != c) || (cvt_e2m1x8(hi) != c);
+  const uint32_t c = cvt_e2m1x8(lo);
+  unsafe = cvt_e2m1x8(hi) != c;
   return c;
 }
 
@@ -327,6 +340,24 @@ __device__ __forceinline__ void minmax8_bf16(const uint4& raw, float& lo, float&
   hi = fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y));
   lo = fminf(__bfloat162float(mn.x), __bfloat162float(mn.y));
 }
+// min / max kept as bf16 pairs across several chunks, widened once at the end
+struct MinMax2 {
+  __nv_bfloat162 mn, mx;
+  __device__ __forceinline__ void first(const uint4& raw) {
+    const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    mx = __hmax2(__hmax2(w[0], w[1]), __hmax2(w[2], w[3]));
+    mn = __hmin2(__hmin2(w[0], w[1]), __hmin2(w[2], w[3]));
+  }
+  __device__ __forceinline__ void add(const uint4& raw) {
+    const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    mx = __hmax2(__hmax2(mx, w[0]), __hmax2(__hmax2(w[1], w[2]), w[3]));
+    mn = __hmin2(__hmin2(mn, w[0]), __hmin2(__hmin2(w[1], w[2]), w[3]));
+  }
+  __device__ __forceinline__ void finish(float& lo, float& hi) const {
+    hi = fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y));
+    lo = fminf(__bfloat162float(mn.x), __bfloat162float(mn.y));
+  }
+};
 __device__ __forceinline__ void unpack8_bf16(const uint4& raw, float (&v)[8]) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -425,12 +456,11 @@ __global__ void __launch_bounds__(kThreads) rtn_group_bf16_kernel(
         raw[k] = live ? ldg_stream(wrow + (int64_t)(c0 + k * L) * 8) : make_uint4(0, 0, 0, 0);
       float lo = INFINITY, hi = -INFINITY;
       if (live) {
+        MinMax2 mm;
+        mm.first(raw[0]);
 #pragma unroll
-        for (int k = 0; k < R; ++k) {
-          float a, b;
-          minmax8_bf16(raw[k], a, b);
-          lo = fminf(lo, a); hi = fmaxf(hi, b);
-        }
+        for (int k = 1; k < R; ++k) mm.add(raw[k]);
+        mm.finish(lo, hi);
       }
       for (int o = L >> 1; o > 0; o >>= 1) {
         lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
@@ -482,12 +512,11 @@ __global__ void __launch_bounds__(kThreads) minmax_group_bf16_kernel(const void*
         raw[k] = live ? ldg_stream(wrow + (int64_t)(c0 + k * L) * 8) : make_uint4(0, 0, 0, 0);
       float lo = INFINITY, hi = -INFINITY;
       if (live) {
+        MinMax2 mm;
+        mm.first(raw[0]);
 #pragma unroll
-        for (int k = 0; k < R; ++k) {
-          float a, b;
-          minmax8_bf16(raw[k], a, b);
-          lo = fminf(lo, a); hi = fmaxf(hi, b);
-        }
+        for (int k = 1; k < R; ++k) mm.add(raw[k]);
+        mm.finish(lo, hi);
       }
       for (int o = L >> 1; o > 0; o >>= 1) {
         lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
