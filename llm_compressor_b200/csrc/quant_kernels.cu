@@ -336,7 +336,8 @@ static int observe_minmax_impl(const void* W, int64_t N, int64_t K, int64_t ldw,
           const int rows2 = stream::kThreads / tx2;
           const int grid2 = grid_for((N + rows2 - 1) / rows2, 8);
           const int txl2 = __builtin_ctz(tx2), ll2 = __builtin_ctz(gsp.L);
-          if (gsp.R == 4) stream::minmax_group_bf16_kernel<4><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, mn, mx);
+          if (gsp.R == 8) stream::minmax_group_bf16_kernel<8><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, mn, mx);
+          else if (gsp.R == 4) stream::minmax_group_bf16_kernel<4><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, mn, mx);
           else if (gsp.R == 2) stream::minmax_group_bf16_kernel<2><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, mn, mx);
           else stream::minmax_group_bf16_kernel<1><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, mn, mx);
         } else {
@@ -557,6 +558,26 @@ static int quant_launch(const void* W, int64_t N, int64_t K, int64_t ldw, const 
                          ((pm.strategy == B200Q_GROUP || pm.strategy == B200Q_TENSOR_GROUP) &&
                           pm.g_idx == nullptr && (pm.group_size & 7) == 0) ||
                          (pm.strategy == B200Q_BLOCK && (pm.block_w & 7) == 0);
+    if constexpr (XDT == B200Q_BF16 && MODE != kPackFake) {
+      const int g = pm.group_size;
+      if ((pm.strategy == B200Q_GROUP || pm.strategy == B200Q_TENSOR_GROUP) && pm.g_idx == nullptr && g >= 8 &&
+          g <= 256 && (g & (g - 1)) == 0 && K % g == 0) {
+        const stream::GroupSplit gsp = stream::make_group_split(g, 4);
+        const int64_t slots = (K / g) * gsp.L;
+        int tx2 = 32;
+        while (tx2 < 256 && tx2 < slots) tx2 <<= 1;
+        const int rows2 = stream::kThreads / tx2;
+        const int grid2 = grid_for((N + rows2 - 1) / rows2, 6);
+        const int txl2 = __builtin_ctz(tx2), ll2 = __builtin_ctz(gsp.L);
+#define B200Q_QG(RR) stream::quant_group_bf16_kernel<SDT, GLOBAL, MODE, RR><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, scale, zp, zp_kind, gscale, qr, out)
+        if (gsp.R == 4) B200Q_QG(4);
+        else if (gsp.R == 2) B200Q_QG(2);
+        else B200Q_QG(1);
+#undef B200Q_QG
+        B200Q_LAUNCH_CHECK();
+        return B200Q_OK;
+      }
+    }
     stream::RowTiling t = stream::make_tiling(N, K, 6);
     stream::quant_rows_kernel<XDT, SDT, GLOBAL, MODE><<<t.grid, stream::kThreads, 0, st>>>(
         W, (int)N, (int)K, ldw, __builtin_ctz(t.tx), scale, zp, zp_kind, pm, uniform, gscale, qr, out, ldo);
@@ -889,7 +910,8 @@ static int rtn_impl(const void* W, int64_t N, int64_t K, int64_t ldw, const b200
 #define B200Q_RB3(MODE, GL, RR) stream::rtn_group_bf16_kernel<stream::MODE, GL, RR><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, qc, qr, gscale, scale_out, zp_out, scale_store, out)
 #define B200Q_RB2(MODE, GL)                         \
   do {                                              \
-    if (gsp.R == 4) B200Q_RB3(MODE, GL, 4);         \
+    if (gsp.R == 8) B200Q_RB3(MODE, GL, 8);         \
+    else if (gsp.R == 4) B200Q_RB3(MODE, GL, 4);    \
     else if (gsp.R == 2) B200Q_RB3(MODE, GL, 2);    \
     else B200Q_RB3(MODE, GL, 1);                    \
   } while (0)

@@ -423,10 +423,11 @@ __device__ __forceinline__ void chunk_codes_bf16(const uint4& raw, float se, flo
 // chunks L apart, so that one load instruction of the L lanes covers L*16 contiguous bytes and
 // the group's fixed cost (statistics, qparams, reciprocal) is paid once per R*8 elements.
 struct GroupSplit { int L, R; };
-inline GroupSplit make_group_split(int g) {
+inline GroupSplit make_group_split(int g, int rmax = 8) {
   const int chunks = g >> 3;
   GroupSplit s;
-  s.R = chunks >= 8 ? 4 : (chunks >= 4 ? 2 : 1);
+  s.R = chunks >= 16 ? 8 : (chunks >= 8 ? 4 : (chunks >= 4 ? 2 : 1));
+  if (s.R > rmax) s.R = rmax;   // measured: 8 pays when statistics are computed, 4 when they are given
   s.L = chunks / s.R;
   return s;
 }
@@ -602,6 +603,46 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(
           }
         }
         store_codes<MODE, XDT>(out, (int64_t)row * cpr + cc, (int64_t)row * ldo + col0, q, qr.kind);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// quantise + pack bf16 weights with given per-group parameters (no g_idx, group a power of two
+// in 8..256): the lane / chunk split of the fused kernel, parameters read once per R chunks.
+template <int SDT, bool GLOBAL, int MODE, int R>
+__global__ void __launch_bounds__(kThreads) quant_group_bf16_kernel(
+    const void* __restrict__ W, int N, int K, int64_t ldw, int g, int l_log2, int tx_log2,
+    const void* __restrict__ scale, const void* __restrict__ zp, int zp_kind, const float* __restrict__ gscale,
+    QRange qr, void* __restrict__ out) {
+  using T = __nv_bfloat16;
+  using ES = Elem<SDT>;
+  const float gs = GLOBAL ? *gscale : 1.0f;
+  const int TX = 1 << tx_log2, rows = kThreads >> tx_log2;
+  const int tx = threadIdx.x & (TX - 1), ty = threadIdx.x >> tx_log2;
+  const int L = 1 << l_log2, cpg = g >> 3, cpr = K >> 3, gpr = K / g;
+  const int slots = gpr << l_log2;
+  for (int row = blockIdx.x * rows + ty; row < N; row += gridDim.x * rows) {
+    const T* wrow = (const T*)W + (int64_t)row * ldw;
+    for (int t = tx; t < slots; t += TX) {
+      const int grp = t >> l_log2, j = t & (L - 1);
+      const int c0 = grp * cpg + j;
+      uint4 raw[R];
+#pragma unroll
+      for (int k = 0; k < R; ++k) raw[k] = ldg_stream(wrow + (int64_t)(c0 + k * L) * 8);
+      const int64_t pi = (int64_t)row * gpr + grp;
+      float s = ES::load((const typename ES::type*)scale + pi);
+      if (GLOBAL) s = __fdiv_rn(s, gs);
+      const float z = zp ? load_zp(zp, zp_kind, pi) : 0.0f;
+      const bool p2 = (__float_as_uint(s) & 0x7FFFFFu) == 0u;
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        uint32_t w0 = 0, w1 = 0;
+        chunk_codes_bf16<MODE, GLOBAL, ES::is_bf16>(raw[k], s, z, p2, qr, w0, w1);
+        const int64_t wi = (int64_t)row * cpr + c0 + k * L;
+        if (MODE == kInt4 || MODE == kFp4) ((uint32_t*)out)[wi] = w0;
+        else reinterpret_cast<uint2*>(out)[wi] = make_uint2(w0, w1);
       }
     }
   }
