@@ -262,7 +262,7 @@ class LayerBench:
             if record:
                 ev = torch.cuda.Event(enable_timing=True)
                 ev.record()
-                self.job_events.append((g_, what, ev))
+                self.job_events.append((len(self.phase_events) // 4, g_, what, ev))
 
         def solve(g_):
             # queued without waiting for the device; status and losses are read at the end
@@ -444,8 +444,10 @@ def run_b200(args):
     jobs = {}
     if len(pe) >= 4:
         t0 = pe[len(pe) - 2]
-        for g_, what, ev in bench.job_events[-3 * len(GROUP_K):]:
-            jobs.setdefault(g_, []).append(round(t0.elapsed_time(ev), 1))
+        last = len(pe) // 4 - 1
+        for step_i, g_, what, ev in bench.job_events:
+            if step_i == last:
+                jobs.setdefault(g_, []).append(round(t0.elapsed_time(ev), 1))
 
     # end to end through the public API with host buffers
     e2e = None

@@ -12,3 +12,4 @@ from .gptq import (accumulate_hessian, make_empty_hessian, quantize_weight,  # n
 from .modifiers import GPTQModifier, QuantizationModifier, match_named_modules  # noqa: F401
 from .oneshot import oneshot, save_compressed_model  # noqa: F401
 from .compressors import compress_state_dict, infer_module_format  # noqa: F401
+from .model_free import model_free_ptq  # noqa: F401

@@ -269,14 +269,6 @@ __global__ void __launch_bounds__(kDiagThreads, 1) chol_diag_kernel(float* __res
     }
 }
 
-// X[k,k] = Linv_kk
-__global__ void copy_block_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t ldd, int n) {
-  for (int idx = threadIdx.x + blockIdx.x * blockDim.x; idx < n * n; idx += blockDim.x * gridDim.x) {
-    int r = idx / n, c = idx - r * n;
-    dst[(int64_t)r * ldd + c] = src[r * NB + c];
-  }
-}
-
 static inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
 }  // namespace solve
@@ -354,7 +346,7 @@ size_t b200q_gptq_factor_workspace_bytes(int64_t K) {
   int64_t nb = (K + NB - 1) / NB;
   // reversed matrix + inverse diagonal blocks + hi/lo copies of the two GEMM operands
   // (split buffers are whole 128-row tiles: the GEMM's TMA boxes read full tiles)
-  return (size_t)(K * lda + nb * NB * NB + 4 * (nb * NB) * NB + 4 * NB * NB) * sizeof(float);
+  return (size_t)(K * lda + nb * NB * NB + 6 * (nb * NB) * NB + 4 * NB * NB) * sizeof(float);
 }
 
 int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* status, void* stream) {
@@ -367,9 +359,9 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
   const int64_t cap = (int64_t)nb * NB * NB;      // floats per split buffer: [roundup(K,128)][128]
   float* sa_hi = Dinv + cap;                      // panel before its update: [rem][128]
   float* sa_lo = sa_hi + cap;
-  float* sb_hi = sa_lo + cap;                     // operand rows by absolute column: [roundup(K,128)][128]
-  float* sb_lo = sb_hi + cap;
-  float* d_hi = sb_lo + cap;                      // Linv_kk and its transpose, split
+  float* sb_base = sa_lo + cap;                   // operand rows by absolute column: [roundup(K,128)][128],
+                                                  // hi and lo, two copies used by alternate steps
+  float* d_hi = sb_base + 4 * cap;                // Linv_kk and its transpose, split
   float* d_lo = d_hi + NB * NB;
   float* dt_hi = d_lo + NB * NB;
   float* dt_lo = dt_hi + NB * NB;
@@ -391,12 +383,23 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
   //   P        = A[k+1:,k] X[k,k]^T                       (= L[k+1:,k])
   //   S[i,k]   = -P X[k,k]                                (in place of P)
   //   S[i,:k] -= P X[k,:k]   and   A[i,j] -= P P^T (j > k, lower tiles)      one GEMM launch
+  //
+  // Look-ahead: the update of step k is split in the tiles step k+1 reads (block row k+1 and
+  // block column k+1: tgemm::kSkipBlockFirst, on the caller's stream) and the rest
+  // (kSkipBlockRest), which runs on a helper stream beside step k+1's diagonal block and panel
+  // work.  Both parts of step k+1 touch tiles the rest of step k also updates, so they wait for it;
+  // the operand panels alternate between two buffers because the helper may still read step k's
+  // while step k+1's are written.
+  tgemm::SideStream* side = tgemm::side_stream(st);
+  bool side_busy = false;
   for (int k = 0; k < nb; ++k) {
     const int k0 = k * NB;
     const int n = (int)min((int64_t)NB, K - k0);
     const int rem = (int)(K - k0 - n);
     float* Dk = Dinv + (int64_t)k * NB * NB;
     float* rowk = A + (int64_t)k0 * lda;        // block row k, columns < k0: n x k0
+    float* sb_hi = sb_base + (int64_t)(k & 1) * 2 * cap;
+    float* sb_lo = sb_hi + cap;
     const int64_t ldn = tgemm::split_ld(n);
     chol_diag_kernel<<<1, kDiagThreads, diag_smem, st>>>(A, lda, k0, n, Dk, status);
     B200Q_LAUNCH_CHECK();
@@ -425,9 +428,23 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
     B200Q_RC(tgemm::launch(tgemm::kNT, Split{ph, pl, ldn}, Split{dt_hi, dt_lo, ldn}, P, lda, rem, n, n, -1.0f, 0.0f,
                            tgemm::kAllTiles, status + 2, st));
     // rows below block k: columns < k0 take -P X[k,:k0], columns > block k take -P P^T
-    B200Q_RC(tgemm::launch(tgemm::kNT, Split{ph, pl, ldn}, Split{sb_hi, sb_lo, ldn}, A + (int64_t)(k0 + n) * lda, lda,
-                           rem, (int)K, n, -1.0f, 1.0f, tgemm::kSkipBlockTiles, status + 2, st, k));
+    float* C = A + (int64_t)(k0 + n) * lda;
+    if (!side) {
+      B200Q_RC(tgemm::launch(tgemm::kNT, Split{ph, pl, ldn}, Split{sb_hi, sb_lo, ldn}, C, lda, rem, (int)K, n, -1.0f,
+                             1.0f, tgemm::kSkipBlockTiles, status + 2, st, k));
+      continue;
+    }
+    B200Q_TRY(cudaEventRecord(side->ready, st));
+    B200Q_TRY(cudaStreamWaitEvent(side->stream, side->ready, 0));
+    if (side_busy) B200Q_TRY(cudaStreamWaitEvent(st, side->done, 0));   // rest of step k-1
+    B200Q_RC(tgemm::launch(tgemm::kNT, Split{ph, pl, ldn}, Split{sb_hi, sb_lo, ldn}, C, lda, rem, (int)K, n, -1.0f,
+                           1.0f, tgemm::kSkipBlockFirst, status + 2, st, k));
+    B200Q_RC(tgemm::launch(tgemm::kNT, Split{ph, pl, ldn}, Split{sb_hi, sb_lo, ldn}, C, lda, rem, (int)K, n, -1.0f,
+                           1.0f, tgemm::kSkipBlockRest, status + 2, side->stream, k));
+    B200Q_TRY(cudaEventRecord(side->done, side->stream));
+    side_busy = true;
   }
+  if (side_busy) B200Q_TRY(cudaStreamWaitEvent(st, side->done, 0));
 #undef B200Q_RC
 
   reverse_out_kernel<<<grid_for((K * K + 255) / 256, 8), 256, 0, st>>>(A, K, lda, H, ldh);

@@ -248,9 +248,10 @@ extern "C" {
 
 size_t b200q_gptq_sweep_workspace_bytes(int64_t N, int64_t K, int blocksize) {
   if (N <= 0 || K <= 0 || blocksize <= 0) return 0;
-  // error panel [N][128] + hi/lo copies of it + hi/lo copies of a 128-row panel of U
+  // error panel [N][128] + two sets of (hi/lo copies of it, hi/lo copies of a 128-row panel of U):
+  // consecutive blocks alternate between the sets because of the look-ahead
   const size_t np = (size_t)((N + 127) / 128 * 128), kp = (size_t)((K + 127) / 128 * 128);
-  return (np * 128 * 3 + 2 * 128 * kp) * sizeof(float) + 64;
+  return (np * 128 * 5 + 4 * 128 * kp) * sizeof(float) + 64;
 }
 
 int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* U, int64_t ldu, const void* scale,
@@ -274,10 +275,8 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
   p.err = (float*)workspace;
   p.lde = 128;
   const size_t np128 = (size_t)((N + 127) / 128 * 128) * 128, kp128 = (size_t)((K + 127) / 128 * 128) * 128;
-  float* sa_hi = p.err + np128;
-  float* sa_lo = sa_hi + np128;
-  float* sb_hi = sa_lo + np128;
-  float* sb_lo = sb_hi + kp128;
+  float* sa_base = p.err + np128;            // [2][hi, lo][np128]
+  float* sb_base = sa_base + 4 * np128;      // [2][hi, lo][kp128]
   int* gemm_status = nullptr;
   p.losses = losses;
   cudaStream_t st = (cudaStream_t)stream;
@@ -295,7 +294,13 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
                                  (int)sweep_smem_bytes(kMaxWarps)));
   int64_t ctas = (batches + warps - 1) / warps;
   const int grid = (int)(ctas < 2 * kNumSMs ? ctas : 2 * kNumSMs);
-  for (int64_t i1 = 0; i1 < K; i1 += blocksize) {
+  // Look-ahead: the trailing update of a block is split in the next 128 columns (which the next
+  // block's sweep reads; caller's stream) and the columns after them, which a helper stream
+  // updates while the next block is swept.
+  tgemm::SideStream* side = U ? tgemm::side_stream(st) : nullptr;
+  bool side_busy = false;
+  int blk = 0;
+  for (int64_t i1 = 0; i1 < K; i1 += blocksize, ++blk) {
     const int bs = (int)((K - i1) < blocksize ? (K - i1) : blocksize);
     p.i1 = (int)i1; p.bs = bs; p.first = (i1 == 0);
     kern<<<grid, kCtaThreads, smem, st>>>(p, warps);
@@ -304,14 +309,38 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
     if (i2 < K && U) {
       // W[:, i2:] -= Err[N, bs] * U[i1:i2, i2:]   (3xTF32 on the tensor cores)
       const int rest = (int)(K - i2);
+      float* sa_hi = sa_base + (size_t)(blk & 1) * 2 * np128;
+      float* sa_lo = sa_hi + np128;
+      float* sb_hi = sb_base + (size_t)(blk & 1) * 2 * kp128;
+      float* sb_lo = sb_hi + kp128;
+      const int64_t ld = tgemm::split_ld(bs);
       rc = tgemm::split(p.err, p.lde, (int)N, bs, sa_hi, sa_lo, st); if (rc) return rc;
       rc = tgemm::split_transposed(U + i1 * ldu + i2, ldu, bs, rest, sb_hi, sb_lo, st); if (rc) return rc;
-      rc = tgemm::launch(tgemm::kNT, tgemm::Split{sa_hi, sa_lo, tgemm::split_ld(bs)},
-                         tgemm::Split{sb_hi, sb_lo, tgemm::split_ld(bs)}, Wf + i2, ldf, (int)N, rest, bs, -1.0f,
-                         1.0f, tgemm::kAllTiles, gemm_status, st);
+      const tgemm::Split A{sa_hi, sa_lo, ld};
+      if (!side) {
+        rc = tgemm::launch(tgemm::kNT, A, tgemm::Split{sb_hi, sb_lo, ld}, Wf + i2, ldf, (int)N, rest, bs, -1.0f, 1.0f,
+                           tgemm::kAllTiles, gemm_status, st);
+        if (rc) return rc;
+        continue;
+      }
+      const int near = rest < 128 ? rest : 128;
+      B200Q_TRY(cudaEventRecord(side->ready, st));
+      B200Q_TRY(cudaStreamWaitEvent(side->stream, side->ready, 0));
+      if (side_busy) B200Q_TRY(cudaStreamWaitEvent(st, side->done, 0));   // far columns of the block before
+      rc = tgemm::launch(tgemm::kNT, A, tgemm::Split{sb_hi, sb_lo, ld}, Wf + i2, ldf, (int)N, near, bs, -1.0f, 1.0f,
+                         tgemm::kAllTiles, gemm_status, st);
       if (rc) return rc;
+      if (rest > near) {
+        rc = tgemm::launch(tgemm::kNT, A, tgemm::Split{sb_hi + (int64_t)near * ld, sb_lo + (int64_t)near * ld, ld},
+                           Wf + i2 + near, ldf, (int)N, rest - near, bs, -1.0f, 1.0f, tgemm::kAllTiles, gemm_status,
+                           side->stream);
+        if (rc) return rc;
+        B200Q_TRY(cudaEventRecord(side->done, side->stream));
+        side_busy = true;
+      }
     }
   }
+  if (side_busy) B200Q_TRY(cudaStreamWaitEvent(st, side->done, 0));
   return B200Q_OK;
 }
 

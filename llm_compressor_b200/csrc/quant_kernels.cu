@@ -158,44 +158,8 @@ static bool vec_ok(const void* p, int64_t K, int64_t ld, int elem_bytes) {
 static bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 
 // ========================================================================================
-// observe_minmax
+// observe_minmax (the streaming group kernels are in stream_kernels.cuh)
 // ========================================================================================
-// GROUP fast path: each thread owns 8 consecutive elements; the g/8 lanes that share a group
-// reduce with xor shuffles.  Chunks are laid out so that a group never straddles a warp.
-template <int DT>
-__global__ void __launch_bounds__(256) minmax_group_vec_kernel(
-    const void* __restrict__ W, int64_t N, int64_t K, int64_t ldw, int g, void* __restrict__ mn_out,
-    void* __restrict__ mx_out) {
-  using E = Elem<DT>;
-  const int lanes = g >> 3;  // lanes per group (1..32)
-  const int64_t chunks_per_row = K >> 3;
-  const int64_t total = N * chunks_per_row;
-  const int64_t groups_per_row = K / g;
-  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < ((total + 31) & ~31LL);
-       c += (int64_t)gridDim.x * blockDim.x) {
-    float lo = INFINITY, hi = -INFINITY;
-    int64_t row = 0, cc = 0;
-    bool live = c < total;
-    if (live) {
-      row = c / chunks_per_row;
-      cc = c - row * chunks_per_row;
-      float v[8];
-      load8<DT>(W, row * ldw + cc * 8, v);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { lo = fminf(lo, v[i]); hi = fmaxf(hi, v[i]); }
-    }
-    for (int o = lanes >> 1; o > 0; o >>= 1) {
-      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
-      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
-    }
-    if (live && (cc % lanes) == 0) {
-      int64_t gi = row * groups_per_row + (cc * 8) / g;
-      E::store((typename E::type*)mn_out + gi, lo);
-      E::store((typename E::type*)mx_out + gi, hi);
-    }
-  }
-}
-
 // generic: one thread per qparam entry (group / block), any sizes
 template <int DT>
 __global__ void minmax_generic_kernel(const void* __restrict__ W, int64_t N, int64_t K, int64_t ldw,
@@ -430,78 +394,6 @@ enum PackMode { kPackFake = 0, kPackInt4 = 1, kPackByte = 2, kPackFp4 = 3, kPack
 template <int SDT>
 __device__ __forceinline__ float load_scale(const void* scale, int64_t i) {
   return Elem<SDT>::load((const typename Elem<SDT>::type*)scale + i);
-}
-
-// Each thread: 8 consecutive elements of one row (vector path).
-template <int XDT, int SDT, bool GLOBAL, int MODE>
-__global__ void __launch_bounds__(256) quant_vec_kernel(
-    const void* __restrict__ W, int64_t N, int64_t K, int64_t ldw, const void* __restrict__ scale,
-    const void* __restrict__ zp, int zp_kind, ParamMap pm, const float* __restrict__ gscale,
-    QRange qr, void* __restrict__ out, int64_t ldo) {
-  constexpr bool XB = Elem<XDT>::is_bf16;
-  constexpr bool SB = Elem<SDT>::is_bf16 && !GLOBAL;  // dtype of the effective scale
-  constexpr bool CB = XB && SB;
-  const float g = GLOBAL ? *gscale : 1.0f;
-  const int64_t cpr = K >> 3, total = N * cpr;
-  const bool uniform = (pm.strategy == B200Q_TENSOR) || (pm.strategy == B200Q_CHANNEL) ||
-                       ((pm.strategy == B200Q_GROUP || pm.strategy == B200Q_TENSOR_GROUP) &&
-                        pm.g_idx == nullptr && (pm.group_size & 7) == 0) ||
-                       (pm.strategy == B200Q_BLOCK && (pm.block_w & 7) == 0);
-  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < total;
-       c += (int64_t)gridDim.x * blockDim.x) {
-    int64_t row = c / cpr, cc = c - row * cpr, col0 = cc * 8;
-    float v[8], q[8];
-    load8<XDT>(W, row * ldw + col0, v);
-    float s = 0.f, z = 0.f;
-    if (uniform) {
-      int64_t pi = pm.index(row, col0);
-      s = load_scale<SDT>(scale, pi);
-      if (GLOBAL) s = __fdiv_rn(s, g);
-      if (zp) z = load_zp(zp, zp_kind, pi);
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (!uniform) {
-        int64_t pi = pm.index(row, col0 + i);
-        s = load_scale<SDT>(scale, pi);
-        if (GLOBAL) s = __fdiv_rn(s, g);
-        if (zp) z = load_zp(zp, zp_kind, pi);
-      }
-      q[i] = quant_code<CB>(v[i], s, z, qr);
-      if (MODE == kPackFake) q[i] = dequant_code<SB>(q[i], s, z);
-    }
-    if constexpr (MODE == kPackFake) {
-      store8<XDT>(out, row * ldo + col0, q);
-    } else if constexpr (MODE == kPackInt4) {
-      uint32_t w = 0;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) w |= ((uint32_t)((int)q[i] + 8) & 0xFu) << (4 * i);
-      ((uint32_t*)out)[row * cpr + cc] = w;
-    } else if constexpr (MODE == kPackInt8Word) {
-      uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        w0 |= ((uint32_t)((int)q[i] + 128) & 0xFFu) << (8 * i);
-        w1 |= ((uint32_t)((int)q[i + 4] + 128) & 0xFFu) << (8 * i);
-      }
-      reinterpret_cast<uint2*>(out)[row * cpr + cc] = make_uint2(w0, w1);
-    } else if constexpr (MODE == kPackByte) {
-      uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t b0 = (qr.kind == kFp8) ? e4m3_bits(q[i]) : ((uint32_t)(int)q[i] & 0xFFu);
-        uint32_t b1 = (qr.kind == kFp8) ? e4m3_bits(q[i + 4]) : ((uint32_t)(int)q[i + 4] & 0xFFu);
-        w0 |= b0 << (8 * i);
-        w1 |= b1 << (8 * i);
-      }
-      reinterpret_cast<uint2*>(out)[row * cpr + cc] = make_uint2(w0, w1);
-    } else {  // kPackFp4
-      uint32_t w = 0;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) w |= e2m1_nibble(q[i]) << (4 * i);
-      ((uint32_t*)out)[row * cpr + cc] = w;
-    }
-  }
 }
 
 // Scalar path for ragged shapes: one thread per output unit (word / byte / element).

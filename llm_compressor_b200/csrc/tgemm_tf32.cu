@@ -16,6 +16,9 @@
 // are bounded; no cluster launch, no multicast.
 #include <cuda.h>
 
+#include <cstdlib>
+#include <mutex>
+
 #include "common.cuh"
 #include "tgemm_tf32.cuh"
 
@@ -123,6 +126,23 @@ __device__ __forceinline__ void tile_from_index(const Params& p, int64_t t, int&
     while ((int64_t)(i + 1) * (i + 2) / 2 <= t) ++i;
     tm = i;
     tn = (int)(t - (int64_t)i * (i + 1) / 2);
+  } else if (p.mask == kSkipBlockFirst) {
+    if (t < p.skip) { tm = 0; tn = (int)t; }
+    else if (t == p.skip) { tm = 0; tn = p.skip + 1; }
+    else { tm = (int)(t - p.skip); tn = p.skip + 1; }
+  } else if (p.mask == kSkipBlockRest) {
+    const int64_t left = (int64_t)(p.tiles_m - 1) * p.skip;
+    if (t < left) {
+      tm = 1 + (int)(t / p.skip);
+      tn = (int)(t - (int64_t)(tm - 1) * p.skip);
+    } else {
+      const int64_t u = t - left;
+      int i = (int)((sqrt(8.0 * (double)u + 1.0) - 1.0) * 0.5);
+      while ((int64_t)i * (i + 1) / 2 > u) --i;
+      while ((int64_t)(i + 1) * (i + 2) / 2 <= u) ++i;
+      tm = i + 1;
+      tn = p.skip + 2 + (int)(u - (int64_t)i * (i + 1) / 2);
+    }
   } else if (p.mask == kSkipBlockTiles) {
     const int64_t left = (int64_t)p.tiles_m * p.skip;
     if (t < left) {
@@ -471,6 +491,7 @@ inline MapCache& map_cache() {
 int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int Kd, float alpha, float beta,
            int mask, int* status, cudaStream_t st, int mask_arg) {
   if (M <= 0 || N <= 0 || Kd <= 0) return B200Q_OK;
+  if (mask == kSkipBlockRest && M <= kTile) return B200Q_OK;   // a single row block has no rest
   if (Kd > 128 || (A.ld & 31) || (B.ld & 31) || A.ld < Kd || B.ld < Kd) return B200Q_ERR_ARG;
   if (trans != kNT) return B200Q_ERR_UNSUPPORTED;
   MapCache& mc = map_cache();
@@ -486,6 +507,8 @@ int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int
   p.skip = mask_arg;
   p.num_tiles = (mask == kLowerTiles) ? (int64_t)p.tiles_m * (p.tiles_m + 1) / 2
               : (mask == kSkipBlockTiles) ? (int64_t)p.tiles_m * mask_arg + (int64_t)p.tiles_m * (p.tiles_m + 1) / 2
+              : (mask == kSkipBlockFirst) ? (int64_t)mask_arg + p.tiles_m
+              : (mask == kSkipBlockRest) ? (int64_t)(p.tiles_m - 1) * mask_arg + (int64_t)p.tiles_m * (p.tiles_m - 1) / 2
               : (int64_t)p.tiles_m * p.tiles_n;
   p.status = status;
   static thread_local int attr_device = -1;
@@ -505,6 +528,35 @@ int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int
   tgemm_kernel<<<grid, kThreads, kSmemBytes, st>>>(mah, mal, mbh, mbl, mc_c, p);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
+}
+
+SideStream* side_stream(cudaStream_t like) {
+  // one helper per (device, caller stream), kept for the life of the process: host threads come
+  // and go, the streams they launch on do not
+  struct Entry { int device; cudaStream_t like; SideStream s; };
+  constexpr int kMax = 64;
+  static Entry entries[kMax];
+  static int used = 0;
+  static std::mutex mu;
+  int dev = 0, prio = 0;
+  static const bool enabled = [] { const char* e = getenv("B200Q_LOOKAHEAD"); return e && e[0] == '1'; }();
+  if (!enabled) return nullptr;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < used; ++i)
+    if (entries[i].device == dev && entries[i].like == like) return &entries[i].s;
+  if (used == kMax) return nullptr;
+  if (cudaStreamGetPriority(like, &prio) != cudaSuccess) { (void)cudaGetLastError(); prio = 0; }
+  Entry& e = entries[used];
+  e.device = dev; e.like = like;
+  if (cudaStreamCreateWithPriority(&e.s.stream, cudaStreamNonBlocking, prio) != cudaSuccess ||
+      cudaEventCreateWithFlags(&e.s.ready, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&e.s.done, cudaEventDisableTiming) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  ++used;
+  return &e.s;
 }
 
 }  // namespace tgemm

@@ -3,6 +3,8 @@
 
 #include "common.cuh"
 
+#include <cuda_runtime.h>
+
 namespace b200q {
 namespace tgemm {
 
@@ -10,7 +12,10 @@ enum Trans { kNN = 0, kNT = 1 };
 // kSkipBlockTiles (argument kb): C spans all columns of a matrix whose row 0 is the first row below
 // block row kb; tiles in column blocks < kb are all computed, column block kb is skipped, and
 // column blocks > kb only on and below the diagonal of the matrix (tile (tm, kb + 1 + j), j <= tm).
-enum TileMask { kAllTiles = 0, kLowerTiles = 1, kSkipBlockTiles = 2 };
+// kSkipBlockFirst / kSkipBlockRest split the kSkipBlockTiles set in two: First = row block 0 and
+// column block kb + 1 (what the next step of a right-looking factorisation reads), Rest = the
+// other tiles (which can run beside that next step).
+enum TileMask { kAllTiles = 0, kLowerTiles = 1, kSkipBlockTiles = 2, kSkipBlockFirst = 3, kSkipBlockRest = 4 };
 
 struct Split {       // a split operand: hi / lo arrays with a common leading dimension
   const float* hi;
@@ -28,6 +33,16 @@ int split_transposed(const float* src, int64_t ld_src, int rows, int cols, float
 // whole 128-row tiles (rows beyond M / N may hold anything).
 int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int Kd, float alpha, float beta,
            int mask, int* status, cudaStream_t st, int mask_arg = 0);
+
+// A helper stream of the calling host thread (same priority as `like`), with two events, for the
+// look-ahead of the blocked solves: the bulk of a rank-128 update runs there while the caller's
+// stream goes on with the next block.  Created once per device and caller stream; null on failure.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ready = nullptr;   // recorded on the caller's stream: operands of the bulk update exist
+  cudaEvent_t done = nullptr;    // recorded on the helper: bulk update finished
+};
+SideStream* side_stream(cudaStream_t like);
 
 }  // namespace tgemm
 }  // namespace b200q

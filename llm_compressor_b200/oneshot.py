@@ -164,13 +164,10 @@ def oneshot(model, recipe=None, dataset=None, num_calibration_samples: int = 512
     return model
 
 
-def save_compressed_model(model, output_dir: str, compress: bool = True) -> dict:
-    """Write the compressed-tensors checkpoint layout: ``model.safetensors`` with
+def compressed_state_dict(model, compress: bool = True):
+    """``(state, quantization_config)`` of ``model`` in the compressed-tensors layout:
     ``<module>.weight_packed`` / ``weight_scale`` / ``weight_shape`` / ... per quantised module,
-    and ``config.json`` carrying ``quantization_config`` (CT model_compressor.py:177-213).
-    Only rank 0 writes.  Returns the state dict that was written."""
-    from safetensors.torch import save_file
-
+    everything else as it is, tensors on the CPU (CT model_compressor.py:177-213)."""
     state, formats, groups, ignore = {}, set(), {}, []
     quantised = {n: m for n, m in model.named_modules() if hasattr(m, "quantization_scheme")}
     skip = set()
@@ -194,7 +191,7 @@ def save_compressed_model(model, output_dir: str, compress: bool = True) -> dict
         if k not in skip and k not in state:
             state[k] = v.detach().contiguous().cpu()
     for n, m in model.named_modules():
-        if isinstance(m, torch.nn.Linear) and n not in quantised:
+        if (isinstance(m, torch.nn.Linear) or type(m).__name__ == "Linear") and n not in quantised:
             ignore.append(n)
 
     def args_dict(a):
@@ -217,6 +214,17 @@ def save_compressed_model(model, output_dir: str, compress: bool = True) -> dict
         "ignore": ignore, "kv_cache_scheme": None, "sparsity_config": {}, "transform_config": {},
         "global_compression_ratio": None,
     }
+    return state, qconfig
+
+
+def save_compressed_model(model, output_dir: str, compress: bool = True) -> dict:
+    """Write the compressed-tensors checkpoint layout: ``model.safetensors`` with
+    ``<module>.weight_packed`` / ``weight_scale`` / ``weight_shape`` / ... per quantised module,
+    and ``config.json`` carrying ``quantization_config`` (CT model_compressor.py:177-213).
+    Only rank 0 writes.  Returns the state dict that was written."""
+    from safetensors.torch import save_file
+
+    state, qconfig = compressed_state_dict(model, compress)
     if bdist.rank() == 0:
         os.makedirs(output_dir, exist_ok=True)
         # tied tensors (embeddings / lm_head) share storage; safetensors wants distinct buffers
