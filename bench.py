@@ -487,6 +487,14 @@ def run_b200(args):
                "d2h_bytes_per_step": d2h_bytes, "steps": steps_e2e,
                "host_pool_fraction": round(feeder.pool_fraction, 3)}
 
+    # quantize / pack kernels (the metric's "pack GB/s"), rank 0, after the timed region
+    pack = None
+    if rank == 0 and not args.no_pack:
+        del results
+        flush = torch.empty(8, dtype=torch.uint8, device=dev)
+        pack = {r["kernel"]: {"gbs": round(r["gbs"], 1), "frac_of_hbm_peak": round(r["frac_of_hbm_peak"], 3)}
+                for r in pack_micro(5, peaks, make_timed(flush), torch.Generator(device=dev).manual_seed(0), dev)}
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         sec, cores, desc = cpu_reference_step_seconds()
@@ -503,7 +511,7 @@ def run_b200(args):
                        "layers": LAYERS, "tokens_per_syrk_call": bench.tokens_per_call,
                        "l2": "inputs larger than L2 (tens of GB streamed per step)",
                        "calibration_scale": scale},
-            "phases_ms": phases, "solve_ms_per_step": solve_steps, "solve_jobs_ms": jobs, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "phases_ms": phases, "solve_ms_per_step": solve_steps, "solve_jobs_ms": jobs, "roofline": roofline, "pack_gbs": pack, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks,
             "published_reference": {"value": 745.03, "unit": "s", "note": "whole oneshot incl. model forwards, "
                                     "GPU not stated (docs/guides/big_models_and_distributed/distributed_oneshot.md:107-111)"},
@@ -513,19 +521,57 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
-def run_micro(args):
-    """Kernel-level figures on small cases (also the cases ncu captures are taken on):
-    Hessian SYRK TFLOP/s and quantize/pack GB/s against their rooflines.  One JSON line."""
+def pack_micro(steps, peaks, timed, g, dev):
+    """Quantize / pack kernels on a 16384 x 8192 bf16 matrix: GB/s of algorithmic bytes and the
+    fraction of the measured HBM copy bandwidth."""
     import torch
 
     from llm_compressor_b200 import ops
     from llm_compressor_b200.quant_args import QuantizationArgs, preset_name_to_scheme
 
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
-    peaks = load_peaks()
-    flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=dev)  # > L2 (126 MB)
-    out = {"micro": args.micro, "peaks": peaks, "results": []}
+    results = []
+    # two 256 MiB inputs used in turn: each launch reads data the previous launch evicted
+    # from L2 (126 MB); an explicit flush would leave dirty lines whose write-back would be
+    # charged to these short kernels
+    N, K = 16384, 8192
+    ws = [(torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16) for _ in range(2)]
+    turn = [0]
+
+    def nxt():
+        turn[0] ^= 1
+        return ws[turn[0]]
+    w = ws[0]
+    cases = [("rtn_int4_g128", "W4A16", 2 + 0.5 + 2 / 128), ("rtn_mxfp4", "MXFP4A16", 2 + 0.5 + 1 / 32 + 2 / 32),
+             ("rtn_mxfp8", "MXFP8A16", 2 + 1 + 1 / 32 + 2 / 32), ("rtn_fp8_channel", "FP8_DYNAMIC", 3.0)]
+    for name, preset, bpe in cases:
+        a = preset_name_to_scheme(preset, ["Linear"]).weights
+        ms = timed(lambda: ops.rtn_quantize_pack(nxt(), a), steps, do_flush=False)
+        gbs = bpe * N * K / (ms * 1e-3) / 1e9
+        results.append({"kernel": name, "N": N, "K": K, "ms": ms, "gbs": gbs, "bytes_per_elem": bpe,
+                               "frac_of_hbm_peak": gbs / peaks["hbm"]})
+    a4 = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128)
+    mn, mx = ops.observe_minmax(w, a4)
+    scale, zp = ops.qparams(mn, mx, a4)
+    ms = timed(lambda: ops.quantize_pack(nxt(), scale, zp, a4), steps, do_flush=False)
+    bpe = 2 + 0.5 + 2 / 128
+    results.append({"kernel": "pack_int4_g128_given_scale", "N": N, "K": K, "ms": ms,
+                           "gbs": bpe * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": bpe,
+                           "frac_of_hbm_peak": bpe * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
+    ms = timed(lambda: ops.observe_minmax(nxt(), a4), steps, do_flush=False)
+    results.append({"kernel": "observe_minmax_g128", "N": N, "K": K, "ms": ms,
+                           "gbs": 2.0 * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": 2.0,
+                           "frac_of_hbm_peak": 2.0 * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
+    gs = torch.tensor([1000.0], device=dev)
+    ms = timed(lambda: ops.nvfp4_quantize_pack(nxt(), gs), steps, do_flush=False)
+    bpe = 2 + 0.5 + 1 / 16 + 2 / 16
+    results.append({"kernel": "nvfp4_given_global_scale", "N": N, "K": K, "ms": ms,
+                           "gbs": bpe * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": bpe,
+                           "frac_of_hbm_peak": bpe * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
+    return results
+
+
+def make_timed(flush):
+    import torch
 
     def timed(fn, iters, do_flush=True):
         for _ in range(3):
@@ -544,6 +590,24 @@ def run_micro(args):
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1))
         return statistics.median(ts)
+    return timed
+
+
+def run_micro(args):
+    """Kernel-level figures on small cases (also the cases ncu captures are taken on):
+    Hessian SYRK TFLOP/s and quantize/pack GB/s against their rooflines.  One JSON line."""
+    import torch
+
+    from llm_compressor_b200 import ops
+    from llm_compressor_b200.quant_args import QuantizationArgs, preset_name_to_scheme
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=dev)  # > L2 (126 MB)
+    out = {"micro": args.micro, "peaks": peaks, "results": []}
+
+    timed = make_timed(flush)
 
     g = torch.Generator(device=dev).manual_seed(0)
     if args.micro in ("syrk", "all"):
@@ -556,43 +620,7 @@ def run_micro(args):
                                    "frac_of_burst_peak": tf / 1661.0 if peaks["source"] == "measured" else None})
             del x, H
     if args.micro in ("pack", "all"):
-        # two 256 MiB inputs used in turn: each launch reads data the previous launch evicted
-        # from L2 (126 MB); an explicit flush would leave dirty lines whose write-back would be
-        # charged to these short kernels
-        N, K = 16384, 8192
-        ws = [(torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16) for _ in range(2)]
-        turn = [0]
-
-        def nxt():
-            turn[0] ^= 1
-            return ws[turn[0]]
-        w = ws[0]
-        cases = [("rtn_int4_g128", "W4A16", 2 + 0.5 + 2 / 128), ("rtn_mxfp4", "MXFP4A16", 2 + 0.5 + 1 / 32 + 2 / 32),
-                 ("rtn_mxfp8", "MXFP8A16", 2 + 1 + 1 / 32 + 2 / 32), ("rtn_fp8_channel", "FP8_DYNAMIC", 3.0)]
-        for name, preset, bpe in cases:
-            a = preset_name_to_scheme(preset, ["Linear"]).weights
-            ms = timed(lambda: ops.rtn_quantize_pack(nxt(), a), args.steps, do_flush=False)
-            gbs = bpe * N * K / (ms * 1e-3) / 1e9
-            out["results"].append({"kernel": name, "N": N, "K": K, "ms": ms, "gbs": gbs, "bytes_per_elem": bpe,
-                                   "frac_of_hbm_peak": gbs / peaks["hbm"]})
-        a4 = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128)
-        mn, mx = ops.observe_minmax(w, a4)
-        scale, zp = ops.qparams(mn, mx, a4)
-        ms = timed(lambda: ops.quantize_pack(nxt(), scale, zp, a4), args.steps, do_flush=False)
-        bpe = 2 + 0.5 + 2 / 128
-        out["results"].append({"kernel": "pack_int4_g128_given_scale", "N": N, "K": K, "ms": ms,
-                               "gbs": bpe * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": bpe,
-                               "frac_of_hbm_peak": bpe * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
-        ms = timed(lambda: ops.observe_minmax(nxt(), a4), args.steps, do_flush=False)
-        out["results"].append({"kernel": "observe_minmax_g128", "N": N, "K": K, "ms": ms,
-                               "gbs": 2.0 * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": 2.0,
-                               "frac_of_hbm_peak": 2.0 * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
-        gs = torch.tensor([1000.0], device=dev)
-        ms = timed(lambda: ops.nvfp4_quantize_pack(nxt(), gs), args.steps, do_flush=False)
-        bpe = 2 + 0.5 + 1 / 16 + 2 / 16
-        out["results"].append({"kernel": "nvfp4_given_global_scale", "N": N, "K": K, "ms": ms,
-                               "gbs": bpe * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": bpe,
-                               "frac_of_hbm_peak": bpe * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
+        out["results"].extend(pack_micro(args.steps, peaks, timed, g, dev))
     if args.micro in ("factor", "all"):
         K = args.micro_k if args.micro == "factor" else 4096
         xx = torch.randn(2 * K, K, generator=g, device=dev)
@@ -625,6 +653,7 @@ def main():
                     help="CUDA streams the factorisations / sweeps of one layer are spread over")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-pack", action="store_true", help="skip the quantize/pack kernel figures")
     args = ap.parse_args()
     if args.micro:
         run_micro(args)

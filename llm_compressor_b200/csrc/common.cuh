@@ -158,7 +158,7 @@ __device__ __forceinline__ float quant_code_fast(float x, float s, float rs, flo
     // interval that contains the exact quotient settle it
     const float a = round_code(qa * (1.0f - 0x1p-20f) + zp, r);
     const float b = round_code(qa * (1.0f + 0x1p-20f) + zp, r);
-    if (a == b) return round_code(qa + zp, r);
+    if (a == b) return a;   // both ends have the sign of qa, so this is also the code's sign of zero
   }
   return quant_code<CB>(x, s, zp, r);
 }

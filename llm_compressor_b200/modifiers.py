@@ -396,9 +396,9 @@ class GPTQModifier(QuantizationMixin):
         items, rank_to, to_rank = bdist.greedy_bin_packing(groups, bdist.world_size(),
                                                            item_weight_fn=lambda g: g.H.shape[0])
         bdist.reduce_hessians(items, to_rank)
-        mine = [m for m in modules if to_rank[self._groups[m]] == bdist.rank()]
+        mod_rank = {m: to_rank[self._groups[m]] for m in modules}   # before the solve drops the groups
+        mine = [m for m in modules if mod_rank[m] == bdist.rank()]
         self.compress_module_list(mine)
-        mod_rank = {m: to_rank[self._groups[m]] for m in modules}
         bdist.broadcast_module_params(modules, mod_rank, ("weight", "weight_scale", "weight_zero_point",
                                                           "weight_g_idx", "weight_global_scale"))
         for m in modules:
