@@ -440,7 +440,7 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
     B200Q_RC(tgemm::launch(tgemm::kNT, Split{ph, pl, ldn}, Split{sb_hi, sb_lo, ldn}, C, lda, rem, (int)K, n, -1.0f,
                            1.0f, tgemm::kSkipBlockFirst, status + 2, st, k));
     B200Q_RC(tgemm::launch(tgemm::kNT, Split{ph, pl, ldn}, Split{sb_hi, sb_lo, ldn}, C, lda, rem, (int)K, n, -1.0f,
-                           1.0f, tgemm::kSkipBlockRest, status + 2, side->stream, k));
+                           1.0f, tgemm::kSkipBlockRest, status + 2, side->stream, k, kNumSMs - tgemm::side_reserve()));
     B200Q_TRY(cudaEventRecord(side->done, side->stream));
     side_busy = true;
   }

@@ -333,7 +333,7 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
       if (rest > near) {
         rc = tgemm::launch(tgemm::kNT, A, tgemm::Split{sb_hi + (int64_t)near * ld, sb_lo + (int64_t)near * ld, ld},
                            Wf + i2 + near, ldf, (int)N, rest - near, bs, -1.0f, 1.0f, tgemm::kAllTiles, gemm_status,
-                           side->stream);
+                           side->stream, 0, kNumSMs - tgemm::side_reserve());
         if (rc) return rc;
         B200Q_TRY(cudaEventRecord(side->done, side->stream));
         side_busy = true;

@@ -489,7 +489,7 @@ inline MapCache& map_cache() {
 
 // A: [M][Kd] split;  B: [N][Kd] split (K-major; [Kd][N] operands go through split_transposed).
 int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int Kd, float alpha, float beta,
-           int mask, int* status, cudaStream_t st, int mask_arg) {
+           int mask, int* status, cudaStream_t st, int mask_arg, int max_ctas) {
   if (M <= 0 || N <= 0 || Kd <= 0) return B200Q_OK;
   if (mask == kSkipBlockRest && M <= kTile) return B200Q_OK;   // a single row block has no rest
   if (Kd > 128 || (A.ld & 31) || (B.ld & 31) || A.ld < Kd || B.ld < Kd) return B200Q_ERR_ARG;
@@ -524,10 +524,20 @@ int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int
   if (beta != 0.0f && (ldc & 3) == 0 && (((uintptr_t)C) & 15) == 0 &&
       make_map(&mc_c, C, M, N, ldc, kTile))
     p.prefetch_c = 1;
-  const int grid = (int)(p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs);
+  int grid = (int)(p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs);
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   tgemm_kernel<<<grid, kThreads, kSmemBytes, st>>>(mah, mal, mbh, mbl, mc_c, p);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
+}
+
+int side_reserve() {
+  static const int r = [] {
+    const char* e = getenv("B200Q_SIDE_RESERVE");
+    int v = e ? atoi(e) : 16;   // measured best for K = 14336 among 0 / 16 / 32 / 48
+    return v < 0 ? 0 : (v > kNumSMs / 2 ? kNumSMs / 2 : v);
+  }();
+  return r;
 }
 
 SideStream* side_stream(cudaStream_t like) {
@@ -539,7 +549,7 @@ SideStream* side_stream(cudaStream_t like) {
   static int used = 0;
   static std::mutex mu;
   int dev = 0, prio = 0;
-  static const bool enabled = [] { const char* e = getenv("B200Q_LOOKAHEAD"); return e && e[0] == '1'; }();
+  static const bool enabled = [] { const char* e = getenv("B200Q_LOOKAHEAD"); return !(e && e[0] == '0'); }();
   if (!enabled) return nullptr;
   if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
   std::lock_guard<std::mutex> lock(mu);

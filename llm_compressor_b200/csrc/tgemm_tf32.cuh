@@ -32,7 +32,9 @@ int split_transposed(const float* src, int64_t ld_src, int rows, int cols, float
 // C[M,N] = beta*C + alpha * A[M,Kd] * B[N,Kd]^T with A, B given as hi/lo splits whose buffers hold
 // whole 128-row tiles (rows beyond M / N may hold anything).
 int launch(int trans, Split A, Split B, float* C, int64_t ldc, int M, int N, int Kd, float alpha, float beta,
-           int mask, int* status, cudaStream_t st, int mask_arg = 0);
+           int mask, int* status, cudaStream_t st, int mask_arg = 0, int max_ctas = 0);
+// CTAs a bulk update leaves free for the look-ahead work that runs beside it
+int side_reserve();
 
 // A helper stream of the calling host thread (same priority as `like`), with two events, for the
 // look-ahead of the blocked solves: the bulk of a rank-128 update runs there while the caller's
