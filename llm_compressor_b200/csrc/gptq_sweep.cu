@@ -8,6 +8,8 @@
 //
 // Rounding follows the reference's sequence of separate float32 operations (product, then
 // subtraction; true divisions), so that the propagated errors agree.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "tgemm_tf32.cuh"
 
@@ -284,7 +286,6 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
   const int64_t batches = (N + 31) / 32;
   int warps = (int)((batches + kNumSMs - 1) / kNumSMs);
   warps = warps < 1 ? 1 : (warps > kMaxWarps ? kMaxWarps : warps);
-  const size_t smem = sweep_smem_bytes(warps);
   void (*kern)(Params, int) = nullptr;
   if (sdtype == B200Q_BF16) kern = gscale ? sweep_block_kernel<B200Q_BF16, true> : sweep_block_kernel<B200Q_BF16, false>;
   else if (sdtype == B200Q_F32) kern = gscale ? sweep_block_kernel<B200Q_F32, true> : sweep_block_kernel<B200Q_F32, false>;
@@ -292,12 +293,27 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
   // always the largest size: host threads on other streams launch the same kernel with other sizes
   B200Q_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)sweep_smem_bytes(kMaxWarps)));
+  // With the look-ahead the far part of a trailing update runs beside the next block's sweep and
+  // leaves `reserve` SMs to it: pack the row batches into that many CTAs when they fit (a warp is
+  // latency-bound, several per SM cost little).
+  tgemm::SideStream* side = U ? tgemm::side_stream(st) : nullptr;
+  static const int kSweepReserve = [] {
+    const char* e = getenv("B200Q_SWEEP_RESERVE");
+    const int v = e ? atoi(e) : 32;
+    return v < 8 ? 8 : (v > kNumSMs / 2 ? kNumSMs / 2 : v);
+  }();
+  int reserve = tgemm::side_reserve();
+  if (side && batches <= (int64_t)kSweepReserve * kMaxWarps) {
+    reserve = kSweepReserve;
+    const int w = (int)((batches + reserve - 1) / reserve);
+    if (w > warps) warps = w;
+  }
   int64_t ctas = (batches + warps - 1) / warps;
   const int grid = (int)(ctas < 2 * kNumSMs ? ctas : 2 * kNumSMs);
+  const size_t smem = sweep_smem_bytes(warps);
   // Look-ahead: the trailing update of a block is split in the next 128 columns (which the next
   // block's sweep reads; caller's stream) and the columns after them, which a helper stream
   // updates while the next block is swept.
-  tgemm::SideStream* side = U ? tgemm::side_stream(st) : nullptr;
   bool side_busy = false;
   int blk = 0;
   for (int64_t i1 = 0; i1 < K; i1 += blocksize, ++blk) {
@@ -333,7 +349,7 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
       if (rest > near) {
         rc = tgemm::launch(tgemm::kNT, A, tgemm::Split{sb_hi + (int64_t)near * ld, sb_lo + (int64_t)near * ld, ld},
                            Wf + i2 + near, ldf, (int)N, rest - near, bs, -1.0f, 1.0f, tgemm::kAllTiles, gemm_status,
-                           side->stream, 0, kNumSMs - tgemm::side_reserve());
+                           side->stream, 0, kNumSMs - reserve);
         if (rc) return rc;
         B200Q_TRY(cudaEventRecord(side->done, side->stream));
         side_busy = true;
