@@ -138,13 +138,15 @@ def test_gptq_golden(golden, name):
 
 
 @pytest.mark.parametrize("N,K,scheme", [(256, 1024, "W4A16"), (96, 640, "W4A16"), (128, 512, "FP8_DYNAMIC"),
-                                        (64, 512, "NVFP4A16")])
+                                        (64, 512, "NVFP4A16"), (40, 2176, "W4A16"), (300, 1152, "MXFP4A16"),
+                                        (48, 5632, "W4A16")])
 def test_gptq_vs_oracle_larger(N, K, scheme):
     spec = oracle.preset(scheme)
     args = args_from({k: getattr(spec, k) for k in ("num_bits", "type", "symmetric", "strategy", "group_size",
                                                      "scale_dtype", "zp_dtype")})
     w = synth_weight(N, K, seed=N + K)
-    x = synth_acts(8, K // 2, K, seed=3)
+    S = min(K // 2, 512)
+    x = synth_acts(max(8, -(-3 * K // (2 * S))), S, K, seed=3)   # at least 1.5 K tokens: H well conditioned
     H, n = oracle.accumulate_hessian(x, oracle.make_empty_hessian(K), 0)
     Hn = H / n
     loss_ref, ref = oracle.quantize_weight(w, spec, Hn.clone())
