@@ -106,6 +106,13 @@ def cpu_reference_step_seconds(sample_scale: float = 1.0):
     import oracle
 
     torch.manual_seed(0)
+    # all host cores this process may use (torchrun presets OMP_NUM_THREADS=1 for its workers)
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    if torch.get_num_threads() < avail:
+        torch.set_num_threads(avail)
     cores = torch.get_num_threads()
     spec = oracle.preset("W4A16")
     t_h = {}
