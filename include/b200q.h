@@ -183,7 +183,9 @@ int b200q_nvfp4_quantize_pack(const void* W, int wdtype, int64_t N, int64_t K, i
  * Only tiles on or below the diagonal are written; b200q_hessian_finalize mirrors them.
  * Replaces accumulate_hessian (src/modifiers/gptq/gptq_quantize.py:28-64; alpha = 2).
  * Requires K % 8 == 0 and 16-byte aligned X, ldx % 8 == 0.  `status` (device int, may be
- * NULL) receives non-zero if a bounded wait inside the kernel expired. */
+ * NULL) receives non-zero if a bounded wait inside the kernel expired.  Launches clusters of
+ * two CTAs (tcgen05.mma.cta_group::2); B200Q_SYRK_SINGLE_CTA=1 in the environment selects the
+ * single-CTA kernel. */
 int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* H, int64_t ldh,
                        float alpha, int* status, void* stream);
 
@@ -223,7 +225,14 @@ int b200q_gptq_zero_dead_columns(const float* diag, int64_t diag_stride, int64_t
  * caller; status[0] is set to B200Q_NOT_POSITIVE_DEFINITE (status[1] to the first bad column
  * + 1) if a pivot is <= 0, status[2] to B200Q_ERR_DEVICE if a bounded wait expired; the
  * caller then takes the reference's identity fallback (:157-164).  workspace:
- * b200q_gptq_factor_workspace_bytes(K) bytes. */
+ * b200q_gptq_factor_workspace_bytes(K) bytes.
+ *
+ * Streams: all work is ordered on `stream`.  Unless the environment has B200Q_LOOKAHEAD=0, the
+ * bulk of each rank-128 update is launched on a helper stream that the library creates once per
+ * (device, `stream`) and keeps; it is forked from and joined to `stream` with events before the
+ * call returns, so callers see ordinary stream semantics (b200q_gptq_sweep does the same).  The
+ * helper streams and the per-thread cache of TMA descriptors are the library's only hidden
+ * state; they hold no device memory. */
 size_t b200q_gptq_factor_workspace_bytes(int64_t K);
 int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* status,
                       void* stream);
