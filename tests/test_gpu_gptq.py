@@ -4,12 +4,15 @@
 Tolerances are the ones the path is specified with: Hessians within 1e-3 relative Frobenius
 norm; GPTQ: at least 99.5 % identical values of the fake-quantised weight (one value per integer
 code), scales identical, per-layer loss within 1 %."""
+import os
+
 import pytest
 import torch
 
 import oracle
 from helpers import args_from, bits_equal, mismatch, synth_acts, synth_weight
 from llm_compressor_b200 import gptq, observers, ops
+from llm_compressor_b200.quant_args import QuantizationArgs
 from test_oracle_golden import spec_from
 
 pytestmark = pytest.mark.gpu
@@ -253,3 +256,41 @@ def test_gemm_tf32x3_lower_tiles_only():
                 assert float((blk - r).norm() / r.norm()) < 3e-6
             else:
                 assert float(blk.abs().max()) == 0.0
+
+
+def _solve_fingerprint(K, N, out_path=None):
+    """Factor a seeded Hessian and sweep a seeded weight on the GPU; returns (U, Wq) on the CPU."""
+    g = torch.Generator(device=DEV).manual_seed(K)
+    X = torch.randn(3 * K, K, generator=g, device=DEV) * (0.25 + 2 * torch.rand(K, generator=g, device=DEV))
+    H = (X.t() @ X) / X.shape[0]
+    H += 0.01 * H.diagonal().mean() * torch.eye(K, device=DEV)
+    assert ops.gptq_factor(H) == 0
+    a = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128)
+    W = (torch.randn(N, K, generator=g, device=DEV) * 0.02)
+    mn, mx = ops.observe_minmax(W.to(torch.bfloat16), a)
+    scale, zp = ops.qparams(mn, mx, a)
+    Wq = W.clone()
+    losses = ops.gptq_sweep(Wq, H, scale, zp, a)
+    res = (H.cpu(), Wq.cpu(), losses.cpu())
+    if out_path:
+        torch.save(res, out_path)
+    return res
+
+
+def test_lookahead_is_bitwise_equal_to_single_stream(tmp_path):
+    """The helper-stream look-ahead of the factorisation and the sweep reorders launches, not
+    arithmetic: results must be bit-identical to a run with B200Q_LOOKAHEAD=0 (the switch is read
+    once per process, hence the child process)."""
+    import subprocess
+    import sys
+    K, N = 4096, 1024
+    out = tmp_path / "ref.pt"
+    env = dict(os.environ, B200Q_LOOKAHEAD="0")
+    code = ("import sys; sys.path.insert(0, %r); sys.path.insert(0, %r); import test_gpu_gptq as t; "
+            "t._solve_fingerprint(%d, %d, %r)" % (os.path.dirname(__file__), os.path.dirname(os.path.dirname(__file__)),
+                                                   K, N, str(out)))
+    subprocess.run([sys.executable, "-c", code], check=True, env=env, timeout=300)
+    U0, W0, L0 = torch.load(out)
+    for _ in range(3):
+        U1, W1, L1 = _solve_fingerprint(K, N)
+        assert torch.equal(U0, U1) and torch.equal(W0, W1) and torch.equal(L0, L1)
