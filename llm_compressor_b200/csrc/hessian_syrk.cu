@@ -687,16 +687,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  // function-local static: initialised once, thread-safely (several host threads start solving at
+  // the same moment)
+  static const EncodeTiledFn fn = [] {
     void* sym = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
         qres == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)sym;
-  }
+      return (EncodeTiledFn)sym;
+    return (EncodeTiledFn) nullptr;
+  }();
   return fn;
 }
 

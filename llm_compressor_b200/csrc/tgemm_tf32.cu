@@ -1,19 +1,22 @@
 // fp32-accurate tile GEMM on the tensor cores (tcgen05, kind::tf32, "3xTF32").
 //
-//   C[M,N] = beta * C + alpha * A[M,Kd] * op(B),   Kd <= 128 (the GPTQ block width)
-//       op(B) = B[N,Kd]^T  (kNT, B K-major)      op(B) = B[Kd,N]  (kNN, B MN-major)
+//   C[M,N] = beta * C + alpha * A[M,Kd] * B[N,Kd]^T,   Kd <= 128 (the GPTQ block width)
 //
 // Each float32 operand x is given as two tf32-exact arrays hi = tf32(x), lo = tf32(x - hi)
-// (split_kernel); every k-step issues three MMAs into one TMEM accumulator,
-// hi*hi + hi*lo + lo*hi, which keeps ~22 significant bits per product with float32
-// accumulation: as accurate as the SIMT float32 GEMM it replaces for the factorisation and the
-// sweep's trailing updates, at tensor-core speed.
+// (split_kernel; split_transposed_kernel for an operand stored [Kd][N]); every k-step issues three
+// MMAs into one TMEM accumulator, hi*hi + hi*lo + lo*hi, which keeps ~22 significant bits per
+// product with float32 accumulation: as accurate as the SIMT float32 GEMM it replaces for the
+// factorisation and the sweep's trailing updates, at tensor-core speed.
 //
-// Structure as in the Hessian kernel: persistent CTAs (one per SM), warp 0 = TMA producer
-// (3-stage ring, one stage = a 32-deep k-chunk of A_hi, A_lo, B_hi, B_lo, 128-byte swizzle),
-// warp 1 = MMA issuer + TMEM owner (two 128-column accumulators), warps 2-5 = epilogue
-// (tcgen05.ld, alpha/beta, bounds, optional lower-block-triangle tile set).  All mbarrier waits
-// are bounded; no cluster launch, no multicast.
+// Structure: persistent CTAs, each with a contiguous range of the row-major tile list.  Warp 0 =
+// TMA producer: the A operand of a block row (all k-chunks, hi and lo, 128 KiB) is loaded once and
+// stays in shared memory while the tiles of that row are computed; B chunks (hi, lo of 32 k-values,
+// 32 KiB) stream through a two-stage ring; the C tile is prefetched into L2.  Warp 1 = MMA issuer
+// and TMEM owner (two 128-column accumulators).  Warps 2-9 = epilogue: the loads of the old C
+// values are issued before the wait for the accumulator, tcgen05.ld, a transpose through a
+// per-warp shared-memory tile so that every global access is a row-contiguous float4, alpha /
+// beta, bounds.  Tile sets: all, lower block triangle, and the sets of the one-pass factorisation
+// (see tgemm_tf32.cuh).  All mbarrier waits are bounded; no cluster launch, no multicast.
 #include <cuda.h>
 
 #include <cstdlib>
@@ -27,12 +30,16 @@ namespace tgemm {
 
 constexpr int kTile = 128;          // output tile is 128 x 128
 constexpr int kChunkK = 32;         // fp32 elements per 128-byte row
-constexpr int kStages = 3;
-constexpr int kOpBytes = kTile * kChunkK * 4;    // one operand part of one stage: 16 KiB
-constexpr int kStageBytes = 4 * kOpBytes;        // A_hi, A_lo, B_hi, B_lo: 64 KiB
-constexpr int kEpiBytes = 4 * 32 * 33 * 4;        // per-warp staging tiles of the epilogue
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kEpiBytes;
-constexpr int kThreads = 192;
+constexpr int kOpBytes = kTile * kChunkK * 4;    // one hi or lo part of one 32-deep k-chunk: 16 KiB
+constexpr int kMaxChunks = 4;                     // Kd <= 128
+constexpr int kABytes = kMaxChunks * 2 * kOpBytes;   // resident A operand: 4 chunks x (hi, lo) = 128 KiB
+constexpr int kStages = 2;                        // ring of B chunks
+constexpr int kStageBytes = 2 * kOpBytes;         // B_hi, B_lo of one chunk: 32 KiB
+constexpr int kEpiWarps = 8;                      // two warps per TMEM lane quarter, two column chunks each
+constexpr int kEpiBytes = kEpiWarps * 32 * 33 * 4;   // per-warp staging tiles of the epilogue
+constexpr int kOperandBytes = kABytes + kStages * kStageBytes;
+constexpr int kSmemBytes = kOperandBytes + 1024 + 256 + kEpiBytes;
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kTmemCols = 256;
 constexpr long long kWaitCycles = 4000000000LL;
 
@@ -170,19 +177,22 @@ tgemm_kernel(const __grid_constant__ CUtensorMap a_hi, const __grid_constant__ C
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* aligned = smem_raw + (base - raw);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + kStages * kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + kOperandBytes);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
   auto accf_bar = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
   auto acce_bar = [&](int b) { return bar0 + 8u * (2 * kStages + 2 + b); };
+  const uint32_t afull_bar = bar0 + 8u * (2 * kStages + 4), aempty_bar = bar0 + 8u * (2 * kStages + 5);
+  const uint32_t b_base = base + kABytes;   // ring of B chunks behind the resident A operand
   __shared__ uint32_t s_tmem_base;
   __shared__ volatile int s_abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), kEpiWarps); }
+    mbar_init(afull_bar, 1); mbar_init(aempty_bar, 1);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -196,14 +206,19 @@ tgemm_kernel(const __grid_constant__ CUtensorMap a_hi, const __grid_constant__ C
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = s_tmem_base;
   const int chunks = (p.Kd + kChunkK - 1) / kChunkK;
-  const bool nn = (p.trans == kNN);
+  // Every CTA takes a contiguous range of the tile list.  The list is row-major, so consecutive
+  // tiles of a CTA mostly share their block row: the A operand of a block row (all k-chunks, hi
+  // and lo) is loaded once and stays in shared memory while only B chunks stream through the ring.
+  const int64_t t_begin = p.num_tiles * blockIdx.x / gridDim.x;
+  const int64_t t_end = p.num_tiles * (blockIdx.x + 1) / gridDim.x;
 
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0;
-      uint32_t phase = 0;
+      uint32_t phase = 0, a_par = 0;
+      int cur_tm = -1;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      for (int64_t t = t_begin; t < t_end && ok; ++t) {
         int tm, tn;
         tile_from_index(p, t, tm, tn);
         if (p.prefetch_c) {
@@ -214,65 +229,71 @@ tgemm_kernel(const __grid_constant__ CUtensorMap a_hi, const __grid_constant__ C
             asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(&c_map),
                          "r"(tn * kTile + q * 32), "r"(tm * kTile) : "memory");
         }
+        if (tm != cur_tm) {
+          if (cur_tm >= 0) {   // the MMAs of the previous block row have read A
+            if (!mbar_wait(aempty_bar, a_par, &s_abort)) { ok = false; break; }
+            a_par ^= 1u;
+          }
+          cur_tm = tm;
+          mbar_expect_tx(afull_bar, (uint32_t)(chunks * 2 * kOpBytes));
+          for (int c = 0; c < chunks; ++c) {
+            // A parts: box [32 k][128 rows] at (k, row)
+            tma_load_2d(base + (c * 2) * kOpBytes, &a_hi, afull_bar, c * kChunkK, tm * kTile);
+            tma_load_2d(base + (c * 2 + 1) * kOpBytes, &a_lo, afull_bar, c * kChunkK, tm * kTile);
+          }
+        }
         for (int c = 0; c < chunks; ++c) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, &s_abort)) { ok = false; break; }
           mbar_expect_tx(full_bar(stage), kStageBytes);
-          const uint32_t sa = base + stage * kStageBytes;
-          // A parts: box [32 k][128 rows] at (k, row)
-          tma_load_2d(sa, &a_hi, full_bar(stage), c * kChunkK, tm * kTile);
-          tma_load_2d(sa + kOpBytes, &a_lo, full_bar(stage), c * kChunkK, tm * kTile);
-          if (!nn) {
-            tma_load_2d(sa + 2 * kOpBytes, &b_hi, full_bar(stage), c * kChunkK, tn * kTile);
-            tma_load_2d(sa + 3 * kOpBytes, &b_lo, full_bar(stage), c * kChunkK, tn * kTile);
-          } else {
-            // B is [Kd][N]: four boxes of [32 n][32 k] per part, 4 KiB each, n-chunk major
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              tma_load_2d(sa + 2 * kOpBytes + q * 4096, &b_hi, full_bar(stage), tn * kTile + q * 32, c * kChunkK);
-              tma_load_2d(sa + 3 * kOpBytes + q * 4096, &b_lo, full_bar(stage), tn * kTile + q * 32, c * kChunkK);
-            }
-          }
+          const uint32_t sb = b_base + stage * kStageBytes;
+          tma_load_2d(sb, &b_hi, full_bar(stage), c * kChunkK, tn * kTile);
+          tma_load_2d(sb + kOpBytes, &b_lo, full_bar(stage), c * kChunkK, tn * kTile);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     int stage = 0;
-    uint32_t phase = 0;
-    int local = 0;
+    uint32_t phase = 0, a_par = 0;
+    int local = 0, cur_tm = -1;
     bool ok = true;
-    const uint32_t idesc = instr_desc(nn);
-    for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, ++local) {
+    const uint32_t idesc = instr_desc(false);
+    for (int64_t t = t_begin; t < t_end && ok; ++t, ++local) {
+      int tm, tn, next_tm = -1, next_tn;
+      tile_from_index(p, t, tm, tn);
+      if (t + 1 < t_end) tile_from_index(p, t + 1, next_tm, next_tn);
       const int buf = local & 1;
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       if (!mbar_wait(acce_bar(buf), acc_phase ^ 1u, &s_abort)) { ok = false; break; }
+      if (tm != cur_tm) {
+        if (!mbar_wait(afull_bar, a_par, &s_abort)) { ok = false; break; }
+        a_par ^= 1u;
+        cur_tm = tm;
+      }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kTile);
       for (int c = 0; c < chunks; ++c) {
         if (!mbar_wait(full_bar(stage), phase, &s_abort)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (lane == 0) {
-          const uint32_t sa = base + stage * kStageBytes;
+          const uint32_t sa = base + (c * 2) * kOpBytes;
+          const uint32_t sb = b_base + stage * kStageBytes;
 #pragma unroll
           for (int kk = 0; kk < kChunkK / 8; ++kk) {
             // K-major, 128-byte rows: 8-row groups 1024 bytes apart; a k-step of 8 tf32 is 32 bytes
             const uint64_t ah = make_desc(sa + kk * 32, 16, 1024);
             const uint64_t al = make_desc(sa + kOpBytes + kk * 32, 16, 1024);
-            uint64_t bh, bl;
-            if (!nn) {
-              bh = make_desc(sa + 2 * kOpBytes + kk * 32, 16, 1024);
-              bl = make_desc(sa + 3 * kOpBytes + kk * 32, 16, 1024);
-            } else {
-              // MN-major: 32-column chunks 4096 bytes apart, one 8-row k group (1024 bytes) per step
-              bh = make_desc(sa + 2 * kOpBytes + kk * 1024, 4096, 1024);
-              bl = make_desc(sa + 3 * kOpBytes + kk * 1024, 4096, 1024);
-            }
+            const uint64_t bh = make_desc(sb + kk * 32, 16, 1024);
+            const uint64_t bl = make_desc(sb + kOpBytes + kk * 32, 16, 1024);
             mma_tf32(d_tmem, ah, bh, idesc, (c | kk) ? 1u : 0u);
             mma_tf32(d_tmem, ah, bl, idesc, 1u);
             mma_tf32(d_tmem, al, bh, idesc, 1u);
           }
           tc_commit(empty_bar(stage));
-          if (c == chunks - 1) tc_commit(accf_bar(buf));
+          if (c == chunks - 1) {
+            tc_commit(accf_bar(buf));
+            if (next_tm >= 0 && next_tm != tm) tc_commit(aempty_bar);   // A may be replaced
+          }
         }
         __syncwarp();
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -285,18 +306,37 @@ tgemm_kernel(const __grid_constant__ CUtensorMap a_hi, const __grid_constant__ C
     const bool vec = ((p.ldc & 3) == 0) && ((((uintptr_t)p.C) & 15) == 0);
     // per-warp staging tile [32 rows][33]: accumulator rows come out of TMEM one row per lane;
     // going through shared memory lets every global access cover whole 128-byte row segments
-    float* stage = reinterpret_cast<float*>(aligned + kStages * kStageBytes + 256) + (warp - 2) * (32 * 33);
+    float* stage = reinterpret_cast<float*>(aligned + kOperandBytes + 256) + (warp - 2) * (32 * 33);
     const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;  // 4 rows x 8 float4 per instruction
-    for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, ++local) {
+    for (int64_t t = t_begin; t < t_end && ok; ++t, ++local) {
       int tm, tn;
       tile_from_index(p, t, tm, tn);
       const int buf = local & 1;
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      const int row0 = tm * kTile + q * 32;
+      // warps 2-5 take column chunks 0 and 1, warps 6-9 chunks 2 and 3
+      const int c_first = (warp - 2) >= 4 ? 2 : 0;
+      // the old values of C do not depend on the accumulator: their loads go out before the wait
+      // for the MMAs, so that memory latency and tensor-core time overlap
+      float4 h[2][8];
+      bool fast[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int col0 = tn * kTile + (c_first + k) * 32;
+        fast[k] = vec && col0 + 31 < p.N;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = row0 + i * 4 + sub_row;
+          h[k][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (fast[k] && p.beta != 0.0f && row < p.M)
+            h[k][i] = *reinterpret_cast<const float4*>(p.C + (int64_t)row * p.ldc + col0 + sub_col);
+        }
+      }
       if (!mbar_wait(accf_bar(buf), acc_phase, &s_abort)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row0 = tm * kTile + q * 32;
-#pragma unroll 1
-      for (int c = 0; c < kTile / 32; ++c) {
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int c = c_first + k;
         const int col0 = tn * kTile + c * 32;
         if (col0 >= p.N) break;
         uint32_t r[32];
@@ -306,23 +346,15 @@ tgemm_kernel(const __grid_constant__ CUtensorMap a_hi, const __grid_constant__ C
         for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]) * p.alpha;
         __syncwarp();
         const int cc = col0 + sub_col;
-        if (vec && col0 + 31 < p.N) {
-          float4 h[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int row = row0 + i * 4 + sub_row;
-            h[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (p.beta != 0.0f && row < p.M)
-              h[i] = *reinterpret_cast<const float4*>(p.C + (int64_t)row * p.ldc + cc);
-          }
+        if (fast[k]) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int lr = i * 4 + sub_row, row = row0 + lr;
             if (row < p.M) {
               const float* sp = stage + lr * 33 + sub_col;
               float4 o;
-              o.x = p.beta * h[i].x + sp[0]; o.y = p.beta * h[i].y + sp[1];
-              o.z = p.beta * h[i].z + sp[2]; o.w = p.beta * h[i].w + sp[3];
+              o.x = p.beta * h[k][i].x + sp[0]; o.y = p.beta * h[k][i].y + sp[1];
+              o.z = p.beta * h[k][i].z + sp[2]; o.w = p.beta * h[k][i].w + sp[3];
               *reinterpret_cast<float4*>(p.C + (int64_t)row * p.ldc + cc) = o;
             }
           }
@@ -415,16 +447,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 inline EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  // function-local static: initialised once, thread-safely (several host threads start solving at
+  // the same moment)
+  static const EncodeTiledFn fn = [] {
     void* sym = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
         qres == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)sym;
-  }
+      return (EncodeTiledFn)sym;
+    return (EncodeTiledFn) nullptr;
+  }();
   return fn;
 }
 // fp32 matrix [rows][cols] (cols contiguous, ld elements per row), boxes of [box_rows][32 cols]
