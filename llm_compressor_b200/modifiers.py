@@ -299,7 +299,7 @@ class GPTQModifier(QuantizationMixin):
 
     def __init__(self, block_size: int = 128, dampening_frac: Optional[float] = 0.01,
                  actorder: Any = _UNSET, offload_hessians: bool = False, share_hessians: bool = True,
-                 parallel_streams: int = 4, hessian_stage_tokens: int = 16384, **quant_kwargs):
+                 parallel_streams: int = 4, hessian_stage_tokens: int = 32768, **quant_kwargs):
         kw = dict(quant_kwargs)
         kw.setdefault("targets", "Linear")
         super().__init__(**kw)
@@ -492,7 +492,7 @@ class _HessianGroup:
     Small calibration batches are gathered in a bf16 staging buffer and added with one kernel
     call per ``stage_tokens`` tokens: the symmetric rank-k update re-reads and re-writes the lower
     triangle of H on every call and fills the machine in whole waves of 256x256 tiles, so a call
-    over 2048 tokens runs at about half the rate of a call over 16384 (K = 4096)."""
+    over 2048 tokens runs at about half the rate of a call over 32768 (K = 4096)."""
 
     def __init__(self, module, offload=False, stage_tokens: int = 0):
         self.members = [module]
