@@ -177,3 +177,70 @@ def test_rejects_cpu_tensors():
     args = args_from(dict(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128))
     with pytest.raises(B200QError):
         ops.observe_minmax(torch.zeros(4, 128, dtype=torch.bfloat16), args)
+
+
+@pytest.mark.parametrize("name", ["w4a16_g128", "w4a16_g32", "w4a16_asym_g128", "w8_g128", "w8a16_channel", "w4_channel",
+                                  "fp8_channel", "mxfp4", "mxfp8"])
+@pytest.mark.parametrize("seed", [0, 1])
+def test_fused_rtn_on_rounding_boundaries(golden, name, seed):
+    """Weights placed on (and one bf16 step beside) the rounding boundaries of the code grid: the
+    reciprocal-multiply fast paths must fall back to the exact division wherever it matters."""
+    args = args_from(golden["ct_cases"][name]["args"])
+    spec = spec_from(golden["ct_cases"][name]["args"])
+    g = torch.Generator().manual_seed(100 + seed)
+    N, K = 64, 1024
+    base = torch.rand(N, 1, generator=g) * 0.05 + 1e-3                      # per-row magnitude
+    steps = torch.randint(-31, 32, (N, K), generator=g).float() * 0.5       # multiples of half a code step
+    w = (steps * base / 7.5).to(torch.bfloat16)
+    # neighbours one bf16 ulp up / down on a third of the entries each
+    bits = w.view(torch.int16).clone()
+    sel = torch.randint(0, 3, (N, K), generator=g) * (w != 0)               # zeros stay zeros (no NaN patterns)
+    bits = torch.where(sel == 1, bits + 1, torch.where(sel == 2, bits - 1, bits))
+    w = bits.view(torch.bfloat16).clone()
+    assert bool(torch.isfinite(w.float()).all())
+    w[:, 0] = (base[:, 0] * 2.0).to(torch.bfloat16)                         # a row maximum that fixes the scale
+    w[0, 5] = -0.0
+    w[1, 7] = 0.0
+    o = oracle.WeightObserver(spec)
+    oqp = o(w).get_qparams()
+    ref = oracle.compress_weight({"weight": w, "weight_scale": oqp["scale"].to(w.dtype),
+                                  "weight_zero_point": oqp["zero_point"]}, spec)
+    r = ops.rtn_quantize_pack(w.to(DEV), args)
+    assert bits_equal(r["scale"], oqp["scale"].to(w.dtype))
+    assert bits_equal(r["zero_point"], oqp["zero_point"])
+    if "weight_packed" in ref:
+        assert bits_equal(r["codes"], ref["weight_packed"]), mismatch(r["codes"], ref["weight_packed"])
+    else:
+        exp = ref["weight"]
+        if exp.dtype == torch.int8:
+            exp = oracle.pack_int32(exp, 8)
+        assert bits_equal(r["codes"], exp), mismatch(r["codes"], exp)
+    # the unfused path (observer -> qparams -> quantize_pack) on the same data
+    mn, mx = ops.observe_minmax(w.to(DEV), args)
+    scale, zp = ops.qparams(mn, mx, args)
+    packed = ops.quantize_pack(w.to(DEV), scale, zp, args, pack_int8=True)
+    a, b = packed.contiguous().view(torch.uint8).flatten(), r["codes"].contiguous().view(torch.uint8).flatten()
+    assert a.numel() == b.numel() and torch.equal(a, b)
+
+
+def test_nvfp4_on_rounding_boundaries():
+    spec = oracle.preset("NVFP4A16")
+    g = torch.Generator().manual_seed(7)
+    N, K = 64, 1024
+    grid = torch.tensor([0.0, 0.25, 0.5, 0.75, 1.0, 1.25, 1.5, 1.75, 2.0, 2.5, 3.0, 3.5, 4.0, 5.0, 6.0])
+    idx = torch.randint(0, len(grid), (N, K), generator=g)
+    sign = torch.randint(0, 2, (N, K), generator=g).float() * 2 - 1
+    blk = (torch.rand(N, K // 16, generator=g) * 0.04 + 1e-3).repeat_interleave(16, dim=1)
+    w = (grid[idx] * sign * blk / 6.0).to(torch.bfloat16)
+    bits = w.view(torch.int16).clone()
+    sel = torch.randint(0, 3, (N, K), generator=g) * (w != 0)
+    w = torch.where(sel == 1, bits + 1, torch.where(sel == 2, bits - 1, bits)).view(torch.bfloat16).clone()
+    assert bool(torch.isfinite(w.float()).all())
+    w[:, ::16] = blk[:, ::16].to(torch.bfloat16)          # block maxima
+    o = oracle.WeightObserver(spec)
+    oqp = o(w).get_qparams()
+    ref = oracle.compress_weight({"weight": w, "weight_scale": oqp["scale"], "weight_zero_point": oqp["zero_point"],
+                                  "weight_global_scale": oqp["global_scale"]}, spec)
+    r = ops.nvfp4_quantize_pack(w.to(DEV), oqp["global_scale"].to(DEV))
+    assert bits_equal(r["codes"], ref["weight_packed"]), mismatch(r["codes"], ref["weight_packed"])
+    assert bits_equal(r["scale_store"], ref["weight_scale"])
