@@ -130,6 +130,129 @@ __global__ void __launch_bounds__(256) mse_group_kernel(const void* __restrict__
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// bf16 weights, integer codes, GROUP strategies: the same search with packed bf16x2 arithmetic.
+// torch evaluates the candidate with element-wise bf16 ops; for bf16 operands a packed
+// HADD2 / HMUL2 gives exactly the rounded result of the float32 operation followed by a
+// rounding to bf16 (the _rn forms of the intrinsics: the plain ones let the compiler fuse the
+// product and the subtraction into one FMA with a single rounding), so add-zero-point, clamp, round-to-integer (magic number 192 for 4 bits,
+// h2rint otherwise), dequantise, subtract and abs run two elements per instruction.  The two
+// places where float32 is needed keep an exact fallback: the quotient x/s is formed as x*(1/s)
+// and the power as exp2(norm*log2 d); a lane whose value lies within a few float ulps of a bf16
+// rounding midpoint (3 ulps for the quotient, 192 for the power, twice the error bound of the
+// MUFU functions at these magnitudes) recomputes that element with the IEEE division / powf.
+__device__ __forceinline__ uint32_t bf2_of(float v) {
+  __nv_bfloat162 r = __float2bfloat162_rn(v);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf2_pack(float hi, float lo) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+#define B200Q_BF2(op, a, b) ([&] { __nv_bfloat162 r_ = op(*reinterpret_cast<const __nv_bfloat162*>(&(a)), \
+                                                         *reinterpret_cast<const __nv_bfloat162*>(&(b)));   \
+                                   return *reinterpret_cast<uint32_t*>(&r_); }())
+
+template <bool FOUR_BIT>
+__global__ void __launch_bounds__(256) mse_group_bf16_int_kernel(const void* __restrict__ W, int64_t N, int64_t K,
+                                                                 int64_t ldw, int g, Cfg c, int* __restrict__ ctl,
+                                                                 int pass, void* __restrict__ mn_out,
+                                                                 void* __restrict__ mx_out) {
+  using T = __nv_bfloat16;
+  __shared__ float s_shrink[1024];
+  const int limit = (pass == 0) ? c.steps : ctl[0];
+  if (pass == 1 && limit >= c.steps) return;  // the search never stopped early
+  for (int i = threadIdx.x; i < limit; i += blockDim.x) s_shrink[i] = shrink_factor(i, c.grid);
+  __syncthreads();
+  const int lanes = g >> 3;
+  const int64_t cpr = K >> 3, total = N * cpr, gpr = K / g;
+  const QRange qr{c.qmin, c.qmax, c.kind};
+  const uint32_t qmin2 = bf2_of(c.qmin), qmax2 = bf2_of(c.qmax), magic = 0x43404340u;  // {192, 192}
+  for (int64_t ch = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; ch < ((total + 31) & ~31LL);
+       ch += (int64_t)gridDim.x * blockDim.x) {
+    const bool live = ch < total;
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+    float lo = INFINITY, hi = -INFINITY;
+    int64_t row = 0, cc = 0;
+    if (live) {
+      row = ch / cpr; cc = ch - row * cpr;
+      const uint4 raw = *reinterpret_cast<const uint4*>((const T*)W + row * ldw + cc * 8);
+      w[0] = raw.x; w[1] = raw.y; w[2] = raw.z; w[3] = raw.w;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float a = __uint_as_float(w[k] << 16), b = __uint_as_float(w[k] & 0xFFFF0000u);
+        lo = fminf(lo, fminf(a, b)); hi = fmaxf(hi, fmaxf(a, b));
+      }
+    }
+    for (int o = lanes >> 1; o > 0; o >>= 1) {
+      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    const float mn = bf16r(lo * c.expand), mx = bf16r(hi * c.expand);
+    float best_err = 3.3895313892515355e38f;  // finfo(bfloat16).max
+    float best_mn = mn, best_mx = mx;
+    for (int i = 0; i < limit; ++i) {
+      const float p = s_shrink[i];
+      const float smn = bf16r(mn * p), smx = bf16r(mx * p);
+      float s, z;
+      qparams_local<true>(smn, smx, c, s, z);
+      const float rs = __frcp_rn(s);
+      const uint32_t s2 = bf2_of(s), z2 = bf2_of(z);
+      float err = 0.0f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float x0 = __uint_as_float(w[k] << 16), x1 = __uint_as_float(w[k] & 0xFFFF0000u);
+        const float q0 = x0 * rs, q1 = x1 * rs;
+        // quotients within 3 ulps of a bf16 midpoint (half-word 0x8000) take the IEEE division
+        const uint32_t mq = (__byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x5410) + 0x80048004u) & 0xFFF0FFF0u;
+        uint32_t cq = bf2_pack(q1, q0);
+        if (((mq & 0xFFFFu) == 0u) || ((mq >> 16) == 0u))
+          cq = bf2_pack(bf16r(__fdiv_rn(x1, s)), bf16r(__fdiv_rn(x0, s)));
+        uint32_t v = c.symmetric ? cq : B200Q_BF2(__hadd2_rn, cq, z2);
+        v = B200Q_BF2(__hmax2, v, qmin2);
+        v = B200Q_BF2(__hmin2, v, qmax2);
+        if (FOUR_BIT) {
+          v = B200Q_BF2(__hadd2_rn, v, magic);   // integers are 1 apart in [128, 256): rounds to nearest even
+          v = B200Q_BF2(__hsub2_rn, v, magic);
+        } else {
+          __nv_bfloat162 r_ = h2rint(*reinterpret_cast<const __nv_bfloat162*>(&v));
+          v = *reinterpret_cast<uint32_t*>(&r_);
+        }
+        if (!c.symmetric) v = B200Q_BF2(__hsub2_rn, v, z2);
+        v = B200Q_BF2(__hmul2_rn, v, s2);
+        v = B200Q_BF2(__hsub2_rn, v, w[k]);
+        v &= 0x7FFF7FFFu;   // |.|
+        const float d0 = __uint_as_float(v << 16), d1 = __uint_as_float(v & 0xFFFF0000u);
+        float e0 = exp2f(c.norm * __log2f(d0)), e1 = exp2f(c.norm * __log2f(d1));
+        e0 = (d0 == 0.0f) ? 0.0f : e0;
+        e1 = (d1 == 0.0f) ? 0.0f : e1;
+        // powers within 192 ulps of a bf16 midpoint, or outside the range where the MUFU error
+        // bounds hold, are recomputed with powf
+        const uint32_t l0 = __float_as_uint(e0) & 0xFFFFu, l1 = __float_as_uint(e1) & 0xFFFFu;
+        // (|log2 d| <= 20 keeps the error of norm * log2 d below 80 ulps of the result)
+        if ((d0 != 0.0f) && (((l0 - 0x7F40u) & 0xFFFFu) <= 0x180u || !(d0 > 9.6e-7f && d0 < 1.0e6f))) e0 = powf(d0, c.norm);
+        if ((d1 != 0.0f) && (((l1 - 0x7F40u) & 0xFFFFu) <= 0x180u || !(d1 > 9.6e-7f && d1 < 1.0e6f))) e1 = powf(d1, c.norm);
+        const uint32_t eb = bf2_pack(e1, e0);
+        err += __uint_as_float(eb << 16);
+        err += __uint_as_float(eb & 0xFFFF0000u);
+      }
+      for (int o = lanes >> 1; o > 0; o >>= 1) err += __shfl_xor_sync(0xffffffffu, err, o);
+      err = bf16r(err);
+      if (live && err < best_err) {
+        best_err = err; best_mn = smn; best_mx = smx;
+        if (pass == 0 && (cc % lanes) == 0 && ((volatile int*)ctl)[1 + i] == 0) atomicOr(&ctl[1 + i], 1);
+      }
+    }
+    if (live && (cc % lanes) == 0) {
+      int64_t gi = row * gpr + (cc * 8) / g;
+      ((T*)mn_out)[gi] = __float2bfloat16_rn(best_mn);
+      ((T*)mx_out)[gi] = __float2bfloat16_rn(best_mx);
+    }
+  }
+}
+#undef B200Q_BF2
+
 template <int DT>
 __global__ void __launch_bounds__(256) mse_channel_kernel(const void* __restrict__ W, int64_t N, int64_t K,
                                                           int64_t ldw, Cfg c, int* __restrict__ ctl, int pass,
@@ -247,7 +370,12 @@ int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t l
       int g = qa->group_size;
       if (!(g >= 8 && g <= 256 && (g & (g - 1)) == 0 && K % g == 0)) return B200Q_ERR_UNSUPPORTED;
       int grid_sz = grid_for((N * (K >> 3) + 255) / 256, 4);
-      if (wdtype == B200Q_BF16) mse_group_kernel<B200Q_BF16><<<grid_sz, 256, 0, st>>>(W, N, K, ldw, g, c, ctl, pass, mn_out, mx_out);
+      const bool fast = wdtype == B200Q_BF16 && qr.kind == kInt && qa->scale_kind != B200Q_SCALE_FP8 &&
+                        qa->scale_kind != B200Q_SCALE_E8M0 && c.steps <= 1024 && (K & 7) == 0 && (ldw & 7) == 0 &&
+                        (((uintptr_t)W) & 15) == 0;
+      if (fast && qa->num_bits == 4) mse_group_bf16_int_kernel<true><<<grid_sz, 256, 0, st>>>(W, N, K, ldw, g, c, ctl, pass, mn_out, mx_out);
+      else if (fast) mse_group_bf16_int_kernel<false><<<grid_sz, 256, 0, st>>>(W, N, K, ldw, g, c, ctl, pass, mn_out, mx_out);
+      else if (wdtype == B200Q_BF16) mse_group_kernel<B200Q_BF16><<<grid_sz, 256, 0, st>>>(W, N, K, ldw, g, c, ctl, pass, mn_out, mx_out);
       else mse_group_kernel<B200Q_F32><<<grid_sz, 256, 0, st>>>(W, N, K, ldw, g, c, ctl, pass, mn_out, mx_out);
     } else if (qa->strategy == B200Q_CHANNEL) {
       size_t smem = (size_t)K * sizeof(float);

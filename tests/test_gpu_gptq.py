@@ -208,6 +208,23 @@ def test_mse_golden(golden):
     assert worst <= 0.05, worst
 
 
+@pytest.mark.parametrize("bits,symmetric,g,kw", [(4, True, 128, {}), (4, False, 128, {}), (8, True, 128, {}),
+                                                 (8, False, 32, {}), (4, True, 64, {"maxshrink": 0.6, "grid": 50.0}),
+                                                 (4, True, 128, {"maxshrink": 1.0, "grid": 100.0, "norm": 2.0})])
+def test_mse_packed_kernel_vs_oracle(bits, symmetric, g, kw):
+    """bf16 weights with integer codes take the packed bf16x2 kernel; same tolerance as the golden cases
+    (the oracle sums the errors of a group in torch's order, the kernel lane by lane)."""
+    spec = oracle.QSpec(num_bits=bits, type="int", symmetric=symmetric, strategy="group", group_size=g)
+    args = QuantizationArgs(num_bits=bits, type="int", symmetric=symmetric, strategy="group", group_size=g,
+                            observer="memoryless_mse", observer_kwargs=kw)
+    w = synth_weight(96, 1024, seed=bits + g)
+    mn_ref, mx_ref = oracle.observe_mse(w, spec, **kw)
+    obs = observers.Observer.load_from_registry("memoryless_mse", base_name="weight", args=args)
+    obs(w.to(DEV))
+    mm = max(mismatch(obs.min_vals, mn_ref), mismatch(obs.max_vals, mx_ref))
+    assert mm <= 0.05, mm
+
+
 # ------------------------------------------------------------------------------- tensor-core GEMM
 @pytest.mark.parametrize("trans_b", [True, False])
 @pytest.mark.parametrize("M,N,Kd", [(128, 128, 32), (256, 384, 128), (2, 128, 128), (128, 2, 128), (130, 70, 2),
