@@ -638,6 +638,28 @@ def run_micro(args):
             del x, H
     if args.micro in ("pack", "all"):
         out["results"].extend(pack_micro(args.steps, peaks, timed, g, dev))
+    if args.micro in ("mse", "all"):
+        import time as _time
+
+        from llm_compressor_b200 import observers
+        from llm_compressor_b200.quant_args import QuantizationArgs
+        for (N, K) in ((4096, 4096), (14336, 4096)):
+            w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            for kw in ({}, {"maxshrink": 1.0, "grid": 100.0, "norm": 2.4}):
+                a = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128,
+                                     observer="memoryless_mse", observer_kwargs=kw)
+                ts = []
+                for _ in range(max(3, args.steps)):
+                    obs = observers.Observer.load_from_registry("memoryless_mse", base_name="weight", args=a)
+                    torch.cuda.synchronize()
+                    t0 = _time.perf_counter()
+                    obs(w)
+                    torch.cuda.synchronize()
+                    ts.append((_time.perf_counter() - t0) * 1e3)
+                ms = statistics.median(ts)
+                steps = int(kw.get("maxshrink", 0.2) * kw.get("grid", 100.0))
+                out["results"].append({"kernel": "observe_mse_int4_g128", "N": N, "K": K, "candidates": steps, "ms": ms,
+                                       "g_element_steps_per_s": N * K * steps / ms / 1e6})
     if args.micro in ("factor", "all"):
         K = args.micro_k if args.micro == "factor" else 4096
         xx = torch.randn(2 * K, K, generator=g, device=dev)
@@ -655,7 +677,7 @@ def run_micro(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["syrk", "pack", "factor", "all"],
+    ap.add_argument("--micro", default=None, choices=["syrk", "pack", "factor", "mse", "all"],
                     help="kernel-level micro benchmark instead of the layer step")
     ap.add_argument("--micro-k", type=int, default=4096)
     ap.add_argument("--micro-t", type=int, default=32768)
