@@ -62,6 +62,16 @@ def _sequential_layers(model, sequential_targets):
         names = list(getattr(model, "_no_split_modules", None) or [])
     if isinstance(names, str):
         names = [names]
+    if not names:
+        # no hint from the model: take the class of the longest ModuleList of same-class blocks
+        # (the decoder stack of the usual architectures)
+        best = None
+        for _, m in model.named_modules():
+            if isinstance(m, torch.nn.ModuleList) and len(m) > 0 and len({type(c) for c in m}) == 1:
+                if best is None or len(m) > len(best):
+                    best = m
+        if best is not None:
+            names = [type(best[0]).__name__]
     layers = [(n, m) for n, m in model.named_modules() if type(m).__name__ in names]
     # keep outermost matches only
     out = []
