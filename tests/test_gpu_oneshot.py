@@ -210,3 +210,62 @@ def test_staged_hessian_accumulation_equals_per_batch_accumulation():
         for n in out[0]:
             layer0 = ".layers.0." in n
             assert mismatch(out[0][n], other[n]) <= (0.005 if layer0 else 0.15), n
+
+
+class _Expert(torch.nn.Module):
+    def __init__(self, h, i):
+        super().__init__()
+        self.gate_proj = torch.nn.Linear(h, i, bias=False)
+        self.up_proj = torch.nn.Linear(h, i, bias=False)
+        self.down_proj = torch.nn.Linear(i, h, bias=False)
+
+    def forward(self, x):
+        return self.down_proj(torch.nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+
+
+class _MoEBlock(torch.nn.Module):
+    def __init__(self, h, i, experts):
+        super().__init__()
+        self.experts = torch.nn.ModuleList([_Expert(h, i) for _ in range(experts)])
+        self.gate = torch.nn.Linear(h, experts, bias=False)
+
+    def forward(self, x, **_):
+        w = torch.softmax(self.gate(x), -1)
+        return x + sum(w[..., e:e + 1] * ex(x) for e, ex in enumerate(self.experts))   # every expert sees every token
+
+
+class _MoEModel(torch.nn.Module):
+    def __init__(self, h=256, i=128, experts=6, layers=2):
+        super().__init__()
+        self.embed_tokens = torch.nn.Embedding(512, h)
+        self.layers = torch.nn.ModuleList([_MoEBlock(h, i, experts) for _ in range(layers)])
+        self.lm_head = torch.nn.Linear(h, 512, bias=False)
+
+    def forward(self, input_ids=None, **_):
+        x = self.embed_tokens(input_ids)
+        for layer in self.layers:
+            x = layer(x)
+        return self.lm_head(x)
+
+
+def test_all_expert_calibration_shares_one_hessian_per_layer():
+    """All experts of a block see the same tokens: their gate / up projections share one Hessian
+    accumulation and one factorisation, every down projection keeps its own; the blocks are found
+    without a hint (longest ModuleList), the router is ignored by pattern."""
+    torch.manual_seed(0)
+    base = _MoEModel().to(torch.bfloat16).to(DEV)
+    for p in base.parameters():
+        p.requires_grad_(False)
+    data = calib(8, 64)
+    out = []
+    for share in (True, False):
+        recipe = GPTQModifier(targets="Linear", scheme="W4A16", ignore=["lm_head", "re:.*\\.gate$"],
+                              actorder=None, share_hessians=share)
+        m = oneshot(copy.deepcopy(base), recipe=recipe, dataset=data)
+        assert len(recipe.losses) == 2 * 6 * 3
+        assert all(v == v and v < float("inf") for v in recipe.losses.values())
+        assert not hasattr(m.layers[0].gate, "weight_scale")
+        out.append({n: p.data.clone() for n, p in m.named_parameters() if n.endswith("proj.weight")})
+    for n in out[0]:
+        assert torch.equal(out[0][n], out[1][n]), n
+    assert not torch.equal(out[0]["layers.0.experts.0.up_proj.weight"], base.layers[0].experts[0].up_proj.weight.data)
