@@ -85,6 +85,21 @@ def accumulate_hessian(inp, module, H, num_samples):
     return H, num_samples
 
 
+def accumulate_hessian_running_mean(inp, module, H, num_samples):
+    """The SparseGPT / Wanda consumers' Hessian: the running mean of 2 X^T X over the samples
+    seen so far (src/llmcompressor/modifiers/pruning/sparsegpt/sgpt_sparsify.py:20-56), same
+    contract as ``accumulate_hessian`` (mutates and returns the full symmetric H and the sample
+    count).  The same rank-k kernel with alpha = 2 / n after the stored part has been rescaled."""
+    if isinstance(module, torch.nn.Conv2d):
+        raise NotImplementedError("Conv2d Hessians are outside this package's path")
+    x, added = _tokens_2d(inp, H.device)
+    ops.hessian_finalize(H, num_samples / (num_samples + added))   # H *= n / (n + added)
+    num_samples += added
+    ops.hessian_syrk(x, H, alpha=2.0 / num_samples)
+    ops.hessian_finalize(H, 1.0)
+    return H, num_samples
+
+
 @dataclass
 class HessianFactor:
     """What the sweep needs from one Hessian: the act-order permutation (or None), the

@@ -38,6 +38,21 @@ def accumulate_hessian(inp: torch.Tensor, H: torch.Tensor, num_samples):
     return H, num_samples
 
 
+def accumulate_hessian_running_mean(inp: torch.Tensor, H: torch.Tensor, num_samples):
+    """The SparseGPT / Wanda variant: H is the running mean of 2 X^T X over the samples seen so
+    far (src/llmcompressor/modifiers/pruning/sparsegpt/sgpt_sparsify.py:20-56)."""
+    if inp.ndim == 2:
+        inp = inp.unsqueeze(0)
+    added = inp.shape[0]
+    x = inp.reshape(-1, inp.shape[-1]).t()
+    H *= num_samples / (num_samples + added)
+    num_samples = num_samples + added
+    x = x.to(torch.float32)
+    x = math.sqrt(2 / num_samples) * x
+    H += x.matmul(x.t())
+    return H, num_samples
+
+
 def hessian_inverse_factor(H: torch.Tensor, percdamp: float):
     """Upper factor U with U^T U = (H + damp I)^-1, computed as the reference does:
     Cholesky, Cholesky-inverse, upper Cholesky (gptq_quantize.py:150-156).  Returns

@@ -62,6 +62,19 @@ def test_hessian_vs_oracle(T, K):
     assert rel_fro(H2, H_ref) < HESSIAN_RTOL
 
 
+def test_hessian_running_mean_variant():
+    K = 512
+    H = torch.zeros(K, K, device=DEV)
+    H_ref, n, n_ref = oracle.make_empty_hessian(K), 0, 0
+    for i, (B, S) in enumerate([(2, 96), (1, 300), (3, 64)]):
+        x = synth_acts(B, S, K, seed=40 + i)
+        H, n = gptq.accumulate_hessian_running_mean(x.to(DEV), torch.nn.Linear(K, 8), H, n)
+        H_ref, n_ref = oracle.accumulate_hessian_running_mean(x, H_ref, n_ref)
+        assert n == n_ref
+        assert rel_fro(H, H_ref) < HESSIAN_RTOL
+        assert torch.equal(H, H.t())
+
+
 def test_hessian_noncontiguous_and_3d():
     x = synth_acts(3, 100, 136, seed=9)  # [B,S,K] with K % 8 == 0
     H_ref, n_ref = oracle.accumulate_hessian(x, oracle.make_empty_hessian(136), 0)
