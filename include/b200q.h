@@ -104,9 +104,10 @@ int b200q_qparams(const void* min_vals, const void* max_vals, int stat_dtype, in
  * Writes the best min/max per group (W's dtype).  GROUP / TENSOR_GROUP (group a power of two,
  * 8..256) and CHANNEL strategies.  scratch: b200q_observe_mse_workspace_bytes (per-candidate
  * "some group improved" flags that reproduce the reference's global early stop). */
+int b200q_observe_mse_steps(double maxshrink, double grid); /* int(maxshrink * grid), -1 if invalid */
 size_t b200q_observe_mse_workspace_bytes(int64_t N, int64_t K, const b200q_qargs* qa, int steps);
 int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw,
-                      const b200q_qargs* qa, float maxshrink, int patience, float grid,
+                      const b200q_qargs* qa, double maxshrink, int patience, double grid,
                       float norm, float expand, void* min_out, void* max_out, void* scratch,
                       void* stream);
 
@@ -123,7 +124,7 @@ int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t l
  *     streams) race on it, so issue them on one stream or order them yourself.  The previous
  *     call's contents are cleared by the search itself. */
 int b200q_observe_mse_noalloc(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw,
-                              const b200q_qargs* qa, float maxshrink, int patience, float grid,
+                              const b200q_qargs* qa, double maxshrink, int patience, double grid,
                               float norm, float expand, void* min_out, void* max_out, void* stream);
 
 /* ------------------------------------------------------------- quantize / pack */
@@ -182,8 +183,9 @@ int b200q_nvfp4_quantize_pack(const void* W, int wdtype, int64_t N, int64_t K, i
 /* H_lower += alpha * X^T X  (fp32 accumulate, bf16 X [T,K] row-major, K contiguous).
  * Only tiles on or below the diagonal are written; b200q_hessian_finalize mirrors them.
  * Replaces accumulate_hessian (src/modifiers/gptq/gptq_quantize.py:28-64; alpha = 2).
- * Requires K % 8 == 0 and 16-byte aligned X, ldx % 8 == 0.  `status` (device int, may be
- * NULL) receives non-zero if a bounded wait inside the kernel expired.  Launches clusters of
+ * Requires K % 8 == 0 and 16-byte aligned X, ldx % 8 == 0 (the Python front end pads other
+ * widths).  `status` (device int, may be NULL; never cleared by the call) receives non-zero if
+ * a bounded wait inside the kernel expired: H is then incomplete.  Launches clusters of
  * two CTAs (tcgen05.mma.cta_group::2); B200Q_SYRK_SINGLE_CTA=1 in the environment selects the
  * single-CTA kernel. */
 int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* H, int64_t ldh,
@@ -255,7 +257,10 @@ int b200q_gemm_tf32x3(int trans_b, const float* A, int64_t lda, const float* B, 
  * Wf fp32 [N,K] in/out (ends as the fake-quantised weight); U from b200q_gptq_factor
  * (NULL = identity: round to nearest); scale [N,G] / [N,1] / [1] of dtype sdtype; zp may be
  * NULL; col_group int32 [K] (group of each column; NULL = column/group_size); losses float [N]
- * (overwritten).  workspace: b200q_gptq_sweep_workspace_bytes(N, K, blocksize). */
+ * (overwritten).  workspace: b200q_gptq_sweep_workspace_bytes(N, K, blocksize) bytes, 16-byte
+ * aligned.  Its first int32 is a status word: the call clears it, and a bounded wait that ran
+ * out inside one of the trailing-update GEMMs sets it to B200Q_ERR_DEVICE (W is then
+ * incomplete); read it after the stream has reached the end of the call. */
 size_t b200q_gptq_sweep_workspace_bytes(int64_t N, int64_t K, int blocksize);
 int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* U, int64_t ldu,
                      const void* scale, int sdtype, const void* zp, const int32_t* col_group,

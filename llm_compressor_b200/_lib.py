@@ -38,7 +38,7 @@ class B200QError(RuntimeError):
     pass
 
 
-_p, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+_p, _i, _i64, _f, _d = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_double
 _qa = C.POINTER(QArgs)
 
 # name -> (restype, argtypes); must list every symbol of include/b200q.h
@@ -52,8 +52,9 @@ SIGNATURES = {
     "b200q_global_scale_finalize": (_i, [_p, _i, _p, _p]),
     "b200q_qparams": (_i, [_p, _p, _i, _i64, _qa, _p, _p, _p, _p]),
     "b200q_observe_mse_workspace_bytes": (C.c_size_t, [_i64, _i64, _qa, _i]),
-    "b200q_observe_mse": (_i, [_p, _i, _i64, _i64, _i64, _qa, _f, _i, _f, _f, _f, _p, _p, _p, _p]),
-    "b200q_observe_mse_noalloc": (_i, [_p, _i, _i64, _i64, _i64, _qa, _f, _i, _f, _f, _f, _p, _p, _p]),
+    "b200q_observe_mse_steps": (_i, [_d, _d]),
+    "b200q_observe_mse": (_i, [_p, _i, _i64, _i64, _i64, _qa, _d, _i, _d, _f, _f, _p, _p, _p, _p]),
+    "b200q_observe_mse_noalloc": (_i, [_p, _i, _i64, _i64, _i64, _qa, _d, _i, _d, _f, _f, _p, _p, _p]),
     "b200q_fake_quantize": (_i, [_p, _i, _i64, _i64, _i64, _p, _i, _p, _p, _p, _qa, _p, _i64, _p]),
     "b200q_quantize_pack": (_i, [_p, _i, _i64, _i64, _i64, _p, _i, _p, _p, _p, _qa, _i, _p, _p]),
     "b200q_pack_zero_points": (_i, [_p, _i64, _i64, _i, _p, _p]),

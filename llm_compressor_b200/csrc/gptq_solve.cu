@@ -23,29 +23,42 @@ namespace solve {
 constexpr int NB = 128;
 
 // ---------------------------------------------------------------------------------------
-// act-order: stable descending rank by counting
+// act-order: stable descending rank by counting.  The comparison runs on an integer key that
+// orders every float the way torch.sort does (NaN above +inf, -0 equal to +0), so the ranks are
+// a permutation of 0..K-1 whatever the diagonal holds.
+__device__ __forceinline__ uint32_t order_key(float d) {
+  if (d != d) return 0xFFFFFFFFu;
+  const uint32_t b = __float_as_uint(d + 0.0f);   // -0 + 0 = +0
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
 __global__ void __launch_bounds__(256) perm_kernel(const float* __restrict__ H, int64_t K, int64_t ldh,
                                                    int32_t* __restrict__ perm) {
-  __shared__ float sd[1024];
+  __shared__ uint32_t sd[1024];
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const float di = (i < K) ? H[i * ldh + i] : 0.0f;
+  const uint32_t ki = (i < K) ? order_key(H[i * ldh + i]) : 0u;
   int rank = 0;
   for (int64_t j0 = 0; j0 < K; j0 += 1024) {
     for (int t = threadIdx.x; t < 1024; t += blockDim.x) {
       int64_t j = j0 + t;
-      sd[t] = (j < K) ? H[j * ldh + j] : -INFINITY;
+      sd[t] = (j < K) ? order_key(H[j * ldh + j]) : 0u;
     }
     __syncthreads();
     if (i < K) {
       const int lim = (int)min((int64_t)1024, K - j0);
       for (int t = 0; t < lim; ++t) {
-        const float dj = sd[t];
-        rank += (dj > di) || (dj == di && (j0 + t) < i);
+        const uint32_t kj = sd[t];
+        rank += (kj > ki) || (kj == ki && (j0 + t) < i);
       }
     }
     __syncthreads();
   }
   if (i < K) perm[rank] = (int32_t)i;
+}
+
+// column index taken from a caller-supplied permutation, kept inside the matrix
+__device__ __forceinline__ int64_t perm_at(const int32_t* __restrict__ perm, int64_t c, int64_t K) {
+  const int64_t v = (int64_t)perm[c];
+  return v < 0 ? 0 : (v >= K ? K - 1 : v);
 }
 
 template <int DT>
@@ -56,7 +69,7 @@ __global__ void gather_cols_kernel(const void* __restrict__ W, int64_t N, int64_
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     int64_t r = i / K, c = i - r * K;
-    int64_t src = perm ? (int64_t)perm[c] : c;
+    int64_t src = perm ? perm_at(perm, c, K) : c;
     out[r * ldo + c] = E::load((const typename E::type*)W + r * ldw + src);
   }
 }
@@ -68,7 +81,7 @@ __global__ void permute_hessian_kernel(const float* __restrict__ H, int64_t K, i
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     int64_t r = i / K, c = i - r * K;
-    out[r * ldo + c] = H[(int64_t)perm[r] * ldh + perm[c]];
+    out[r * ldo + c] = H[perm_at(perm, r, K) * ldh + perm_at(perm, c, K)];
   }
 }
 
@@ -80,7 +93,7 @@ __global__ void scatter_cols_kernel(const float* __restrict__ Wf, int64_t N, int
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     int64_t r = i / K, c = i - r * K;
-    int64_t dst = perm ? (int64_t)perm[c] : c;
+    int64_t dst = perm ? perm_at(perm, c, K) : c;
     E::store((typename E::type*)out + r * ldo + dst, Wf[r * ldf + c]);
   }
 }

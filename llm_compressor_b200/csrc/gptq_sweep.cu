@@ -17,6 +17,7 @@ namespace b200q {
 namespace sweep {
 
 constexpr int kMaxBlock = 128;
+constexpr size_t kSweepHeaderBytes = 256;   // status word at the start of the workspace
 
 struct Params {
   float* W; int64_t ldw; int64_t N; int64_t K;
@@ -249,11 +250,12 @@ using namespace b200q;
 extern "C" {
 
 size_t b200q_gptq_sweep_workspace_bytes(int64_t N, int64_t K, int blocksize) {
+  using b200q::sweep::kSweepHeaderBytes;
   if (N <= 0 || K <= 0 || blocksize <= 0) return 0;
   // error panel [N][128] + two sets of (hi/lo copies of it, hi/lo copies of a 128-row panel of U):
   // consecutive blocks alternate between the sets because of the look-ahead
   const size_t np = (size_t)((N + 127) / 128 * 128), kp = (size_t)((K + 127) / 128 * 128);
-  return (np * 128 * 5 + 4 * 128 * kp) * sizeof(float) + 64;
+  return kSweepHeaderBytes + (np * 128 * 5 + 4 * 128 * kp) * sizeof(float) + 64;
 }
 
 int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* U, int64_t ldu, const void* scale,
@@ -262,6 +264,7 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
   using namespace b200q::sweep;
   if (!Wf || !scale || !qa || !losses || !workspace || N <= 0 || K <= 0 || ldf < K) return B200Q_ERR_ARG;
   if (U && ldu < K) return B200Q_ERR_ARG;
+  if (((uintptr_t)workspace) & 15) return B200Q_ERR_ARG;
   if (blocksize <= 0 || blocksize > kMaxBlock) return B200Q_ERR_UNSUPPORTED;
   Params p;
   int rc = make_qrange(qa, &p.qr); if (rc) return rc;
@@ -274,14 +277,17 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
   p.block_h = qa->block_h > 0 ? qa->block_h : 1;
   p.zp_kind = qa->zp_kind;
   p.groups_per_row = pm.groups_per_row;
-  p.err = (float*)workspace;
+  // header of the workspace: a status word that a bounded wait expiring inside one of the
+  // trailing-update GEMMs sets to B200Q_ERR_DEVICE (cleared here, read by the caller afterwards)
+  int* gemm_status = (int*)workspace;
+  p.err = (float*)((char*)workspace + kSweepHeaderBytes);
   p.lde = 128;
   const size_t np128 = (size_t)((N + 127) / 128 * 128) * 128, kp128 = (size_t)((K + 127) / 128 * 128) * 128;
   float* sa_base = p.err + np128;            // [2][hi, lo][np128]
   float* sb_base = sa_base + 4 * np128;      // [2][hi, lo][kp128]
-  int* gemm_status = nullptr;
   p.losses = losses;
   cudaStream_t st = (cudaStream_t)stream;
+  B200Q_TRY(cudaMemsetAsync(gemm_status, 0, sizeof(int), st));
   // warps per CTA: one 32-row batch per warp; few rows -> small CTAs so that every SM gets work
   const int64_t batches = (N + 31) / 32;
   int warps = (int)((batches + kNumSMs - 1) / kNumSMs);

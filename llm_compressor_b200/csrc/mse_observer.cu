@@ -23,7 +23,8 @@ struct Cfg {
   float qmin, qmax, half_range, range, eps;
   int kind;
   int steps, patience;
-  float grid, norm, expand;
+  double grid;
+  float norm, expand;
 };
 
 // qparams of calculate_qparams without a global scale, in dtype T (TB: bf16).
@@ -68,8 +69,8 @@ __device__ __forceinline__ float elem_error(float x, float s, float z, const Cfg
   return rnd_if<TB>(e);
 }
 
-__device__ __forceinline__ float shrink_factor(int i, float grid) {
-  return (float)(1.0 - (double)i / (double)grid);
+__device__ __forceinline__ float shrink_factor(int i, double grid) {
+  return (float)(1.0 - (double)i / grid);
 }
 
 // ctl[0] = number of steps to run, ctl[1..] = per-step "some group improved" flags
@@ -330,12 +331,19 @@ using namespace b200q;
 
 extern "C" {
 
+// int(maxshrink * grid) in double precision, as the reference's Python evaluates it
+int b200q_observe_mse_steps(double maxshrink, double grid) {
+  const double v = maxshrink * grid;
+  if (!(v >= 0.0)) return -1;
+  return v > 2147483647.0 ? 2147483647 : (int)v;
+}
+
 size_t b200q_observe_mse_workspace_bytes(int64_t, int64_t, const b200q_qargs*, int steps) {
   return sizeof(int) * (size_t)(steps + 1 > 1 ? steps + 1 : 1);
 }
 
 int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw, const b200q_qargs* qa,
-                      float maxshrink, int patience, float grid, float norm, float expand, void* mn_out,
+                      double maxshrink, int patience, double grid, float norm, float expand, void* mn_out,
                       void* mx_out, void* scratch, void* stream) {
   using namespace b200q::mse;
   if (!W || !qa || !mn_out || !mx_out || !scratch || N <= 0 || K <= 0 || ldw < K) return B200Q_ERR_ARG;
@@ -350,7 +358,7 @@ int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t l
   if (qa->scale_kind == B200Q_SCALE_FP8) c.eps = 0.125f;
   else if (qa->scale_kind == B200Q_SCALE_E8M0) c.eps = 1.0f;
   else c.eps = (wdtype == B200Q_BF16) ? 0.0078125f : 1.1920928955078125e-07f;
-  c.steps = (int)((double)maxshrink * (double)grid);
+  c.steps = b200q_observe_mse_steps(maxshrink, grid);
   c.patience = patience; c.grid = grid; c.norm = norm; c.expand = expand;
   if (wdtype == B200Q_BF16) {
     // torch casts the python exponent to the tensor's dtype: |e|.pow(2.4) on bf16 uses 2.40625
@@ -442,11 +450,11 @@ static int static_ctl_address(int** out) {
 }  // namespace b200q
 
 extern "C" int b200q_observe_mse_noalloc(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw,
-                                         const b200q_qargs* qa, float maxshrink, int patience, float grid,
+                                         const b200q_qargs* qa, double maxshrink, int patience, double grid,
                                          float norm, float expand, void* mn_out, void* mx_out, void* stream) {
   using namespace b200q::mse;
-  const double steps = (double)maxshrink * (double)grid;
-  if (!(steps >= 0.0) || steps > (double)kStaticMaxSteps) {
+  const int steps = b200q_observe_mse_steps(maxshrink, grid);
+  if (steps < 0 || steps > kStaticMaxSteps) {
     b200q::set_last_error("b200q_observe_mse_noalloc: int(maxshrink*grid) exceeds the built-in scratch (1023 candidates)",
                           cudaErrorInvalidValue);
     return B200Q_ERR_ARG;

@@ -154,9 +154,12 @@ def quantize_weight(module, quant_args, hessian: Optional[torch.Tensor], blocksi
     ``factor`` (from ``factor_hessian`` with the same ``percdamp`` and act-order setting) may
     be passed instead of ``hessian`` when several modules share one Hessian.
 
-    ``defer``: nothing waits for the device; the loss comes back as a 0-dim device tensor and
-    a deferred ``factor`` is used as it is.  The caller must ``factor.resolve()`` afterwards
-    and repeat the call without ``defer`` if the factorisation turned out to have failed."""
+    ``defer``: nothing waits for the device; the loss comes back as a 0-dim device tensor, a
+    deferred ``factor`` is used as it is, and the dict carries one extra entry ``"_status"``
+    (the sweep's int32 device status word, non-zero after an expired bounded wait) that the
+    caller must pop and check.  The caller must also ``factor.resolve()`` afterwards and repeat
+    the call without ``defer`` (after re-observing the weight) if the factorisation turned out
+    to have failed."""
     args = QuantizationArgs.of(quant_args)
     strategy, actorder = args.strategy, args.actorder
     weight = module.weight.data if isinstance(module.weight, torch.nn.Parameter) else module.weight
@@ -198,11 +201,16 @@ def quantize_weight(module, quant_args, hessian: Optional[torch.Tensor], blocksi
     scale, zero_point, global_scale = qparams["scale"], qparams["zero_point"], qparams["global_scale"]
 
     ops.gptq_zero_dead_columns(factor.diag, W)
-    losses = ops.gptq_sweep(W, factor.U, scale, zero_point, args, blocksize=blocksize,
-                            col_group=col_group, global_scale=global_scale)
+    losses, status = ops.gptq_sweep(W, factor.U, scale, zero_point, args, blocksize=blocksize,
+                                    col_group=col_group, global_scale=global_scale, return_status=True)
 
     Wq = ops.scatter_columns_cast(W, final_dtype, perm)
-    loss = losses.sum() if defer else float(losses.sum().item())
+    if defer:
+        loss = losses.sum()
+    else:
+        loss, st = torch.stack([losses.sum(), status[0].to(torch.float32)]).tolist()
+        if st != 0:
+            raise _lib.B200QError("b200q_gptq_sweep: a bounded wait inside the GEMM kernel expired")
     out = {
         "weight": Wq,
         "weight_scale": scale.to(final_dtype),
@@ -214,4 +222,6 @@ def quantize_weight(module, quant_args, hessian: Optional[torch.Tensor], blocksi
         invperm = torch.empty_like(perm)
         invperm[perm.long()] = torch.arange(K, device=perm.device, dtype=perm.dtype)
         out["weight_g_idx"] = g_idx[invperm.long()]
+    if defer:
+        out["_status"] = status   # the sweep's device status word; the caller checks and removes it
     return loss, out

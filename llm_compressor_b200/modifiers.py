@@ -20,6 +20,7 @@ import torch
 
 from . import dist as bdist
 from . import gptq
+from ._lib import B200QError
 from .observers import Observer, fuse_weight_observers
 from .streams import run_concurrent
 from .quant_args import (PRESET_SCHEMES, QuantizationArgs, QuantizationScheme,
@@ -182,6 +183,7 @@ class QuantizationMixin(HooksMixin):
                     bad.append((name, K, w.group_size))
                     continue
                 module.quantization_scheme = scheme
+                module.quantization_status = "initialized"   # "frozen" once its qparams are written
                 self._module_names[module] = name
                 dev, dt = module.weight.device, module.weight.dtype
                 shape = w.qparam_shape(N, K)
@@ -243,6 +245,8 @@ def update_qparams(modules: Iterable[torch.nn.Module], base_name: str = "weight"
             getattr(m, f"{base_name}_zero_point").shape))
         if qp["global_scale"] is not None and hasattr(m, f"{base_name}_global_scale"):
             getattr(m, f"{base_name}_global_scale").data.copy_(qp["global_scale"])
+        if base_name == "weight":
+            m.quantization_status = "frozen"
 
 
 # ------------------------------------------------------------------------------------------
@@ -270,6 +274,8 @@ class QuantizationModifier(QuantizationMixin):
             update_qparams(mine)
             bdist.broadcast_module_params(items, to_rank,
                                           ("weight_scale", "weight_zero_point", "weight_global_scale"))
+            for m in items:
+                m.quantization_status = "frozen"
         else:
             observe(modules)
             update_qparams(modules)
@@ -312,6 +318,8 @@ class GPTQModifier(QuantizationMixin):
         self.hessian_stage_tokens = hessian_stage_tokens
         self._groups: dict = {}        # module -> _HessianGroup
         self._num_samples: dict = {}   # module -> None (membership: modules awaiting compression)
+        self._hooked: list = []        # every module that got a calibration hook
+        self._done: set = set()        # modules whose quantised weight has been written
         self.losses: dict = {}
 
     # ---- config ------------------------------------------------------------------------------
@@ -359,13 +367,20 @@ class GPTQModifier(QuantizationMixin):
             if getattr(module, "quantization_scheme", None) is None or module.quantization_scheme.weights is None:
                 continue
             self.register_hook(module, self.calibrate_module, "forward")
+            self._hooked.append(module)
             added = True
         if not added:
             raise ValueError(
                 "GPTQModifier requires a weight quantization config be specified by this modifier or a "
                 "modifier preceding it")
 
+    def pending_modules(self):
+        """Hooked modules that have not been compressed yet."""
+        return [m for m in self._hooked if m not in self._done]
+
     def calibrate_module(self, module, args, _output):
+        if module in self._done:
+            return
         inp = args[0]
         group = self._groups.get(module)
         if group is None:
@@ -376,6 +391,14 @@ class GPTQModifier(QuantizationMixin):
                 group.members.append(module)
             self._groups[module] = group
             self._num_samples[module] = None
+        elif module is not group.members[0] and not group.same_input(inp):
+            # membership was decided on the first batch; the first member adds every batch and
+            # the others must keep receiving that very tensor
+            raise RuntimeError(
+                f"{self._module_names.get(module, type(module).__name__)} shared a Hessian with "
+                f"{self._module_names.get(group.members[0], type(group.members[0]).__name__)} because both received "
+                "the same input on the first calibration batch, but its input differs on a later batch; "
+                "set GPTQModifier(share_hessians=False)")
         group.accumulate(inp)
 
     def _find_shared(self, inp):
@@ -409,6 +432,8 @@ class GPTQModifier(QuantizationMixin):
         for m in modules:
             self._num_samples.pop(m, None)
             self._groups.pop(m, None)
+            m.quantization_status = "frozen"
+            self._done.add(m)
 
     def compress_module_list(self, module_list):
         """Quantise the modules; the modules of one Hessian form a job (one factorisation per
@@ -432,9 +457,11 @@ class GPTQModifier(QuantizationMixin):
         # the distinct act-order settings that still need this Hessian
         left = {module.quantization_scheme.weights.actorder for module in module_list}
         queued = []
+        hess_status = {}
         t0 = time.perf_counter()
         for module in module_list:
             group = self._groups.pop(module)
+            hess_status[id(group)] = group.status
             self._num_samples.pop(module, None)
             qargs = module.quantization_scheme.weights
             if qargs.actorder not in factors:
@@ -446,8 +473,23 @@ class GPTQModifier(QuantizationMixin):
                 loss, out = gptq.quantize_weight(module, qargs, None, blocksize=self.block_size,
                                                  percdamp=self.dampening_frac, factor=factor, defer=True)
             queued.append((module, qargs, factor, loss, out))
+        # one read for every device status word of the job (the first wait for the device)
+        words = [s for s in (out.pop("_status", None) for _, _, _, _, out in queued) if s is not None]
+        words += [s for s in hess_status.values() if s is not None]
+        if words and int(torch.cat([w.reshape(-1)[:1] for w in words]).abs().amax().item()) != 0:
+            raise B200QError("a bounded wait inside the Hessian or GEMM kernels of this job expired; "
+                             "its results are incomplete")
+        redo = [q for q in queued if not q[2].resolve().ok]
+        # the deferred call consumed the observers' statistics: observe again before the
+        # round-to-nearest redo (act-order "group" re-observes the permuted weight itself)
+        for module, qargs, *_ in redo:
+            if qargs.actorder != "group":
+                module.weight_observer.delete_statistics(check_fused=False)
+        for module, qargs, *_ in redo:
+            if qargs.actorder != "group":
+                module.weight_observer(module.weight.data)
         for module, qargs, factor, loss, out in queued:
-            if not factor.resolve().ok:
+            if not factor.ok:
                 with torch.no_grad():
                     loss, out = gptq.quantize_weight(module, qargs, None, blocksize=self.block_size,
                                                      percdamp=self.dampening_frac, factor=factor)
@@ -463,6 +505,8 @@ class GPTQModifier(QuantizationMixin):
                     p.data.copy_(val.reshape(p.shape))
                 else:
                     module.register_parameter(attr, torch.nn.Parameter(val, requires_grad=False))
+            module.quantization_status = "frozen"
+            self._done.add(module)
 
     @staticmethod
     def _log_metric(name, seconds, loss):
@@ -476,7 +520,12 @@ class GPTQModifier(QuantizationMixin):
     def on_finalize(self, model, **_):
         if len(self._num_samples) > 0:
             raise ValueError(f"Failed to compress {len(self._num_samples)} modules")
-        self._groups, self._num_samples = {}, {}
+        missed = self.pending_modules()
+        if missed:
+            names = ", ".join(self._module_names.get(m, type(m).__name__) for m in missed[:8])
+            raise ValueError(f"{len(missed)} targeted modules never received calibration data and were not "
+                             f"compressed: {names}{' ...' if len(missed) > 8 else ''}")
+        self._groups, self._num_samples, self._hooked = {}, {}, []
         return True
 
 
@@ -501,6 +550,7 @@ class _HessianGroup:
         self.H = torch.zeros((K, K), dtype=torch.float32, device=self.device)
         self.n = 0
         self._last = None  # (tensor kept alive, version) of the batch accumulated last
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)   # bounded-wait expiry of any update
         self.offload = offload
         self._final = None
         self.stage_tokens = int(stage_tokens)
@@ -517,7 +567,7 @@ class _HessianGroup:
     def _syrk(self, x: torch.Tensor) -> None:
         if self.offload and self.H.device != self.device:
             self.H = self.H.to(self.device)
-        gptq.ops.hessian_syrk(x, self.H, alpha=2.0)
+        gptq.ops.hessian_syrk(x, self.H, alpha=2.0, status=self.status)
         if self.offload:
             self.H = self.H.to("cpu")
 

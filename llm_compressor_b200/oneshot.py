@@ -121,10 +121,31 @@ def _run_sequential(model, modifiers, batches, sequential_targets):
             for args, kwargs in captured:  # propagation pass with the quantised weights
                 out = layer(*args, **kwargs)
                 hidden = out[0] if isinstance(out, (tuple, list)) else out
-                nxt.append(((hidden,) + tuple(args[1:]), kwargs))
+                nxt.append(_with_hidden(args, kwargs, hidden))
         captured = nxt
+    del captured
+    # targeted modules outside the blocks (an lm_head that is not ignored, a head or adapter behind
+    # the stack): one more pass over the whole model, whose blocks now carry their quantised
+    # weights, calibrates them; modules that are already done ignore their hooks
+    rest = [mod for m in modifiers for mod in getattr(m, "pending_modules", lambda: [])()]
+    if rest:
+        with torch.no_grad():
+            for b in batches:
+                model(**b)
+        for m in modifiers:
+            m.on_sequential_epoch_end(model, rest)
     for m in modifiers:
         m.on_calibration_end(model)
+
+
+def _with_hidden(args, kwargs, hidden):
+    """The next block's call: the previous block's output in place of its hidden states, which
+    may have been passed positionally or as the ``hidden_states`` keyword."""
+    if args:
+        return (hidden,) + tuple(args[1:]), kwargs
+    if "hidden_states" in kwargs:
+        return (), dict(kwargs, hidden_states=hidden)
+    raise ValueError("cannot tell which argument of the sequential block carries the hidden states")
 
 
 def _run_data_free(model, modifiers):
@@ -183,6 +204,9 @@ def compressed_state_dict(model, compress: bool = True):
     skip = set()
     for name, mod in quantised.items():
         scheme = mod.quantization_scheme
+        if scheme.weights is not None and getattr(mod, "quantization_status", "frozen") != "frozen":
+            raise ValueError(f"{name} has a weight quantisation scheme but was never calibrated: its scale is "
+                             "uninitialised (was it outside the calibrated blocks, or never reached by a forward pass?)")
         local = {k: getattr(mod, k).data for k in ("weight", "weight_scale", "weight_zero_point",
                                                    "weight_global_scale", "weight_g_idx") if hasattr(mod, k)}
         if "weight_g_idx" in local and bool((local["weight_g_idx"] < 0).any()):

@@ -64,7 +64,9 @@ def observe_mse(w, args, maxshrink=0.20, patience=5, grid=100.0, norm=2.4, expan
     shape = args.qparam_shape(N, K)
     mn = torch.empty(shape, dtype=w.dtype, device=w.device)
     mx = torch.empty(shape, dtype=w.dtype, device=w.device)
-    steps = int(maxshrink * grid)
+    steps = lib.b200q_observe_mse_steps(float(maxshrink), float(grid))
+    if steps < 0:
+        raise ValueError(f"maxshrink * grid = {maxshrink * grid} is not a valid number of candidates")
     nbytes = lib.b200q_observe_mse_workspace_bytes(N, K, qa, steps)
     scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=w.device)
     check(lib.b200q_observe_mse(ptr(w), _dt(w), N, K, ld, qa, float(maxshrink), int(patience),
@@ -92,7 +94,7 @@ def observe_mse_noalloc(w, args, mn: torch.Tensor, mx: torch.Tensor, maxshrink=0
     rc = lib.b200q_observe_mse_noalloc(ptr(w), _dt(w), N, K, ld, args.c_struct(), float(maxshrink),
                                        int(patience), float(grid), float(norm), float(expand), ptr(mn),
                                        ptr(mx), stream_ptr())
-    if rc == -1 and int(maxshrink * grid) > 1023:
+    if rc == -1 and lib.b200q_observe_mse_steps(float(maxshrink), float(grid)) > 1023:
         raise _lib.B200QError("b200q_observe_mse_noalloc: int(maxshrink*grid) = %d candidates exceed the "
                               "built-in scratch of 1023; use observe_mse" % int(maxshrink * grid))
     check(rc, "b200q_observe_mse_noalloc")
@@ -240,12 +242,23 @@ def nvfp4_quantize_pack(w, global_scale: torch.Tensor):
 
 # ------------------------------------------------------------------------------- Hessian
 def hessian_syrk(x: torch.Tensor, H: torch.Tensor, alpha: float = 2.0, status=None):
-    """H_lower += alpha * x^T x ; x [T,K] bf16 with contiguous rows."""
+    """H_lower += alpha * x^T x ; x [T,K] bf16 with contiguous rows.  ``status`` (int32 device
+    tensor, optional) becomes non-zero if a bounded wait inside the kernel ran out."""
     _need_cuda(x, H)
     if x.dtype != torch.bfloat16:
         raise TypeError("hessian_syrk takes bfloat16 activations")
     T, K, ld = _2d(x)
     assert H.dtype == torch.float32 and H.shape == (K, K) and H.stride(1) == 1
+    if K % 8 or H.stride(0) % 4:
+        # the kernel's tiles need 16-byte rows: widths that are not a multiple of 8 go through a
+        # zero-padded copy (the reference accepts any width)
+        Kp = -(-K // 8) * 8
+        xp = torch.zeros((T, Kp), dtype=x.dtype, device=x.device)
+        xp[:, :K] = x
+        Hp = torch.zeros((Kp, Kp), dtype=torch.float32, device=H.device)
+        hessian_syrk(xp, Hp, alpha, status)
+        H += Hp[:K, :K]
+        return H
     check(_lib.load().b200q_hessian_syrk(ptr(x), T, K, ld, ptr(H), H.stride(0), float(alpha),
                                          ptr(status), stream_ptr()), "b200q_hessian_syrk")
     return H
@@ -342,8 +355,10 @@ def gptq_factor(H: torch.Tensor) -> int:
 
 
 def gptq_sweep(wf, U, scale, zp, args: QuantizationArgs, blocksize=128, col_group=None,
-               global_scale=None) -> torch.Tensor:
-    """Runs the column sweep in place on wf; returns per-row losses."""
+               global_scale=None, return_status: bool = False):
+    """Runs the column sweep in place on wf; returns per-row losses, and with ``return_status``
+    also the call's device status word (int32 [1]; non-zero: a bounded wait inside a
+    trailing-update GEMM ran out and wf is incomplete)."""
     _need_cuda(wf, U, scale, zp, col_group, global_scale)
     lib = _lib.load()
     N, K, ld = _2d(wf)
@@ -360,6 +375,8 @@ def gptq_sweep(wf, U, scale, zp, args: QuantizationArgs, blocksize=128, col_grou
                                ptr(scale), _dt(scale), ptr(zp), ptr(col_group), ptr(global_scale),
                                args.c_struct(), int(blocksize), ptr(losses), ptr(ws), stream_ptr()),
           "b200q_gptq_sweep")
+    if return_status:
+        return losses, ws[:4].view(torch.int32)
     return losses
 
 
