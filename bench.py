@@ -40,6 +40,15 @@ MODULES = [("q_proj", HIDDEN, "attn_in"), ("k_proj", KV_OUT, "attn_in"), ("v_pro
 GROUP_K = {"attn_in": HIDDEN, "o_in": HIDDEN, "mlp_in": HIDDEN, "down_in": INTER}
 
 
+# DRAM traffic of one rank-k update launch (dram__bytes_read.sum + dram__bytes_write.sum of ncu
+# captures of 32768-token launches); a step runs 96 launches of width 4096 and 32 of width 14336.
+SYRK_TRAFFIC = {
+    "K4096": 620.0e6, "K14336": None,
+    "per_launch_weighted": 620.0e6,
+    "note": "bytes per K=4096 launch of 32768 tokens, from the ncu capture; algorithmic 2TK + 4K(K+1) = 336e6",
+}
+
+
 def f_syrk(tokens: int, K: int) -> float:
     """Algorithmic flops of a symmetric rank-k update: one multiply-add per token for each of
     the K(K+1)/2 distinct entries."""
@@ -172,8 +181,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "configs[2]: GPTQ W4A16 g128, Llama-3-8B shapes, 512x2048 calibration tokens",
-                   "step": "one decoder layer (bounded CPU sample, extrapolated)", "layers": LAYERS},
+        "config": workload_config(args.seqs, args.tokens_per_call),
+        "step_note": "one decoder layer (bounded CPU sample, extrapolated)",
         "cpu_baseline": {"value": value, "unit": "s", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -184,17 +193,45 @@ def run_reference(args):
 # ======================================================================================
 # GPU arm
 # ======================================================================================
+def workload_config(seqs=SEQS, tokens_per_call=32768):
+    """The `config` object of both arms' JSON lines."""
+    return {"workload": "configs[2]: GPTQ W4A16 g128 (sym int4, block 128, damp 0.01, no act-order), "
+                        "Llama-3-8B shapes, %d x %d calibration tokens" % (seqs, SEQ_LEN),
+            "step": "one decoder layer: 4 Hessians over all tokens + 7 modules observe/factor/sweep/pack",
+            "layers": LAYERS, "tokens_per_syrk_call": tokens_per_call,
+            "l2": "inputs larger than L2 (tens of GB streamed per step)",
+            "calibration_scale": SEQS / seqs}
+
+
+class _Layer:
+    """Seven Linear modules with the shapes of one Llama-3-8B decoder layer."""
+
+    def __init__(self, torch, device):
+        gw = torch.Generator(device=device).manual_seed(0)
+        self.module = torch.nn.Module()
+        self.mods = []
+        for name, n_out, grp in MODULES:
+            lin = torch.nn.Linear(GROUP_K[grp], n_out, bias=False, device=device, dtype=torch.bfloat16)
+            lin.weight.data = (torch.randn(n_out, GROUP_K[grp], generator=gw, device=device) * 0.02).to(torch.bfloat16)
+            lin.requires_grad_(False)
+            setattr(self.module, name, lin)
+            self.mods.append((name, lin, grp))
+        self.W0 = {name: lin.weight.data.clone() for name, lin, _ in self.mods}
+
+
 class LayerBench:
-    def __init__(self, rank, world, tokens_per_call, seqs, device):
+    """One step = the product's own calls for one decoder layer: ``GPTQModifier.calibrate_module``
+    (the forward hook) for every module and calibration chunk, ``on_sequential_epoch_end`` (observe,
+    and ``compress_modules``: owner assignment, Hessian reduction, solves, broadcast - all of
+    llm_compressor_b200.dist), then the int4 pack of the layer's modules."""
+
+    def __init__(self, rank, world, tokens_per_call, seqs, device, solve_streams=4):
         import torch
 
-        from llm_compressor_b200.observers import MemorylessMinMaxObserver
-        from llm_compressor_b200.quant_args import QuantizationArgs
+        from llm_compressor_b200 import GPTQModifier
 
         self.torch = torch
         self.rank, self.world, self.dev = rank, world, device
-        self.qargs = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128)
-        self.Observer = MemorylessMinMaxObserver
         # this rank's share of the calibration sequences (src/llmcompressor/datasets/utils.py:244-253)
         lo, hi = (seqs * rank) // world, (seqs * (rank + 1)) // world
         self.local_seqs, self.total_seqs = hi - lo, seqs
@@ -209,111 +246,66 @@ class LayerBench:
                 t1 = min(self.local_tokens, t0 + 65536)
                 x[t0:t1] = (torch.randn(t1 - t0, K, generator=g, device=device) * colscale).to(torch.bfloat16)
             self.X[name] = x
-        gw = torch.Generator(device=device).manual_seed(0)
-        self.mods = []
-        for name, n_out, grp in MODULES:
-            lin = torch.nn.Linear(GROUP_K[grp], n_out, bias=False, device=device, dtype=torch.bfloat16)
-            lin.weight.data = (torch.randn(n_out, GROUP_K[grp], generator=gw, device=device) * 0.02).to(torch.bfloat16)
-            lin.requires_grad_(False)
-            self.mods.append((name, lin, grp))
-        self.H = {g_: torch.zeros(K, K, dtype=torch.float32, device=device) for g_, K in GROUP_K.items()}
-        # owners of the Hessian groups: greedy bin packing by K, heaviest first
-        loads, self.owner = [0] * world, {}
-        for g_ in sorted(GROUP_K, key=lambda n: -GROUP_K[n]):
-            r = loads.index(min(loads))
-            self.owner[g_] = r
-            loads[r] += GROUP_K[g_] ** 3
-        self.syrk_events = []
-        self.phase_events = []
-        self.job_events = []
-        self.streams = 4
+        self.layer = _Layer(torch, device)
+        self.modifier = GPTQModifier(targets="Linear", scheme="W4A16", actorder=None, block_size=128,
+                                     dampening_frac=0.01, parallel_streams=solve_streams,
+                                     hessian_stage_tokens=self.tokens_per_call)
+        self.modifier.on_initialize(self.layer.module)
+        self.qargs = self.layer.mods[0][1].quantization_scheme.weights
+        self.syrk_events, self.phase_events, self.job_events = [], [], []
+        self._record = False
+        self.modifier.trace = self._trace
 
-    def step(self, from_host=None, record=False):
+    def _trace(self, event, module):
+        if not self._record:
+            return
+        ev = self.torch.cuda.Event(enable_timing=True)
+        ev.record()
+        if event.startswith("job_"):
+            grp = next(g_ for _, lin, g_ in self.layer.mods if lin is module)
+            self.job_events.append((self._step_index, grp, event[4:], ev))
+        else:
+            self.phase_events.append((self._step_index, event, ev))
+
+    def step(self, from_host=None, record=False, index=0):
         """One decoder layer.  `from_host`: HostFeeder supplying activation chunks from pinned
         host memory (end-to-end arm); otherwise activations are resident in HBM."""
         torch = self.torch
-        from llm_compressor_b200 import compressors, gptq
-        from llm_compressor_b200.streams import run_concurrent
-        import torch.distributed as dist
+        from llm_compressor_b200 import compressors
 
-        def mark():
-            if record:
-                ev = torch.cuda.Event(enable_timing=True)
-                ev.record()
-                self.phase_events.append(ev)
-
-        mark()
-        for g_, H in self.H.items():
-            H.zero_()
-        n = {g_: 0 for g_ in self.H}
+        self._record, self._step_index = record, index
+        mod = self.modifier
+        for name, lin, _ in self.layer.mods:   # the previous step left its quantised weights here
+            lin.weight.data.copy_(self.layer.W0[name])
+        self._trace("begin", None)
+        mod.on_calibration_start(self.layer.module)
         for g_, K in GROUP_K.items():
             X = self.X[g_]
+            members = [lin for _, lin, grp in self.layer.mods if grp == g_]
             for t0 in range(0, self.local_tokens, self.tokens_per_call):
                 t1 = min(self.local_tokens, t0 + self.tokens_per_call)
                 chunk = from_host.next_chunk(g_, t0, t1) if from_host is not None else X[t0:t1]
-                seqs = (t1 - t0) // SEQ_LEN
+                batch = chunk.view((t1 - t0) // SEQ_LEN, SEQ_LEN, K)
                 if record:
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record()
-                gptq.accumulate_hessian_lower(chunk.view(seqs, SEQ_LEN, K), self.H[g_], 0)
+                for lin in members:   # the hook of every module that receives this tensor
+                    mod.calibrate_module(lin, (batch,), None)
                 if record:
                     e1.record()
                     self.syrk_events.append((e0, e1, t1 - t0, K))
                 if from_host is not None:
                     from_host.release(chunk)
-                n[g_] += seqs
-        mark()
-        if self.world > 1:
-            for g_ in self.H:
-                dist.reduce(self.H[g_], dst=self.owner[g_], op=dist.ReduceOp.SUM)
-        mark()
+        mod.on_sequential_epoch_end(self.layer.module, list(self.layer.module.modules()))
+        mod.on_calibration_end(self.layer.module)
         results = {}
-
-        def stamp(g_, what):
-            if record:
-                ev = torch.cuda.Event(enable_timing=True)
-                ev.record()
-                self.job_events.append((len(self.phase_events) // 4, g_, what, ev))
-
-        def solve(g_):
-            # queued without waiting for the device; status and losses are read at the end
-            stamp(g_, "start")
-            gptq.finalize_hessian(self.H[g_], self.total_seqs)
-            factor = gptq.factor_hessian(self.H[g_], percdamp=0.01, actorder=None, defer=True)
-            stamp(g_, "factored")
-            queued = []
-            for name, lin, grp in self.mods:
-                if grp != g_:
-                    continue
-                lin.weight_observer = self.Observer("weight", self.qargs)
-                lin.weight_observer(lin.weight.data)
-                loss, out = gptq.quantize_weight(lin, self.qargs, None, blocksize=128, percdamp=0.01, factor=factor,
-                                                 defer=True)
+        if self.rank == 0:   # the save path packs on the writing rank
+            for name, lin, _ in self.layer.mods:
                 packed = compressors.compress_state_dict(
-                    {"weight": out["weight"], "weight_scale": out["weight_scale"],
-                     "weight_zero_point": out["weight_zero_point"]}, self.qargs)
-                queued.append((name, loss, out["weight"], packed))
-            stamp(g_, "swept")
-            if not factor.resolve().ok:
-                raise RuntimeError("synthetic Hessian of %s is not positive definite" % g_)
-            self.H[g_] = factor.U
-            for name, loss, w, packed in queued:
-                results[name] = (float(loss), w, packed)
-
-        # the solves of different Hessians are independent chains of small launches: they run
-        # concurrently on side streams (widest Hessian first), as GPTQModifier runs them
-        mine = sorted((g_ for g_ in GROUP_K if self.owner[g_] == self.rank), key=lambda g_: -GROUP_K[g_])
-        run_concurrent([lambda g_=g_: solve(g_) for g_ in mine], self.dev, max_streams=self.streams)
-        if self.world > 1:
-            # every rank needs the fake-quantised weights to propagate activations
-            # (src/llmcompressor/utils/dist.py:55-88)
-            for name, lin, grp in self.mods:
-                if name in results:
-                    buf = results[name][1]
-                else:
-                    buf = torch.empty_like(lin.weight.data)
-                dist.broadcast(buf, src=self.owner[grp])
-        mark()
+                    {"weight": lin.weight.data, "weight_scale": lin.weight_scale.data,
+                     "weight_zero_point": lin.weight_zero_point.data}, self.qargs)
+                results[name] = (mod.losses.get(name), lin.weight.data, packed)
+        self._trace("end", None)
         return results
 
 
@@ -372,6 +364,52 @@ class HostFeeder:
         chunk._feeder_free.record(self.torch.cuda.current_stream())
 
 
+def parity_check(bench, snapshot, losses):
+    """Ties the timed numbers to verified output: k_proj (1024 x 4096) of the last timed step against
+    the CPU oracle on the same weight and the same calibration tokens, and the rank-k update against
+    the oracle's Hessian on a 4096-token sample.  Runs after the timed regions, on every rank for the
+    collective and on rank 0 for the comparison."""
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from llm_compressor_b200 import gptq
+
+    t_start = time.perf_counter()
+    K = HIDDEN
+    X = bench.X["attn_in"]
+    H = torch.zeros(K, K, dtype=torch.float32, device=bench.dev)
+    for t0 in range(0, bench.local_tokens, bench.tokens_per_call):
+        t1 = min(bench.local_tokens, t0 + bench.tokens_per_call)
+        gptq.accumulate_hessian_lower(X[t0:t1].view(-1, SEQ_LEN, K), H, 0)
+    if bench.world > 1:
+        dist.all_reduce(H)
+    gptq.finalize_hessian(H, bench.total_seqs)
+    if bench.rank != 0:
+        return None
+    spec = oracle.preset("W4A16")
+    w0 = bench.layer.W0["k_proj"].cpu()
+    loss_ref, ref = oracle.quantize_weight(w0, spec, H.cpu())
+    wq, scale = snapshot
+    code_match = float((wq.cpu().view(torch.int16) == ref["weight"].view(torch.int16)).float().mean())
+    scale_equal = bool(torch.equal(scale.cpu().view(torch.int16), ref["weight_scale"].view(torch.int16)))
+    loss = losses.get("k_proj")
+    # Hessian of a 4096-token sample, oracle on the host against the kernel
+    xs = X[:4096]
+    Hs = torch.zeros(K, K, dtype=torch.float32, device=bench.dev)
+    gptq.accumulate_hessian_lower(xs.view(2, SEQ_LEN, K), Hs, 0)
+    gptq.finalize_hessian(Hs, 1)
+    Ho, _ = oracle.accumulate_hessian(xs.cpu().view(2, SEQ_LEN, K), oracle.make_empty_hessian(K), 0)
+    herr = float((Hs.cpu().double() - Ho.double()).norm() / Ho.double().norm())
+    return {"module": "k_proj 1024x4096 of the last timed step, against the CPU oracle",
+            "code_match": round(code_match, 6), "scale_equal": scale_equal,
+            "loss_rel": None if loss is None else round(abs(loss - loss_ref) / abs(loss_ref), 6),
+            "hessian_rel_fro_4096_tokens": herr,
+            "ok": bool(code_match >= 0.995 and scale_equal and herr < 1e-3 and
+                       (loss is None or abs(loss - loss_ref) <= 0.01 * abs(loss_ref))),
+            "seconds": round(time.perf_counter() - t_start, 1)}
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -390,8 +428,7 @@ def run_b200(args):
     lib = _lib.load()
     peaks = load_peaks()
     seqs = args.seqs
-    bench = LayerBench(rank, world, args.tokens_per_call, seqs, dev)
-    bench.streams = args.solve_streams
+    bench = LayerBench(rank, world, args.tokens_per_call, seqs, dev, solve_streams=args.solve_streams)
 
     def barrier():
         if world > 1:
@@ -412,13 +449,11 @@ def run_b200(args):
     sampler.ready.wait(timeout=10)
     launches0 = lib.b200q_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    bench.syrk_events = []
-    bench.phase_events = []
-    bench.job_events = []
+    bench.syrk_events, bench.phase_events, bench.job_events = [], [], []
     barrier()
     e0.record()
-    for _ in range(args.steps):
-        results = bench.step(record=True)
+    for i in range(args.steps):
+        results = bench.step(record=True, index=i)
     e1.record()
     barrier()
     launches = lib.b200q_launch_count() - launches0
@@ -429,8 +464,15 @@ def run_b200(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / args.steps
-    scale = (SEQS / seqs)  # 1 unless a reduced calibration set was asked for
     value = ms_per_step / 1e3 * LAYERS
+    # what the parity check compares: k_proj as the last timed step left it
+    kp = dict((n, l) for n, l, _ in bench.layer.mods)["k_proj"]
+    snapshot = (kp.weight.data.clone(), kp.weight_scale.data.clone())
+    losses = dict(bench.modifier.losses)
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, losses)
+        losses = {k: v for d in gathered for k, v in d.items()}
 
     # dominant kernel: the SYRK; achieved = algorithmic flops / CUDA-event time of its launches
     syrk_ms = sum(a.elapsed_time(b) for a, b, _, _ in bench.syrk_events)
@@ -438,30 +480,39 @@ def run_b200(args):
     achieved = syrk_flops / (syrk_ms * 1e-3) / 1e12 if syrk_ms > 0 else 0.0
     roofline = {"bound": "tensor", "kernel": "syrk_pair_kernel (tcgen05 cta_group::2)", "achieved": achieved, "peak": peaks["tflops"],
                 "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
-                # dram__bytes_read.sum + dram__bytes_write.sum of one ncu-captured launch (K=4096, T=32768;
-                # profiles/syrk_pair_kernel_K4096_T32768.md); the K=14336 launches were not captured
-                "traffic": 620.0e6, "traffic_note": "bytes per K=4096 launch of 32768 tokens, from the ncu capture; "
-                                                    "algorithmic 2TK + 4K(K+1) = 336e6",
+                # dram__bytes_read.sum + dram__bytes_write.sum of ncu-captured launches, weighted by
+                # how often each width runs in a step
+                "traffic": SYRK_TRAFFIC["per_launch_weighted"], "traffic_note": SYRK_TRAFFIC["note"],
                 "peak_source": peaks["source"] + " bf16_tflops_sustained",
                 "share_of_step": syrk_ms / ms if ms else None,
                 "launches": len(bench.syrk_events)}
 
-    # device time of the step's phases (mean per step): Hessian accumulation, the reduce to the
-    # owners, and the solve (factorise, sweep, pack, broadcast)
-    pe = bench.phase_events
-    phases = {"hessian": 0.0, "reduce": 0.0, "solve": 0.0}
-    solve_steps = [round(pe[i + 2].elapsed_time(pe[i + 3]), 1) for i in range(0, len(pe) - 3, 4)]
-    for i in range(0, len(pe) - 3, 4):
-        phases["hessian"] += pe[i].elapsed_time(pe[i + 1]) / args.steps
-        phases["reduce"] += pe[i + 1].elapsed_time(pe[i + 2]) / args.steps
-        phases["solve"] += pe[i + 2].elapsed_time(pe[i + 3]) / args.steps
+    # device time of the step's phases (mean per step): Hessian accumulation (hook calls, weight
+    # observers), the reduction to the owners, the solve (factorise, sweep) and the broadcast + pack
+    phases = {"hessian": 0.0, "reduce": 0.0, "solve": 0.0, "broadcast_pack": 0.0}
+    solve_steps = []
+    by_step = {}
+    for idx, name, ev in bench.phase_events:
+        by_step.setdefault(idx, {})[name] = ev
+    for idx in sorted(by_step):
+        evs = by_step[idx]
+        if not {"begin", "solve", "done", "end"} <= set(evs):
+            continue
+        first = evs.get("reduce", evs["solve"])
+        phases["hessian"] += evs["begin"].elapsed_time(first) / args.steps
+        if "reduce" in evs:
+            phases["reduce"] += evs["reduce"].elapsed_time(evs["solve"]) / args.steps
+        solve_end = evs.get("broadcast", evs["done"])
+        phases["solve"] += evs["solve"].elapsed_time(solve_end) / args.steps
+        phases["broadcast_pack"] += solve_end.elapsed_time(evs["end"]) / args.steps
+        solve_steps.append(round(evs["solve"].elapsed_time(solve_end), 1))
 
-    # device time line of the last timed step's solve jobs, ms after the solve phase began:
-    # {group: [start, factored, swept]}
+    # device time line of the last timed step's solve jobs on this rank, ms after the solve phase
+    # began: {group: [start, factored, swept]}
     jobs = {}
-    if len(pe) >= 4:
-        t0 = pe[len(pe) - 2]
-        last = len(pe) // 4 - 1
+    last = args.steps - 1
+    if last in by_step and "solve" in by_step[last]:
+        t0 = by_step[last]["solve"]
         for step_i, g_, what, ev in bench.job_events:
             if step_i == last:
                 jobs.setdefault(g_, []).append(round(t0.elapsed_time(ev), 1))
@@ -503,13 +554,23 @@ def run_b200(args):
         e2e = {"value": ms_e2e / 1e3 * LAYERS, "unit": "s", "h2d_bytes_per_step": feeder.h2d_bytes,
                "d2h_bytes_per_step": d2h_bytes, "steps": steps_e2e,
                "host_pool_fraction": round(feeder.pool_fraction, 3)}
+        del feeder, host_out
+
+    parity = None
+    if not args.no_parity:
+        try:
+            parity = parity_check(bench, snapshot, losses)
+        except Exception as e:  # noqa: BLE001 - the timing line must still be printed
+            parity = {"ok": False, "error": f"{type(e).__name__}: {e}"}
 
     # quantize / pack kernels (the metric's "pack GB/s"), rank 0, after the timed region
     pack = None
     if rank == 0 and not args.no_pack:
         del results
+        bench.X.clear()
         flush = torch.empty(8, dtype=torch.uint8, device=dev)
-        pack = {r["kernel"]: {"gbs": round(r["gbs"], 1), "frac_of_hbm_peak": round(r["frac_of_hbm_peak"], 3)}
+        pack = {r["kernel"]: {"gbs": round(r["gbs"], 1), "frac_of_hbm_peak": round(r["frac_of_hbm_peak"], 3),
+                              "bytes_per_elem": r["bytes_per_elem"], "moved_bytes_per_elem": r.get("moved_bytes_per_elem")}
                 for r in pack_micro(5, peaks, make_timed(flush), torch.Generator(device=dev).manual_seed(0), dev)}
 
     cpu = None
@@ -522,13 +583,11 @@ def run_b200(args):
             "metric": METRIC, "value": value, "unit": "s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "configs[2]: GPTQ W4A16 g128 (sym int4, block 128, damp 0.01, no act-order), "
-                                   "Llama-3-8B shapes, %d x %d calibration tokens" % (seqs, SEQ_LEN),
-                       "step": "one decoder layer: 4 Hessians over all tokens + 7 modules observe/factor/sweep/pack",
-                       "layers": LAYERS, "tokens_per_syrk_call": bench.tokens_per_call,
-                       "l2": "inputs larger than L2 (tens of GB streamed per step)",
-                       "calibration_scale": scale},
-            "phases_ms": phases, "solve_ms_per_step": solve_steps, "solve_jobs_ms": jobs, "roofline": roofline, "pack_gbs": pack, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "config": workload_config(seqs, args.tokens_per_call),
+            "product_path": "GPTQModifier.calibrate_module / on_sequential_epoch_end / compress_modules "
+                            "(llm_compressor_b200.dist owner assignment, reduction, broadcast)",
+            "phases_ms": phases, "solve_ms_per_step": solve_steps, "solve_jobs_ms": jobs, "roofline": roofline,
+            "parity_check": parity, "pack_gbs": pack, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks,
             "published_reference": {"value": 745.03, "unit": "s", "note": "whole oneshot incl. model forwards, "
                                     "GPU not stated (docs/guides/big_models_and_distributed/distributed_oneshot.md:107-111)"},
@@ -539,14 +598,22 @@ def run_b200(args):
 
 
 def pack_micro(steps, peaks, timed, g, dev):
-    """Quantize / pack kernels on a 16384 x 8192 bf16 matrix: GB/s of algorithmic bytes and the
-    fraction of the measured HBM copy bandwidth."""
+    """Quantize / pack kernels on a 16384 x 8192 bf16 matrix, and the NVFP4 / MXFP4 weight path on
+    the two large Llama-3-8B matrices with 0.1 % outliers: GB/s of ALGORITHMIC bytes (the weight
+    read, the codes and the stored scale bytes; the bf16 copy of the scales that the module keeps
+    is extra and listed as moved bytes) and the fraction of the measured HBM copy bandwidth."""
     import torch
 
     from llm_compressor_b200 import ops
     from llm_compressor_b200.quant_args import QuantizationArgs, preset_name_to_scheme
 
     results = []
+
+    def add(name, N, K, ms, bpe, moved):
+        gbs = bpe * N * K / (ms * 1e-3) / 1e9
+        results.append({"kernel": name, "N": N, "K": K, "ms": ms, "gbs": gbs, "bytes_per_elem": bpe,
+                        "moved_bytes_per_elem": moved, "frac_of_hbm_peak": gbs / peaks["hbm"]})
+
     # two 256 MiB inputs used in turn: each launch reads data the previous launch evicted
     # from L2 (126 MB); an explicit flush would leave dirty lines whose write-back would be
     # charged to these short kernels
@@ -558,32 +625,47 @@ def pack_micro(steps, peaks, timed, g, dev):
         turn[0] ^= 1
         return ws[turn[0]]
     w = ws[0]
-    cases = [("rtn_int4_g128", "W4A16", 2 + 0.5 + 2 / 128), ("rtn_mxfp4", "MXFP4A16", 2 + 0.5 + 1 / 32 + 2 / 32),
-             ("rtn_mxfp8", "MXFP8A16", 2 + 1 + 1 / 32 + 2 / 32), ("rtn_fp8_channel", "FP8_DYNAMIC", 3.0)]
-    for name, preset, bpe in cases:
+    # (name, preset, algorithmic bytes per element, bytes actually moved per element)
+    cases = [("rtn_int4_g128", "W4A16", 2 + 0.5 + 2 / 128, 2 + 0.5 + 2 / 128 + 1 / 128),
+             ("rtn_mxfp4", "MXFP4A16", 2 + 0.5 + 1 / 32, 2 + 0.5 + 1 / 32 + 2 / 32 + 1 / 32),
+             ("rtn_mxfp8", "MXFP8A16", 2 + 1 + 1 / 32, 2 + 1 + 1 / 32 + 2 / 32 + 1 / 32),
+             ("rtn_fp8_channel", "FP8_DYNAMIC", 3.0, 3.0)]
+    for name, preset, bpe, moved in cases:
         a = preset_name_to_scheme(preset, ["Linear"]).weights
         ms = timed(lambda: ops.rtn_quantize_pack(nxt(), a), steps, do_flush=False)
-        gbs = bpe * N * K / (ms * 1e-3) / 1e9
-        results.append({"kernel": name, "N": N, "K": K, "ms": ms, "gbs": gbs, "bytes_per_elem": bpe,
-                               "frac_of_hbm_peak": gbs / peaks["hbm"]})
+        add(name, N, K, ms, bpe, moved)
     a4 = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128)
     mn, mx = ops.observe_minmax(w, a4)
     scale, zp = ops.qparams(mn, mx, a4)
     ms = timed(lambda: ops.quantize_pack(nxt(), scale, zp, a4), steps, do_flush=False)
-    bpe = 2 + 0.5 + 2 / 128
-    results.append({"kernel": "pack_int4_g128_given_scale", "N": N, "K": K, "ms": ms,
-                           "gbs": bpe * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": bpe,
-                           "frac_of_hbm_peak": bpe * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
+    add("pack_int4_g128_given_scale", N, K, ms, 2 + 0.5 + 2 / 128, 2 + 0.5 + 2 / 128)
     ms = timed(lambda: ops.observe_minmax(nxt(), a4), steps, do_flush=False)
-    results.append({"kernel": "observe_minmax_g128", "N": N, "K": K, "ms": ms,
-                           "gbs": 2.0 * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": 2.0,
-                           "frac_of_hbm_peak": 2.0 * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
+    add("observe_minmax_g128", N, K, ms, 2.0, 2.0 + 4 / 128)
     gs = torch.tensor([1000.0], device=dev)
     ms = timed(lambda: ops.nvfp4_quantize_pack(nxt(), gs), steps, do_flush=False)
-    bpe = 2 + 0.5 + 1 / 16 + 2 / 16
-    results.append({"kernel": "nvfp4_given_global_scale", "N": N, "K": K, "ms": ms,
-                           "gbs": bpe * N * K / (ms * 1e-3) / 1e9, "bytes_per_elem": bpe,
-                           "frac_of_hbm_peak": bpe * N * K / (ms * 1e-3) / 1e9 / peaks["hbm"]})
+    add("nvfp4_given_global_scale", N, K, ms, 2 + 0.5 + 1 / 16, 2 + 0.5 + 1 / 16 + 2 / 16)
+    del ws, w, mn, mx, scale, zp
+
+    # the data-free FP4 weight path on the MLP matrices of Llama-3-8B (0.1 % of the entries replaced
+    # by N(0, 0.5) outliers): NVFP4 needs the tensor-wide amax first, hence two reads of the weight
+    for (n_, k_) in ((INTER, HIDDEN), (HIDDEN, INTER)):
+        pair = []
+        for _ in range(3):   # 3 x 117 MB: each launch reads a matrix that has left L2
+            m = torch.randn(n_, k_, generator=g, device=dev) * 0.02
+            idx = torch.randint(0, n_ * k_, (n_ * k_ // 1000,), generator=g, device=dev)
+            m.view(-1)[idx] = torch.randn(idx.numel(), generator=g, device=dev) * 0.5
+            pair.append(m.to(torch.bfloat16))
+        cyc = [0]
+
+        def nx():
+            cyc[0] = (cyc[0] + 1) % len(pair)
+            return pair[cyc[0]]
+        ms = timed(lambda: ops.nvfp4_two_pass(nx()), steps, do_flush=False)
+        add(f"nvfp4_two_pass_{n_}x{k_}", n_, k_, ms, 2 * 2 + 0.5 + 1 / 16, 2 * 2 + 0.5 + 1 / 16 + 2 / 16)
+        amx = preset_name_to_scheme("MXFP4A16", ["Linear"]).weights
+        ms = timed(lambda: ops.rtn_quantize_pack(nx(), amx), steps, do_flush=False)
+        add(f"rtn_mxfp4_{n_}x{k_}", n_, k_, ms, 2 + 0.5 + 1 / 32, 2 + 0.5 + 1 / 32 + 2 / 32 + 1 / 32)
+        del pair
     return results
 
 
@@ -693,6 +775,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-pack", action="store_true", help="skip the quantize/pack kernel figures")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the last timed step")
     args = ap.parse_args()
     if args.micro:
         run_micro(args)

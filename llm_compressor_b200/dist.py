@@ -59,19 +59,24 @@ def reduce_hessians(groups: Sequence, group_to_rank: dict) -> None:
     """Sum each group's partial Hessian and sample count onto its owner; other ranks drop
     theirs.  ``groups`` have attributes ``H`` (float32 [K,K]) and ``n``."""
     me = rank()
-    pending, counts = [], []
+    pending = []
+    if not groups:
+        return
+    dev = None
     for g in groups:
         dst = group_to_rank[g]
         H = g.H if g.H.device.type != "cpu" or dist.get_backend() == "gloo" else g.H.to(g.device)
         g.H = H
+        dev = H.device
         pending.append(dist.reduce(H, dst=dst, op=dist.ReduceOp.SUM, async_op=True))
-        n = torch.tensor([float(g.n)], dtype=torch.float32, device=H.device)
-        pending.append(dist.reduce(n, dst=dst, op=dist.ReduceOp.SUM, async_op=True))
-        counts.append((g, n, dst))
+    # every sample count in one collective and one read
+    counts = torch.tensor([float(g.n) for g in groups], dtype=torch.float32, device=dev)
+    pending.append(dist.all_reduce(counts, op=dist.ReduceOp.SUM, async_op=True))
     wait_for_comms(pending)
-    for g, n, dst in counts:
-        if dst == me:
-            g.n = float(n.item())
+    totals = counts.tolist()
+    for g, n in zip(groups, totals):
+        if group_to_rank[g] == me:
+            g.n = n
         else:
             g.H = None
 

@@ -318,6 +318,7 @@ class GPTQModifier(QuantizationMixin):
         self.hessian_stage_tokens = hessian_stage_tokens
         self._groups: dict = {}        # module -> _HessianGroup
         self._num_samples: dict = {}   # module -> None (membership: modules awaiting compression)
+        self.trace = None              # optional callback(event: str, module | None) for instrumentation
         self._hooked: list = []        # every module that got a calibration hook
         self._done: set = set()        # modules whose quantised weight has been written
         self.losses: dict = {}
@@ -360,6 +361,7 @@ class GPTQModifier(QuantizationMixin):
 
     def on_calibration_start(self, model, **_):
         self.start_calibration(model)
+        self._hooked, self._done = [], set()   # a fresh calibration
         added = False
         for _, module in self.quantized_modules(model):
             if isinstance(module, torch.nn.Embedding):
@@ -412,10 +414,16 @@ class GPTQModifier(QuantizationMixin):
         observe(mods, "weight")
         self.compress_modules(mods)
 
+    def _trace(self, event, module=None):
+        if self.trace is not None:
+            self.trace(event, module)
+
     def compress_modules(self, modules=None):
         modules = list(self._num_samples.keys()) if modules is None else list(modules)
         if not bdist.is_distributed():
+            self._trace("solve")
             self.compress_module_list(modules)
+            self._trace("done")
             return
         # owners by Hessian width over the distinct Hessians (base.py:306-318)
         groups = list({id(self._groups[m]): self._groups[m] for m in modules}.values())
@@ -423,10 +431,13 @@ class GPTQModifier(QuantizationMixin):
                                                            item_weight_fn=lambda g: g.H.shape[0])
         for g in items:
             g.flush()   # staged calibration tokens
+        self._trace("reduce")
         bdist.reduce_hessians(items, to_rank)
         mod_rank = {m: to_rank[self._groups[m]] for m in modules}   # before the solve drops the groups
         mine = [m for m in modules if mod_rank[m] == bdist.rank()]
+        self._trace("solve")
         self.compress_module_list(mine)
+        self._trace("broadcast")
         bdist.broadcast_module_params(modules, mod_rank, ("weight", "weight_scale", "weight_zero_point",
                                                           "weight_g_idx", "weight_global_scale"))
         for m in modules:
@@ -434,6 +445,7 @@ class GPTQModifier(QuantizationMixin):
             self._groups.pop(m, None)
             m.quantization_status = "frozen"
             self._done.add(m)
+        self._trace("done")
 
     def compress_module_list(self, module_list):
         """Quantise the modules; the modules of one Hessian form a job (one factorisation per
@@ -459,6 +471,7 @@ class GPTQModifier(QuantizationMixin):
         queued = []
         hess_status = {}
         t0 = time.perf_counter()
+        self._trace("job_start", module_list[0])
         for module in module_list:
             group = self._groups.pop(module)
             hess_status[id(group)] = group.status
@@ -468,11 +481,13 @@ class GPTQModifier(QuantizationMixin):
                 left.discard(qargs.actorder)
                 H = group.finalized(keep=bool(left))  # factor_hessian consumes its argument
                 factors[qargs.actorder] = gptq.factor_hessian(H, self.dampening_frac, qargs.actorder, defer=True)
+                self._trace("job_factored", module)
             factor = factors[qargs.actorder]
             with torch.no_grad():
                 loss, out = gptq.quantize_weight(module, qargs, None, blocksize=self.block_size,
                                                  percdamp=self.dampening_frac, factor=factor, defer=True)
             queued.append((module, qargs, factor, loss, out))
+        self._trace("job_swept", module_list[0])
         # one read for every device status word of the job (the first wait for the device)
         words = [s for s in (out.pop("_status", None) for _, _, _, _, out in queued) if s is not None]
         words += [s for s in hess_status.values() if s is not None]

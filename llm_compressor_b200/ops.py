@@ -240,6 +240,24 @@ def nvfp4_quantize_pack(w, global_scale: torch.Tensor):
     return dict(scale=scale, scale_store=store.view(torch.float8_e4m3fn), codes=out)
 
 
+def nvfp4_two_pass(w, partners=()):
+    """NVFP4 weight quantisation from nothing but the weight: pass 1 finds the tensor-wide
+    largest magnitude (over ``w`` and the ``partners`` that share its global scale: q/k/v,
+    gate/up) and turns it into the global scale, pass 2 is ``nvfp4_quantize_pack``.  Returns its
+    dict plus ``global_scale``."""
+    from .quant_args import QuantizationArgs
+    _need_cuda(w, *partners)
+    targs = QuantizationArgs(num_bits=4, type="float", symmetric=True, strategy="tensor")
+    absmax = torch.zeros(1, dtype=torch.float32, device=w.device)
+    for t in (w, *partners):
+        mn, mx = observe_minmax(t, targs)
+        absmax_accumulate(mn, mx, absmax)
+    gs = global_scale_from_absmax(absmax, w.dtype)
+    out = nvfp4_quantize_pack(w, gs)
+    out["global_scale"] = gs
+    return out
+
+
 # ------------------------------------------------------------------------------- Hessian
 def hessian_syrk(x: torch.Tensor, H: torch.Tensor, alpha: float = 2.0, status=None):
     """H_lower += alpha * x^T x ; x [T,K] bf16 with contiguous rows.  ``status`` (int32 device

@@ -324,3 +324,52 @@ def test_lookahead_is_bitwise_equal_to_single_stream(tmp_path):
     for _ in range(3):
         U1, W1, L1 = _solve_fingerprint(K, N)
         assert torch.equal(U0, U1) and torch.equal(W0, W1) and torch.equal(L0, L1)
+
+
+# ------------------------------------------------------------------------------- act-order ranking
+def test_actorder_perm_is_a_permutation_for_any_diagonal():
+    """NaN, infinities, signed zeros and ties: the ranking is total, so the result is always a
+    permutation, in torch's order (NaN first when descending, ties by index)."""
+    K = 1500
+    g = torch.Generator().manual_seed(0)
+    d = torch.randn(K, generator=g).abs()
+    d[5] = float("nan"); d[700] = float("nan"); d[1499] = -float("nan")
+    d[9] = float("inf"); d[10] = 0.0; d[11] = -0.0; d[12] = 0.0; d[40] = d[41] = d[1000] = 0.75
+    H = torch.zeros(K, K)
+    H[torch.arange(K), torch.arange(K)] = d
+    perm = ops.actorder_perm(H.to(DEV)).cpu().long()
+    assert torch.equal(torch.sort(perm).values, torch.arange(K))
+    ref = torch.argsort(d, descending=True, stable=True)
+    assert torch.equal(perm, ref)
+    # the gathers and the scatter keep their indices inside the matrix even for a bad map
+    bad = torch.tensor([0, 5, -3, 9999], dtype=torch.int32, device=DEV)
+    w = torch.arange(8, dtype=torch.float32, device=DEV).reshape(2, 4)
+    out = ops.gather_columns_f32(w, bad)
+    assert out.shape == (2, 4) and bool(torch.isfinite(out).all())
+
+
+def test_hessian_width_not_a_multiple_of_eight():
+    x = synth_acts(2, 90, 100, seed=11)
+    H_ref, n_ref = oracle.accumulate_hessian(x, oracle.make_empty_hessian(100), 0)
+    lin = torch.nn.Linear(100, 4, bias=False, device=DEV)
+    H, n = gptq.accumulate_hessian(x.to(DEV), lin, gptq.make_empty_hessian(lin), 0)
+    assert n == n_ref == 2
+    assert rel_fro(H, H_ref) < HESSIAN_RTOL
+    assert torch.equal(H, H.t())
+
+
+def test_sweep_and_hessian_status_words_stay_zero():
+    K, N = 512, 64
+    a = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128)
+    x = synth_acts(1, 1024, K, seed=2).to(DEV)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    H = torch.zeros(K, K, device=DEV)
+    ops.hessian_syrk(x.reshape(-1, K), H, 2.0, status=st)
+    ops.hessian_finalize(H, 1.0)
+    ops.gptq_prepare(H, None, 0.01)
+    assert ops.gptq_factor(H) == 0
+    W = (synth_weight(N, K, seed=1).to(DEV)).float()
+    mn, mx = ops.observe_minmax(W.to(torch.bfloat16), a)
+    scale, zp = ops.qparams(mn, mx, a)
+    losses, st2 = ops.gptq_sweep(W, H, scale, zp, a, return_status=True)
+    assert int(st.item()) == 0 and int(st2.item()) == 0 and bool(torch.isfinite(losses).all())

@@ -269,3 +269,81 @@ def test_all_expert_calibration_shares_one_hessian_per_layer():
     for n in out[0]:
         assert torch.equal(out[0][n], out[1][n]), n
     assert not torch.equal(out[0]["layers.0.experts.0.up_proj.weight"], base.layers[0].experts[0].up_proj.weight.data)
+
+
+def _one_linear_modifier(K=256, N=64, actorder=None, scheme="W4A16"):
+    torch.manual_seed(0)
+    holder = torch.nn.Module()
+    holder.proj = torch.nn.Linear(K, N, bias=False)
+    holder = holder.to(torch.bfloat16).to(DEV)
+    holder.proj.weight.data.normal_(0, 0.02)
+    mod = GPTQModifier(targets="Linear", scheme=scheme, actorder=actorder)
+    mod.on_initialize(holder)
+    mod.on_calibration_start(holder)
+    return holder, mod
+
+
+@pytest.mark.parametrize("actorder", [None, "static", "group"])
+def test_not_positive_definite_hessian_falls_back_to_rtn_through_the_modifier(actorder):
+    """A Hessian whose factorisation fails (made on the host: a negative diagonal entry) must end in
+    the reference's warning and a round-to-nearest result, for every act-order setting."""
+    holder, mod = _one_linear_modifier(actorder=actorder)
+    lin = holder.proj
+    w0 = lin.weight.data.clone()
+    x = torch.randn(2, 64, 256, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(DEV)
+    mod.calibrate_module(lin, (x,), None)
+    grp = mod._groups[lin]
+    grp.flush()
+    grp.H.diagonal().copy_(-grp.H.diagonal().abs() - 1.0)   # not positive definite
+    with pytest.warns(UserWarning, match="Falling back to round-to-nearest"):
+        mod.on_sequential_epoch_end(holder, [lin])
+    mod.on_calibration_end(holder)
+    assert mod.on_finalize(holder)
+    spec = oracle.preset("W4A16", actorder=actorder)
+    # oracle: same Hessian -> Cholesky fails -> identity -> plain round to nearest (with the permutation applied)
+    K = 256
+    xs = x.cpu()
+    H, n = oracle.accumulate_hessian(xs, oracle.make_empty_hessian(K), 0)
+    d = H.diagonal().clone()
+    H.diagonal().copy_(-d.abs() - 1.0)
+    loss_ref, ref = oracle.quantize_weight(w0.cpu(), spec, H / n)
+    assert torch.equal(lin.weight_scale.data.cpu(), ref["weight_scale"])
+    assert mismatch(lin.weight.data, ref["weight"]) <= 0.005
+    assert not torch.equal(lin.weight.data, w0)
+
+
+def test_member_whose_input_diverges_is_reported():
+    torch.manual_seed(0)
+    holder = torch.nn.Module()
+    holder.a = torch.nn.Linear(128, 32, bias=False)
+    holder.b = torch.nn.Linear(128, 32, bias=False)
+    holder = holder.to(torch.bfloat16).to(DEV)
+    mod = GPTQModifier(targets="Linear", scheme="W8A16", actorder=None)
+    mod.on_initialize(holder)
+    mod.on_calibration_start(holder)
+    x = torch.randn(1, 16, 128, device=DEV, dtype=torch.bfloat16)
+    mod.calibrate_module(holder.a, (x,), None)
+    mod.calibrate_module(holder.b, (x,), None)      # same tensor: one shared Hessian
+    assert mod._groups[holder.a] is mod._groups[holder.b]
+    y = torch.randn(1, 16, 128, device=DEV, dtype=torch.bfloat16)
+    mod.calibrate_module(holder.a, (y,), None)
+    with pytest.raises(RuntimeError, match="share_hessians=False"):
+        mod.calibrate_module(holder.b, (y.clone(),), None)
+
+
+def test_targeted_module_behind_the_blocks_is_calibrated_and_unreached_ones_are_reported(tmp_path):
+    base = tiny_llama(seed=6)
+    data = calib(8, 64)
+    recipe = GPTQModifier(targets="Linear", scheme="W8A16", actorder=None)    # lm_head is NOT ignored
+    model = oneshot(copy.deepcopy(base), recipe=recipe, dataset=data)
+    assert "lm_head" in recipe.losses and len(recipe.losses) == 15
+    assert not torch.equal(model.lm_head.weight.data, base.lm_head.weight.data)
+    assert model.lm_head.quantization_status == "frozen"
+    save_compressed_model(model, str(tmp_path / "ok"))
+    # a targeted module that no forward pass reaches: finalisation reports it instead of leaving an
+    # uninitialised scale in the checkpoint
+    broken = copy.deepcopy(base)
+    broken.orphan = torch.nn.Linear(256, 256, bias=False, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="never received calibration data"):
+        oneshot(broken, recipe=GPTQModifier(targets="Linear", scheme="W8A16", ignore=["lm_head"], actorder=None),
+                dataset=data)

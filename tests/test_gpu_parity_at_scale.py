@@ -1,0 +1,233 @@
+"""Parity at the shapes the benchmark runs: the factorisation at K = 4096 and 14336 against the
+float64 chain, Hessian -> factor -> sweep -> pack of Llama-3-8B sized modules against the CPU
+oracle (row slices: rows of a weight are independent in GPTQ, the full K-long chain and the real
+factor U are exercised), and the CPU-runnable 2-layer Llama configuration through ``oneshot()``.
+
+The oracle side of these cases takes tens of seconds each on the host cores."""
+import copy
+
+import pytest
+import torch
+
+import oracle
+from helpers import args_from, bits_equal, mismatch, synth_weight
+from llm_compressor_b200 import GPTQModifier, compressors, gptq, observers, oneshot, ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+CODE_MATCH = 0.995
+LOSS_RTOL = 0.01
+HESSIAN_RTOL = 1e-3
+
+
+def _spd(K, seed):
+    """Seeded Hessian-like matrix made on the device (2 X^T X / n with per-column scales, damped)."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    X = torch.randn(2 * K, K, generator=g, device=DEV) * (0.25 + 2 * torch.rand(K, generator=g, device=DEV))
+    H = (2.0 / X.shape[0]) * (X.t() @ X)
+    H += 0.01 * H.diagonal().mean() * torch.eye(K, device=DEV)
+    return H
+
+
+@pytest.mark.parametrize("K", [4096, 14336])
+def test_factor_matches_float64_at_benchmark_widths(K):
+    H = _spd(K, K)
+    Hc = H.cpu()
+    U = H.clone()
+    assert ops.gptq_factor(U) == 0
+    U = U.cpu().double()
+    Hd = Hc.double()
+    U_ref = torch.linalg.cholesky(torch.cholesky_inverse(torch.linalg.cholesky(Hd)), upper=True)
+    del Hd
+    assert float(U.tril(-1).abs().max()) == 0.0
+    err = float((U - U_ref).norm() / U_ref.norm())
+    # the reference's own float32 chain, for scale
+    U32 = torch.linalg.cholesky(torch.cholesky_inverse(torch.linalg.cholesky(Hc)), upper=True).double()
+    err32 = float((U32 - U_ref).norm() / U_ref.norm())
+    assert err < max(5e-5, 4 * err32), (err, err32)
+    # the defining property at full size: U^T U (H) = I, checked on a random probe
+    g = torch.Generator().manual_seed(1)
+    v = torch.randn(K, 4, generator=g, dtype=torch.float64)
+    r = U.t() @ (U @ (Hc.double() @ v)) - v
+    assert float(r.norm() / v.norm()) < 1e-3
+
+
+def _sequences(K, count, seed, S=2048):
+    """Seeded calibration sequences [1, S, K] bf16 with per-column scales, one at a time (the whole
+    set of the widest case would be several GB of float32 on the host)."""
+    g = torch.Generator().manual_seed(seed)
+    colscale = 0.25 + 2.0 * torch.rand(K, generator=g)
+    for _ in range(count):
+        yield (torch.randn(1, S, K, generator=g) * colscale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("name,N,K", [("gate_proj", 256, 4096), ("down_proj", 256, 14336)])
+def test_llama8b_module_hessian_factor_sweep_pack_vs_oracle(name, N, K):
+    """The whole chain at a real module width, each side on its own: the oracle accumulates its
+    Hessian on the host and solves with it, the device path accumulates its own (half of the
+    sequences one call each, the rest in one large call) and solves with that.  8 K calibration
+    tokens: GPTQ codes react to perturbations of H of the order of float32 rounding when H is
+    barely better than singular (tokens close to K); the named configuration has 73 K tokens."""
+    spec = oracle.preset("W4A16")
+    args = args_from(dict(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128))
+    w = synth_weight(N, K, seed=K // 64)
+    seqs = 8 * K // 2048
+    Href, nref = oracle.make_empty_hessian(K), 0
+    H, n = torch.zeros(K, K, device=DEV), 0
+    rest = []
+    for b, x in enumerate(_sequences(K, seqs, seed=K // 64 + 1)):
+        Href, nref = oracle.accumulate_hessian(x, Href, nref)
+        if b < seqs // 2:
+            H, n = gptq.accumulate_hessian_lower(x.to(DEV), H, n)
+        else:
+            rest.append(x.to(DEV))
+    H, n = gptq.accumulate_hessian_lower(torch.cat(rest, 0), H, n)
+    del rest
+    Href /= nref
+    gptq.finalize_hessian(H, n)
+    assert n == nref == seqs
+    herr = float((H.cpu().double() - Href.double()).norm() / Href.double().norm())
+    assert herr < HESSIAN_RTOL, herr
+    assert torch.equal(H, H.t())
+
+    loss_ref, ref = oracle.quantize_weight(w, spec, Href.clone())
+    packed_ref = oracle.compress_weight({"weight": ref["weight"], "weight_scale": ref["weight_scale"],
+                                         "weight_zero_point": ref["weight_zero_point"]}, spec)
+    lin = torch.nn.Linear(K, N, bias=False, device=DEV, dtype=torch.bfloat16)
+    lin.weight.data = w.to(DEV)
+    lin.weight_observer = observers.MemorylessMinMaxObserver("weight", args)
+    lin.weight_observer(lin.weight.data)
+    loss, out = gptq.quantize_weight(lin, args, H, blocksize=128, percdamp=0.01)
+    assert bits_equal(out["weight_scale"], ref["weight_scale"])
+    mm = mismatch(out["weight"], ref["weight"])
+    assert mm <= 1 - CODE_MATCH, (name, mm)
+    assert loss == pytest.approx(loss_ref, rel=LOSS_RTOL)
+    packed = compressors.compress_state_dict({"weight": out["weight"], "weight_scale": out["weight_scale"],
+                                              "weight_zero_point": out["weight_zero_point"]}, args)
+    a = packed["weight_packed"].cpu().view(torch.uint8)
+    b = packed_ref["weight_packed"].view(torch.uint8)
+    nib = (((a & 0xF) != (b & 0xF)).float().mean() + ((a >> 4) != (b >> 4)).float().mean()) / 2
+    assert float(nib) <= 1 - CODE_MATCH
+    assert packed["weight_shape"].tolist() == [N, K]
+
+
+def test_solve_at_k14336_given_the_same_barely_regular_hessian():
+    """With only 1.5 K tokens (H barely better than singular) the two sides still agree when they
+    are handed the SAME Hessian: what differs between them is the factorisation and the sweep."""
+    K, N = 14336, 256
+    spec = oracle.preset("W4A16")
+    args = args_from(dict(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128))
+    w = synth_weight(N, K, seed=3)
+    H, n = torch.zeros(K, K, device=DEV), 0
+    for x in _sequences(K, 3 * K // 2 // 2048, seed=4):
+        H, n = gptq.accumulate_hessian_lower(x.to(DEV), H, n)
+    gptq.finalize_hessian(H, n)
+    loss_ref, ref = oracle.quantize_weight(w, spec, H.cpu())
+    lin = torch.nn.Linear(K, N, bias=False, device=DEV, dtype=torch.bfloat16)
+    lin.weight.data = w.to(DEV)
+    lin.weight_observer = observers.MemorylessMinMaxObserver("weight", args)
+    lin.weight_observer(lin.weight.data)
+    loss, out = gptq.quantize_weight(lin, args, H, blocksize=128, percdamp=0.01)
+    assert bits_equal(out["weight_scale"], ref["weight_scale"])
+    assert mismatch(out["weight"], ref["weight"]) <= 1 - CODE_MATCH
+    assert loss == pytest.approx(loss_ref, rel=LOSS_RTOL)
+
+
+def test_wide_output_rows_are_independent_of_the_slice():
+    """Rows do not interact in the sweep: a 14336-row module (gate_proj's height) gives, on its
+    first 256 rows, bit for bit what the 256-row slice gives alone."""
+    K, N = 4096, 14336
+    args = args_from(dict(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128))
+    H = _spd(K, 7)
+    factor = gptq.factor_hessian(H, 0.01, None)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    W = (torch.randn(N, K, generator=g, device=DEV) * 0.02).to(torch.bfloat16)
+    outs = []
+    for rows in (N, 256):
+        lin = torch.nn.Linear(K, rows, bias=False, device=DEV, dtype=torch.bfloat16)
+        lin.weight.data = W[:rows].contiguous()
+        lin.weight_observer = observers.MemorylessMinMaxObserver("weight", args)
+        lin.weight_observer(lin.weight.data)
+        _, out = gptq.quantize_weight(lin, args, None, factor=factor)
+        outs.append(out["weight"][:256].clone())
+    assert torch.equal(outs[0], outs[1])
+
+
+# ------------------------------------------------------------------ the CPU-runnable configuration
+def _config0_model():
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(hidden_size=2048, intermediate_size=5632, num_hidden_layers=2, num_attention_heads=32,
+                      num_key_value_heads=4, head_dim=64, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=1e4,
+                      tie_word_embeddings=False, max_position_embeddings=2048)
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16)
+    g = torch.Generator().manual_seed(0)
+    for n, p in model.named_parameters():
+        if "norm" in n:
+            p.data.fill_(1.0)
+        else:
+            p.data.copy_((torch.randn(p.shape, generator=g) * 0.02).to(torch.bfloat16))
+    return model.to(DEV).eval()
+
+
+def test_config0_oneshot_layer0_matches_oracle():
+    """GPTQ W4A16 (g128, block 128, damp 0.01, no act-order) through ``oneshot()`` on the random-init
+    2-layer Llama decoder (hidden 2048, intermediate 5632, 32 / 4 heads), 128 x 512 calibration
+    tokens.  Layer 0 sees the very inputs the oracle-driven procedure sees, so the path's
+    tolerances apply as they are there."""
+    base = _config0_model()
+    data = torch.randint(0, 32000, (128, 512), generator=torch.Generator().manual_seed(1))
+    spec = oracle.preset("W4A16")
+
+    # oracle side: layer 0's inputs from the same device forward, everything else on the CPU
+    layer0 = base.model.layers[0]
+    lin0 = [(n, m) for n, m in layer0.named_modules() if isinstance(m, torch.nn.Linear)]
+    Hs = {m: [None, 0] for _, m in lin0}
+    seen = {}
+
+    def hook(mod, args, _out):
+        x = args[0].detach()
+        key = (x.data_ptr(), x._version)
+        if key not in seen:   # q/k/v and gate/up receive one tensor: transfer it once
+            seen.clear()
+            seen[key] = x.cpu()
+        H, n = Hs[mod]
+        if H is None:
+            H = oracle.make_empty_hessian(mod.weight.shape[1])
+        Hs[mod] = list(oracle.accumulate_hessian(seen[key], H, n))
+
+    class Stop(Exception):
+        pass
+
+    def stop(_m, _a, _o):
+        raise Stop()
+    hooks = [m.register_forward_hook(hook) for _, m in lin0] + [layer0.register_forward_hook(stop)]
+    with torch.no_grad():
+        for row in data:
+            try:
+                base(input_ids=row[None].to(DEV))
+            except Stop:
+                pass
+    for h in hooks:
+        h.remove()
+    ref = {}
+    for n, m in lin0:
+        H, cnt = Hs[m]
+        loss, out = oracle.quantize_weight(m.weight.data.cpu(), spec, H / cnt)
+        ref[n] = (loss, out)
+        Hs[m] = None
+
+    recipe = GPTQModifier(targets="Linear", scheme="W4A16", ignore=["lm_head"], actorder=None, block_size=128,
+                          dampening_frac=0.01)
+    model = oneshot(copy.deepcopy(base), recipe=recipe, dataset=data, num_calibration_samples=128)
+    assert len(recipe.losses) == 14
+    for n, (loss_ref, out_ref) in ref.items():
+        m = dict(model.model.layers[0].named_modules())[n]
+        assert bits_equal(m.weight_scale.data, out_ref["weight_scale"].reshape(m.weight_scale.shape)), n
+        mm = mismatch(m.weight.data, out_ref["weight"])
+        assert mm <= 1 - CODE_MATCH, (n, mm)
+        assert recipe.losses[f"model.layers.0.{n}"] == pytest.approx(loss_ref, rel=LOSS_RTOL), n
+    # layer 1 ran on propagated (quantised) activations: finite losses, weights changed
+    for n, v in recipe.losses.items():
+        assert v == v and 0 < v < float("inf"), n
+    assert not torch.equal(model.model.layers[1].mlp.down_proj.weight.data, base.model.layers[1].mlp.down_proj.weight.data)

@@ -244,3 +244,26 @@ def test_nvfp4_on_rounding_boundaries():
     r = ops.nvfp4_quantize_pack(w.to(DEV), oqp["global_scale"].to(DEV))
     assert bits_equal(r["codes"], ref["weight_packed"]), mismatch(r["codes"], ref["weight_packed"])
     assert bits_equal(r["scale_store"], ref["weight_scale"])
+
+
+@pytest.mark.parametrize("N,K", [(64, 512), (300, 1024)])
+def test_nvfp4_two_pass_equals_observer_then_compressor(N, K):
+    """amax pass + fused NVFP4 pass (alone, and with fused partners sharing the global scale) equals
+    observer -> calculate_qparams -> NVFP4 compressor of the oracle, bit for bit."""
+    spec = oracle.preset("NVFP4A16")
+    w = synth_weight(N, K, seed=N + K)
+    p = synth_weight(N // 2, K, seed=N + K + 1) * 3
+    for partners in ([], [p]):
+        obs = [oracle.WeightObserver(spec) for _ in range(1 + len(partners))]
+        for i, o in enumerate(obs):
+            o.fused = [q for j, q in enumerate(obs) if j != i]
+        for o, t in zip(obs, [w] + partners):
+            o(t)
+        qp = obs[0].get_qparams()
+        ref = oracle.compress_weight({"weight": w, "weight_scale": qp["scale"].to(w.dtype),
+                                      "weight_zero_point": qp["zero_point"],
+                                      "weight_global_scale": qp["global_scale"]}, spec)
+        r = ops.nvfp4_two_pass(w.to(DEV), [t.to(DEV) for t in partners])
+        assert bits_equal(r["global_scale"], qp["global_scale"])
+        assert bits_equal(r["codes"], ref["weight_packed"])
+        assert bits_equal(r["scale_store"], ref["weight_scale"])
