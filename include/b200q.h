@@ -101,9 +101,11 @@ int b200q_qparams(const void* min_vals, const void* max_vals, int stat_dtype, in
 
 /* MSE shrink-grid search over per-group ranges.  Replaces _grid_search_mse /
  * _grid_search_eager / _calculate_error (src/observers/mse_quant.py:19-141,255-284).
- * Writes the best min/max per group (W's dtype).  GROUP / TENSOR_GROUP (group a power of two,
- * 8..256) and CHANNEL strategies.  scratch: b200q_observe_mse_workspace_bytes (per-candidate
- * "some group improved" flags that reproduce the reference's global early stop). */
+ * Writes the best min/max per group (W's dtype).  Strategies: GROUP / TENSOR_GROUP (group a power
+ * of two, 8..256), CHANNEL and BLOCK (a row / block of up to 51200 elements per CTA, ragged blocks
+ * completed with zeros) and TENSOR (one launch per candidate).  scratch:
+ * b200q_observe_mse_workspace_bytes (per-candidate "some group improved" flags that reproduce the
+ * reference's global early stop; for TENSOR also the search state and per-CTA partial sums). */
 int b200q_observe_mse_steps(double maxshrink, double grid); /* int(maxshrink * grid), -1 if invalid */
 size_t b200q_observe_mse_workspace_bytes(int64_t N, int64_t K, const b200q_qargs* qa, int steps);
 int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw,
@@ -117,7 +119,8 @@ int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t l
  * in a 4 KiB array inside the library image, which every GPU that loads the library holds
  * until exit; nothing is allocated or freed by this call.
  *   - limit: int(maxshrink * grid) <= 1023 candidates, otherwise B200Q_ERR_ARG is returned
- *     (text in b200q_last_error) and nothing is launched;
+ *     (text in b200q_last_error) and nothing is launched; the TENSOR strategy, whose search needs
+ *     more scratch than the array holds, returns B200Q_ERR_UNSUPPORTED;
  *   - the first call on each device looks the array's device address up
  *     (cudaGetSymbolAddress); make that first call outside any stream capture;
  *   - all calls on a device share the one array: calls that overlap on the GPU (different

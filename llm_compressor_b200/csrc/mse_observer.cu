@@ -254,10 +254,14 @@ __global__ void __launch_bounds__(256) mse_group_bf16_int_kernel(const void* __r
 }
 #undef B200Q_BF2
 
+// One CTA per group held in shared memory: a row (CHANNEL, bh = 1, bw = K) or a bh x bw block
+// (BLOCK; blocks that stick out of the matrix are completed with zeros, which take part in the
+// statistics like the reference's padding).  The per-candidate error is summed in a fixed order
+// (thread-strided partial sums, warp tree, warps in order), so results do not depend on timing.
 template <int DT>
-__global__ void __launch_bounds__(256) mse_channel_kernel(const void* __restrict__ W, int64_t N, int64_t K,
-                                                          int64_t ldw, Cfg c, int* __restrict__ ctl, int pass,
-                                                          void* __restrict__ mn_out, void* __restrict__ mx_out) {
+__global__ void __launch_bounds__(256) mse_tile_kernel(const void* __restrict__ W, int64_t N, int64_t K,
+                                                       int64_t ldw, int bh, int bw, Cfg c, int* __restrict__ ctl,
+                                                       int pass, void* __restrict__ mn_out, void* __restrict__ mx_out) {
   using E = Elem<DT>;
   using T = typename E::type;
   constexpr bool TB = E::is_bf16;
@@ -267,10 +271,14 @@ __global__ void __launch_bounds__(256) mse_channel_kernel(const void* __restrict
   const int limit = (pass == 0) ? c.steps : ctl[0];
   if (pass == 1 && limit >= c.steps) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int64_t row = blockIdx.x; row < N; row += gridDim.x) {
+  const int64_t gpr = (K + bw - 1) / bw, groups = ((N + bh - 1) / bh) * gpr;
+  const int elems = bh * bw;
+  for (int64_t grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+    const int64_t r0 = (grp / gpr) * bh, c0 = (grp % gpr) * bw;
     float lo = INFINITY, hi = -INFINITY;
-    for (int64_t x = threadIdx.x; x < K; x += blockDim.x) {
-      float v = E::load((const T*)W + row * ldw + x);
+    for (int x = threadIdx.x; x < elems; x += blockDim.x) {
+      const int64_t r = r0 + x / bw, cc = c0 + x % bw;
+      const float v = (r < N && cc < K) ? E::load((const T*)W + r * ldw + cc) : 0.0f;
       srow[x] = v; lo = fminf(lo, v); hi = fmaxf(hi, v);
     }
     lo = warp_min(lo); hi = warp_max(hi);
@@ -290,7 +298,7 @@ __global__ void __launch_bounds__(256) mse_channel_kernel(const void* __restrict
       float s, z;
       qparams_local<TB>(smn, smx, c, s, z);
       float err = 0.0f;
-      for (int64_t x = threadIdx.x; x < K; x += blockDim.x) err += elem_error<TB>(srow[x], s, z, c);
+      for (int x = threadIdx.x; x < elems; x += blockDim.x) err += elem_error<TB>(srow[x], s, z, c);
       err = warp_sum(err);
       __syncthreads();
       if (lane == 0) s_a[warp] = err;
@@ -304,11 +312,105 @@ __global__ void __launch_bounds__(256) mse_channel_kernel(const void* __restrict
       }
     }
     if (threadIdx.x == 0) {
-      E::store((T*)mn_out + row, best_mn);
-      E::store((T*)mx_out + row, best_mx);
+      E::store((T*)mn_out + grp, best_mn);
+      E::store((T*)mx_out + grp, best_mx);
     }
     __syncthreads();
   }
+}
+
+// ---------------------------------------------------------------------------------------
+// TENSOR strategy: the whole matrix is one group.  One launch per shrink candidate sums the
+// element errors into per-CTA partials (grid-stride, fixed order inside a CTA); a one-warp kernel
+// folds the partials in index order, compares with the best so far and keeps the reference's
+// patience counter, all on the device.  After the search has stopped the remaining launches return
+// at once.  state: [0] min, [1] max (expanded), [2] best error, [3] best min, [4] best max,
+// [5] stale count, [6] stopped flag (both as int bit patterns), then the partials.
+constexpr int kSpanState = 8;
+
+template <int DT>
+__global__ void __launch_bounds__(256) mse_span_range_kernel(const void* __restrict__ W, int64_t N, int64_t K,
+                                                             int64_t ldw, float* __restrict__ partial) {
+  using E = Elem<DT>;
+  using T = typename E::type;
+  __shared__ float s_a[8], s_b[8];
+  float lo = INFINITY, hi = -INFINITY;
+  const int64_t total = N * K;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / K, cc = i - r * K;
+    const float v = E::load((const T*)W + r * ldw + cc);
+    lo = fminf(lo, v); hi = fmaxf(hi, v);
+  }
+  lo = warp_min(lo); hi = warp_max(hi);
+  if ((threadIdx.x & 31) == 0) { s_a[threadIdx.x >> 5] = lo; s_b[threadIdx.x >> 5] = hi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) { lo = fminf(lo, s_a[w]); hi = fmaxf(hi, s_b[w]); }
+    partial[2 * blockIdx.x] = lo; partial[2 * blockIdx.x + 1] = hi;
+  }
+}
+template <bool TB>
+__global__ void mse_span_init_kernel(float* __restrict__ state, const float* __restrict__ partial, int nblocks, Cfg c) {
+  float lo = INFINITY, hi = -INFINITY;
+  for (int i = 0; i < nblocks; ++i) { lo = fminf(lo, partial[2 * i]); hi = fmaxf(hi, partial[2 * i + 1]); }
+  const float mn = rnd_if<TB>(lo * c.expand), mx = rnd_if<TB>(hi * c.expand);
+  state[0] = mn; state[1] = mx;
+  state[2] = TB ? 3.3895313892515355e38f : 3.402823466e38f;
+  state[3] = mn; state[4] = mx;
+  ((int*)state)[5] = 0; ((int*)state)[6] = 0;
+}
+template <int DT>
+__global__ void __launch_bounds__(256) mse_span_error_kernel(const void* __restrict__ W, int64_t N, int64_t K,
+                                                             int64_t ldw, Cfg c, int step,
+                                                             const float* __restrict__ state,
+                                                             float* __restrict__ partial) {
+  using E = Elem<DT>;
+  using T = typename E::type;
+  constexpr bool TB = E::is_bf16;
+  __shared__ float s_a[8];
+  if (((const int*)state)[6]) return;
+  const float p = shrink_factor(step, c.grid);
+  const float smn = rnd_if<TB>(state[0] * p), smx = rnd_if<TB>(state[1] * p);
+  float s, z;
+  qparams_local<TB>(smn, smx, c, s, z);
+  float err = 0.0f;
+  const int64_t total = N * K;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / K, cc = i - r * K;
+    err += elem_error<TB>(E::load((const T*)W + r * ldw + cc), s, z, c);
+  }
+  err = warp_sum(err);
+  if ((threadIdx.x & 31) == 0) s_a[threadIdx.x >> 5] = err;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.0f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += s_a[w];
+    partial[blockIdx.x] = tot;
+  }
+}
+template <bool TB>
+__global__ void mse_span_fold_kernel(float* __restrict__ state, const float* __restrict__ partial, int nblocks, Cfg c,
+                                     int step) {
+  int* istate = (int*)state;
+  if (istate[6]) return;
+  float tot = 0.0f;
+  for (int i = 0; i < nblocks; ++i) tot += partial[i];
+  tot = rnd_if<TB>(tot);
+  if (tot < state[2]) {
+    const float p = shrink_factor(step, c.grid);
+    state[2] = tot; state[3] = rnd_if<TB>(state[0] * p); state[4] = rnd_if<TB>(state[1] * p);
+    istate[5] = 0;
+  } else if (++istate[5] >= c.patience) {
+    istate[6] = 1;
+  }
+}
+template <int DT>
+__global__ void mse_span_store_kernel(const float* __restrict__ state, void* __restrict__ mn_out,
+                                      void* __restrict__ mx_out) {
+  using E = Elem<DT>;
+  using T = typename E::type;
+  E::store((T*)mn_out, state[3]);
+  E::store((T*)mx_out, state[4]);
 }
 
 // ctl[0] <- number of candidates the reference's loop evaluates before it breaks
@@ -338,8 +440,11 @@ int b200q_observe_mse_steps(double maxshrink, double grid) {
   return v > 2147483647.0 ? 2147483647 : (int)v;
 }
 
-size_t b200q_observe_mse_workspace_bytes(int64_t, int64_t, const b200q_qargs*, int steps) {
-  return sizeof(int) * (size_t)(steps + 1 > 1 ? steps + 1 : 1);
+size_t b200q_observe_mse_workspace_bytes(int64_t, int64_t, const b200q_qargs* qa, int steps) {
+  const size_t flags = sizeof(int) * (size_t)(steps + 1 > 1 ? steps + 1 : 1);
+  if (qa && qa->strategy == B200Q_TENSOR)   // search state and per-CTA partials
+    return flags + sizeof(float) * (size_t)(b200q::mse::kSpanState + 2 * 4 * b200q::kNumSMs);
+  return flags;
 }
 
 int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw, const b200q_qargs* qa,
@@ -385,17 +490,46 @@ int b200q_observe_mse(const void* W, int wdtype, int64_t N, int64_t K, int64_t l
       else if (fast) mse_group_bf16_int_kernel<false><<<grid_sz, 256, 0, st>>>(W, N, K, ldw, g, c, ctl, pass, mn_out, mx_out);
       else if (wdtype == B200Q_BF16) mse_group_kernel<B200Q_BF16><<<grid_sz, 256, 0, st>>>(W, N, K, ldw, g, c, ctl, pass, mn_out, mx_out);
       else mse_group_kernel<B200Q_F32><<<grid_sz, 256, 0, st>>>(W, N, K, ldw, g, c, ctl, pass, mn_out, mx_out);
-    } else if (qa->strategy == B200Q_CHANNEL) {
-      size_t smem = (size_t)K * sizeof(float);
-      if (smem > 200 * 1024) return B200Q_ERR_UNSUPPORTED;
-      int grid_sz = grid_for(N, smem > 100 * 1024 ? 1 : 2);
+    } else if (qa->strategy == B200Q_CHANNEL || qa->strategy == B200Q_BLOCK) {
+      const bool blk = qa->strategy == B200Q_BLOCK;
+      if (blk && (qa->block_h <= 0 || qa->block_w <= 0)) return B200Q_ERR_ARG;
+      const int64_t bh = blk ? qa->block_h : 1, bw = blk ? qa->block_w : K;
+      const size_t smem = (size_t)(bh * bw) * sizeof(float);
+      if (bh * bw > (int64_t)50 * 1024) return B200Q_ERR_UNSUPPORTED;   // group does not fit in shared memory
+      const int64_t groups = ((N + bh - 1) / bh) * ((K + bw - 1) / bw);
+      int grid_sz = grid_for(groups, smem > 100 * 1024 ? 1 : 2);
       if (wdtype == B200Q_BF16) {
-        B200Q_TRY(cudaFuncSetAttribute(mse_channel_kernel<B200Q_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        mse_channel_kernel<B200Q_BF16><<<grid_sz, 256, smem, st>>>(W, N, K, ldw, c, ctl, pass, mn_out, mx_out);
+        B200Q_TRY(cudaFuncSetAttribute(mse_tile_kernel<B200Q_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        mse_tile_kernel<B200Q_BF16><<<grid_sz, 256, smem, st>>>(W, N, K, ldw, (int)bh, (int)bw, c, ctl, pass, mn_out, mx_out);
       } else {
-        B200Q_TRY(cudaFuncSetAttribute(mse_channel_kernel<B200Q_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        mse_channel_kernel<B200Q_F32><<<grid_sz, 256, smem, st>>>(W, N, K, ldw, c, ctl, pass, mn_out, mx_out);
+        B200Q_TRY(cudaFuncSetAttribute(mse_tile_kernel<B200Q_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        mse_tile_kernel<B200Q_F32><<<grid_sz, 256, smem, st>>>(W, N, K, ldw, (int)bh, (int)bw, c, ctl, pass, mn_out, mx_out);
       }
+    } else if (qa->strategy == B200Q_TENSOR) {
+      // one group: the search runs candidate by candidate, with its state on the device
+      if (pass == 1) break;
+      float* state = (float*)(ctl + c.steps + 1);
+      float* partial = state + kSpanState;
+      const int nblk = grid_for((N * K + 255) / 256, 4);
+      const bool tb = wdtype == B200Q_BF16;
+      if (tb) mse_span_range_kernel<B200Q_BF16><<<nblk, 256, 0, st>>>(W, N, K, ldw, partial);
+      else mse_span_range_kernel<B200Q_F32><<<nblk, 256, 0, st>>>(W, N, K, ldw, partial);
+      B200Q_LAUNCH_CHECK();
+      if (tb) mse_span_init_kernel<true><<<1, 1, 0, st>>>(state, partial, nblk, c);
+      else mse_span_init_kernel<false><<<1, 1, 0, st>>>(state, partial, nblk, c);
+      B200Q_LAUNCH_CHECK();
+      for (int i = 0; i < c.steps; ++i) {
+        if (tb) mse_span_error_kernel<B200Q_BF16><<<nblk, 256, 0, st>>>(W, N, K, ldw, c, i, state, partial);
+        else mse_span_error_kernel<B200Q_F32><<<nblk, 256, 0, st>>>(W, N, K, ldw, c, i, state, partial);
+        B200Q_LAUNCH_CHECK();
+        if (tb) mse_span_fold_kernel<true><<<1, 1, 0, st>>>(state, partial, nblk, c, i);
+        else mse_span_fold_kernel<false><<<1, 1, 0, st>>>(state, partial, nblk, c, i);
+        B200Q_LAUNCH_CHECK();
+      }
+      if (tb) mse_span_store_kernel<B200Q_BF16><<<1, 1, 0, st>>>(state, mn_out, mx_out);
+      else mse_span_store_kernel<B200Q_F32><<<1, 1, 0, st>>>(state, mn_out, mx_out);
+      B200Q_LAUNCH_CHECK();
+      return B200Q_OK;
     } else {
       return B200Q_ERR_UNSUPPORTED;
     }
@@ -458,6 +592,12 @@ extern "C" int b200q_observe_mse_noalloc(const void* W, int wdtype, int64_t N, i
     b200q::set_last_error("b200q_observe_mse_noalloc: int(maxshrink*grid) exceeds the built-in scratch (1023 candidates)",
                           cudaErrorInvalidValue);
     return B200Q_ERR_ARG;
+  }
+  if (qa && qa->strategy == B200Q_TENSOR) {
+    // the whole-tensor search keeps per-CTA partial sums in its scratch, more than the array holds
+    b200q::set_last_error("b200q_observe_mse_noalloc: the TENSOR strategy needs more scratch than the built-in array",
+                          cudaErrorInvalidValue);
+    return B200Q_ERR_UNSUPPORTED;
   }
   int* ctl = nullptr;
   int rc = static_ctl_address(&ctl);

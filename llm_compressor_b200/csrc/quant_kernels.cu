@@ -23,6 +23,7 @@ void set_last_error(const char* what, cudaError_t e) {
 struct QParamCfg {
   int symmetric, scale_kind, zp_kind, mx_offset, has_global;
   float qmin, qmax, half_range, range, eps;
+  float inv_half_range, inv_range;   // float32 reciprocals, used for bf16 statistics (see qparams_one)
 };
 
 static int make_qparam_cfg(const b200q_qargs* qa, bool stat_bf16, bool has_global, QParamCfg* c) {
@@ -32,6 +33,7 @@ static int make_qparam_cfg(const b200q_qargs* qa, bool stat_bf16, bool has_globa
   c->symmetric = qa->symmetric; c->scale_kind = qa->scale_kind; c->zp_kind = qa->zp_kind;
   c->has_global = has_global ? 1 : 0;
   c->qmin = r.qmin; c->qmax = r.qmax; c->range = r.qmax - r.qmin; c->half_range = c->range / 2.0f;
+  c->inv_half_range = 1.0f / c->half_range; c->inv_range = 1.0f / c->range;
   c->mx_offset = (qa->num_bits == 4) ? 2 : 8;
   if (qa->scale_kind == B200Q_SCALE_E8M0 &&
       !(qa->qtype == B200Q_QFLOAT && qa->group_size == 32 && qa->symmetric))
@@ -65,12 +67,15 @@ __device__ __forceinline__ void qparams_one(float mn, float mx, const QParamCfg&
       }
       s = (biased == 0) ? -INFINITY : (float)(biased - c.mx_offset);
     } else {
-      s = rnd_if<TB>(__fdiv_rn(amax, c.half_range));
+      // bf16 statistics: the quotient of an 8-bit significand by 7.5, 127.5, 448 or 6 stays at least
+      // 129 float32 ulps away from every bf16 rounding midpoint (checked over all significands), so
+      // the product with the float32 reciprocal rounds to the same bf16 value as the division
+      s = TB ? bf16r(amax * c.inv_half_range) : __fdiv_rn(amax, c.half_range);
     }
     zp = 0.0f;
   } else {
     float d = rnd_if<TB>(mx - mn);
-    s = rnd_if<TB>(__fdiv_rn(d, c.range));
+    s = TB ? bf16r(d * c.inv_range) : __fdiv_rn(d, c.range);
     float z = rnd_if<TB>(__fdiv_rn(mn, s));
     z = rnd_if<TB>(c.qmin - z);
     // 0/0 for an all-zero group: torch's clamp keeps the NaN and the integer cast makes it 0
@@ -360,7 +365,10 @@ __global__ void global_scale_kernel(const float* __restrict__ absmax, int stat_b
   float a = *absmax;
   float tiny = 1.17549435e-38f;  // smallest normal of both bf16 and float32
   a = fmaxf(a, tiny);
-  float g = __fdiv_rn(448.0f * 6.0f, a);
+  // "scalar / tensor" in torch is tensor.reciprocal() * scalar: two roundings in the statistics' dtype
+  float r = __frcp_rn(a);
+  if (stat_bf16) r = bf16r(r);
+  float g = __fmul_rn(r, 448.0f * 6.0f);
   if (stat_bf16) g = bf16r(g);
   if (!(fabsf(g) <= 3.402823466e38f)) g = 1.0f;  // NaN / Inf -> 1
   *out = g;
@@ -450,7 +458,11 @@ static int quant_launch(const void* W, int64_t N, int64_t K, int64_t ldw, const 
                          ((pm.strategy == B200Q_GROUP || pm.strategy == B200Q_TENSOR_GROUP) &&
                           pm.g_idx == nullptr && (pm.group_size & 7) == 0) ||
                          (pm.strategy == B200Q_BLOCK && (pm.block_w & 7) == 0);
-    if constexpr (XDT == B200Q_BF16 && MODE != kPackFake) {
+    // bf16 weights with per-group parameters in column order: lane / chunk split kernels.  The
+    // combinations that occur: a bf16 scale without a global scale, or a float32 scale with one
+    // (FP4 only); everything else takes the row kernel below.
+    if constexpr (XDT == B200Q_BF16 && MODE != kPackFake &&
+                  ((SDT == B200Q_BF16 && !GLOBAL) || (SDT == B200Q_F32 && GLOBAL && MODE == kPackFp4))) {
       const int g = pm.group_size;
       if ((pm.strategy == B200Q_GROUP || pm.strategy == B200Q_TENSOR_GROUP) && pm.g_idx == nullptr && g >= 8 &&
           g <= 256 && (g & (g - 1)) == 0 && K % g == 0) {
@@ -460,11 +472,16 @@ static int quant_launch(const void* W, int64_t N, int64_t K, int64_t ldw, const 
         while (tx2 < 256 && tx2 < slots) tx2 <<= 1;
         const int rows2 = stream::kThreads / tx2;
         const int grid2 = grid_for((N + rows2 - 1) / rows2, 6);
-        const int txl2 = __builtin_ctz(tx2), ll2 = __builtin_ctz(gsp.L);
-#define B200Q_QG(RR) stream::quant_group_bf16_kernel<SDT, GLOBAL, MODE, RR><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, scale, zp, zp_kind, gscale, qr, out)
-        if (gsp.R == 4) B200Q_QG(4);
-        else if (gsp.R == 2) B200Q_QG(2);
-        else B200Q_QG(1);
+        const int txl2 = __builtin_ctz(tx2);
+#define B200Q_QG(RR, LL) stream::quant_group_bf16_kernel<SDT, GLOBAL, MODE, RR, LL><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, txl2, scale, zp, zp_kind, gscale, qr, out)
+        switch (g) {
+          case 8: B200Q_QG(1, 1); break;
+          case 16: B200Q_QG(2, 1); break;
+          case 32: B200Q_QG(4, 1); break;
+          case 64: B200Q_QG(4, 2); break;
+          case 128: B200Q_QG(4, 4); break;
+          default: B200Q_QG(4, 8); break;
+        }
 #undef B200Q_QG
         B200Q_LAUNCH_CHECK();
         return B200Q_OK;
@@ -791,26 +808,38 @@ static int rtn_impl(const void* W, int64_t N, int64_t K, int64_t ldw, const b200
     if (!(pow2(g) && g >= 8 && g <= 256 && K % g == 0)) return B200Q_ERR_UNSUPPORTED;
     stream::RowTiling t = stream::make_tiling(N, K, 6);
     const int txl = __builtin_ctz(t.tx);
-    // bf16 weights: R chunks per lane, L lanes per group
+    // bf16 weights: R chunks per lane, L lanes per group (both compile-time)
     const stream::GroupSplit gsp = stream::make_group_split(g);
     const int64_t slots = (K / g) * gsp.L;
     int tx2 = 32;
     while (tx2 < 256 && tx2 < slots) tx2 <<= 1;
     const int rows2 = stream::kThreads / tx2;
     const int grid2 = grid_for((N + rows2 - 1) / rows2, 6);
-    const int txl2 = __builtin_ctz(tx2), ll2 = __builtin_ctz(gsp.L);
-#define B200Q_RB3(MODE, GL, RR) stream::rtn_group_bf16_kernel<stream::MODE, GL, RR><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, g, ll2, txl2, qc, qr, gscale, scale_out, zp_out, scale_store, out)
-#define B200Q_RB2(MODE, GL)                         \
-  do {                                              \
-    if (gsp.R == 8) B200Q_RB3(MODE, GL, 8);         \
-    else if (gsp.R == 4) B200Q_RB3(MODE, GL, 4);    \
-    else if (gsp.R == 2) B200Q_RB3(MODE, GL, 2);    \
-    else B200Q_RB3(MODE, GL, 1);                    \
+    const int txl2 = __builtin_ctz(tx2);
+#define B200Q_RB3(MODE, GL, RR, LL) stream::rtn_group_bf16_kernel<stream::MODE, GL, RR, LL><<<grid2, stream::kThreads, 0, st>>>(W, (int)N, (int)K, ldw, txl2, qc, qr, gscale, scale_out, zp_out, scale_store, out)
+#define B200Q_RB2(MODE, GL)                          \
+  do {                                               \
+    switch (g) {                                     \
+      case 8: B200Q_RB3(MODE, GL, 1, 1); break;      \
+      case 16: B200Q_RB3(MODE, GL, 2, 1); break;     \
+      case 32: B200Q_RB3(MODE, GL, 4, 1); break;     \
+      case 64: B200Q_RB3(MODE, GL, 4, 2); break;     \
+      case 128: B200Q_RB3(MODE, GL, 8, 2); break;    \
+      default: B200Q_RB3(MODE, GL, 8, 4); break;     \
+    }                                                \
   } while (0)
-#define B200Q_RB(MODE)                              \
-  do {                                              \
-    if (gscale) B200Q_RB2(MODE, true);              \
-    else B200Q_RB2(MODE, false);                    \
+#define B200Q_RB(MODE)                                                            \
+  do {                                                                            \
+    if (gscale) {                                                                 \
+      if constexpr (stream::MODE == stream::kFp4) {                               \
+        if (g != 16) return B200Q_ERR_UNSUPPORTED;                                \
+        B200Q_RB3(MODE, true, 2, 1);                                              \
+      } else {                                                                    \
+        return B200Q_ERR_UNSUPPORTED;                                             \
+      }                                                                           \
+    } else {                                                                      \
+      B200Q_RB2(MODE, false);                                                     \
+    }                                                                             \
   } while (0)
 #define B200Q_R(MODE)                                                                              \
   do {                                                                                             \

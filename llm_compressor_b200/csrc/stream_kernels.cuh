@@ -101,15 +101,22 @@ __device__ __forceinline__ void store_codes(void* out, int64_t word_index, int64
 
 // ---------------------------------------------------------------------------------------
 // Packed fast paths for 8 bf16 elements that share one scale.  They produce exactly what
-// quant_code<CB> + store_codes produce, in about a third of the instructions:
-//   q = x * (1/s) in float32 (a couple of ulps from the IEEE quotient), two values rounded to
-//   bf16 with one cvt, zero point / clamp / round-to-integer done on bf16x2 registers (the
-//   integer rounding is an addition of 192: bf16 has unit spacing in [128,256)), FP8 / FP4
-//   codes made by the hardware converters (round-to-nearest-even, saturating: the same tie
-//   rules as the reference's table).
-// `unsafe` is set when a quotient is within 3 float ulps of a bf16 rounding midpoint; the
-// caller then recomputes the chunk with true divisions.  Power-of-two (MX) scales make x*(1/s)
-// exact, so they never need that.
+// quant_code<CB> + store_codes produce, in about a quarter of the instructions.
+//
+// bf16 weight, bf16 scale (CB).  The reference forms q = bf16(float(x) / float(s)).  x and s carry
+// 8 significant bits each, so the exact quotient is a ratio of two integers below 256; a bf16
+// rounding midpoint has 9 significant bits, so the quotient can neither be a midpoint (that would
+// need s to be a multiple of 256) nor come closer to one than 1 / (511 * 255) = 7.7e-6 relative:
+// 129 float32 ulps, verified exhaustively over all pairs of mantissas.  x * (1/s) in float32 is
+// within 2 ulps of the quotient, therefore bf16(x * (1/s)) is ALWAYS the reference's q and no
+// check is needed.  The product is formed two elements at a time (fma.rn.f32x2, with a +0 addend
+// where the sign of a zero quotient matters: -0 + 0 = +0 is what the reference's "+ zero_point"
+// does), two values are rounded to bf16 with one cvt, the zero point, the clamp and the integer
+// rounding run on bf16x2 registers (rounding to an integer is the addition of 192: bf16 has unit
+// spacing in [128, 256)), FP8 / FP4 codes come from the hardware converters (round to nearest
+// even, saturating: the same ties and the same clamp as the reference).  Power-of-two (MX) scales
+// make the product exact in bf16 itself: one packed HFMA2 per pair, no float32 at all.
+// Scales outside 2^-100 .. 2^100 (where 1/s leaves the normal range) take the exact path.
 __device__ __forceinline__ uint32_t cvt_bf16x2(float hi, float lo) {
   uint32_t d;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
@@ -119,47 +126,76 @@ __device__ __forceinline__ uint32_t bf2_add(uint32_t a, uint32_t b) {
   __nv_bfloat162 r = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
   return *reinterpret_cast<uint32_t*>(&r);
 }
-__device__ __forceinline__ uint32_t bf2_clamp(uint32_t a, uint32_t lo, uint32_t hi) {
-  __nv_bfloat162 r = __hmin2(__hmax2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&lo)),
-                             *reinterpret_cast<__nv_bfloat162*>(&hi));
+__device__ __forceinline__ uint32_t bf2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  __nv_bfloat162 r = __hfma2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b),
+                             *reinterpret_cast<__nv_bfloat162*>(&c));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf2_min(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmin2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf2_max(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
   return *reinterpret_cast<uint32_t*>(&r);
 }
 __device__ __forceinline__ uint32_t bf2_splat(float v) {
   __nv_bfloat162 r = __float2bfloat162_rn(v);
   return *reinterpret_cast<uint32_t*>(&r);
 }
-__device__ __forceinline__ bool near_bf16_midpoint(float q) {
-  return ((__float_as_uint(q) + 0x8003u) & 0xFFFFu) <= 6u;  // low half-word in [0x7FFD, 0x8003]
+// {a0, a1} * r + c on the packed float32 pipe (one instruction for both lanes)
+__device__ __forceinline__ void fma2_f32(float a0, float a1, float r, float c, float& q0, float& q1) {
+  uint64_t a, b, cc, d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a0), "f"(a1));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(b) : "f"(r));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(cc) : "f"(c));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(cc));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(q0), "=f"(q1) : "l"(d));
 }
 
-// common front end: 4 words of bf16 pairs -> 4 words of clamped bf16 pairs bf16(bf16(x/s)+zp)
+// What the 8-element paths need from one (scale, zero point), prepared once per group.
 //
-// Midpoint test, two quotients at a time: the low half-words of both products are packed into
-// one word and 0x8004 is added to each (one 32-bit add; a carry out of the low half only widens
-// the window of the high half by one), which maps "within 3 ulps of the bf16 midpoint 0x8000" to
-// half-words 1..8.  The four words of a chunk are reduced with the packed 16-bit minimum and one
-// test "some half-word below 16" decides; false alarms only cost the exact path.
-template <bool EXACT, bool ADD_ZP>
-__device__ __forceinline__ void front8_bf16(const uint4& raw, float rs, uint32_t zp2, uint32_t lo2, uint32_t hi2,
-                                            uint32_t (&v)[4], bool& unsafe) {
+// The quotient itself stays in packed bf16 arithmetic: with 1/s (float32) split into two bf16
+// parts r_hi = bf16(1/s), r_lo = bf16(1/s - r_hi),
+//     t = fma(x, r_lo, +0)        q = fma(x, r_hi, t)            (two HFMA2 per pair)
+// gives q = bf16(x / s) for every pair of bf16 significands (checked exhaustively with exact
+// rational arithmetic: the error of t, 2^-18 relative to q, is below the 7.7e-6 that separates
+// x / s from the nearest rounding midpoint).  A zero x gives +0 whatever its sign, like the
+// reference's "+ zero_point".  Power-of-two scales have r_lo = 0 and need one HFMA2.
+struct GroupQ {
+  float se, rs, z;
+  uint32_t z2;           // zero point as a bf16 pair
+  uint32_t rhi2, rlo2;   // the two bf16 parts of 1/scale, each as a pair
+  bool slow;             // 1/scale leaves the normal range: exact path
+};
+template <bool CB>
+__device__ __forceinline__ GroupQ make_group_q(float se, float z) {
+  GroupQ g;
+  g.se = se; g.z = z;
+  g.rs = __frcp_rn(se);
+  g.slow = !(se >= 0x1p-100f && se <= 0x1p100f);
+  if (CB) {
+    const float rhi = bf16r(g.rs);
+    g.rhi2 = bf2_splat(rhi);
+    g.rlo2 = bf2_splat(g.rs - rhi);
+    g.z2 = bf2_splat(z);
+  } else {
+    g.rhi2 = g.rlo2 = g.z2 = 0u;
+  }
+  return g;
+}
+
+// q = bf16(x / s) for the 8 elements of a chunk, as 4 bf16 pairs.
+template <bool POW2>
+__device__ __forceinline__ void quot8_bf16(const uint4& raw, const GroupQ& g, uint32_t (&v)[4]) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  uint32_t m[4];
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
-    const float q0 = __uint_as_float(w[p] << 16) * rs;
-    const float q1 = __uint_as_float(w[p] & 0xFFFF0000u) * rs;
-    if (!EXACT) m[p] = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x5410) + 0x80048004u;
-    const uint32_t c = cvt_bf16x2(q1, q0);
-    v[p] = bf2_clamp(ADD_ZP ? bf2_add(c, zp2) : c, lo2, hi2);
-  }
-  if (!EXACT) {
-    const uint32_t mm = __vimin3_u16x2(__vimin3_u16x2(m[0], m[1], m[2]), m[3], m[3]) & 0xFFF0FFF0u;
-    unsafe = ((mm & 0xFFFFu) == 0u) || ((mm >> 16) == 0u);
-  } else {
-    unsafe = false;
+    const uint32_t t = POW2 ? 0u : bf2_fma(w[p], g.rlo2, 0u);
+    v[p] = bf2_fma(w[p], g.rhi2, t);
   }
 }
-// int4: 8 nibbles (value + 8) in one word
+// int4: 8 nibbles (value + 8) in one word; v holds bf16 pairs already clamped to [-8, 7]
 __device__ __forceinline__ uint32_t tail8_int4(const uint32_t (&v)[4]) {
   const uint32_t magic = 0x43404340u;  // bf16x2 {192, 192}
   uint32_t t[4];
@@ -172,12 +208,30 @@ __device__ __forceinline__ uint32_t tail8_int4(const uint32_t (&v)[4]) {
   b |= b >> 4;
   return __byte_perm(a, b, 0x6420) ^ 0x88888888u;
 }
+// int8: 8 bytes; v holds bf16 pairs already clamped to [-128, 127].  Rounding to an integer is
+// the float32 addition of 1.5 * 2^23 (the value is exact in float32, so this is round half to
+// even on it), whose low byte is the two's-complement code.
+template <bool OFFSET>
+__device__ __forceinline__ void tail8_int8(const uint32_t (&v)[4], uint32_t& w0, uint32_t& w1) {
+  uint32_t t[8];
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    float a, b;
+    fma2_f32(__uint_as_float(v[p] << 16), __uint_as_float(v[p] & 0xFFFF0000u), 1.0f, 12582912.0f, a, b);
+    t[2 * p] = __float_as_uint(a); t[2 * p + 1] = __float_as_uint(b);
+  }
+  w0 = __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410);
+  w1 = __byte_perm(__byte_perm(t[4], t[5], 0x0040), __byte_perm(t[6], t[7], 0x0040), 0x5410);
+  if (OFFSET) { w0 ^= 0x80808080u; w1 ^= 0x80808080u; }
+}
 __device__ __forceinline__ void tail8_fp8(const uint32_t (&v)[4], uint32_t& w0, uint32_t& w1) {
   uint32_t h[4];
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
-    float2 f = make_float2(__uint_as_float(v[p] << 16), __uint_as_float(v[p] & 0xFFFF0000u));
-    h[p] = (uint32_t)__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(__uint_as_float(v[p] & 0xFFFF0000u)),
+        "f"(__uint_as_float(v[p] << 16)));
+    h[p] = r;
   }
   w0 = h[0] | (h[1] << 16);
   w1 = h[2] | (h[3] << 16);
@@ -209,15 +263,15 @@ __device__ __forceinline__ uint32_t tail8_fp4(const uint32_t (&v)[4]) {
 __device__ __forceinline__ uint32_t nvfp4_8(const uint4& raw, float rs, bool& unsafe) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
   // both ends of an interval that holds the exact quotient (reciprocal, its scaling and the
-  // product each round by 2^-24 or less; the margin is 2^-21).  The fused "+ 0" turns a -0.0
+  // product each round by 2^-23 or less; the margin is 2^-21).  The fused "+ 0" turns a -0.0
   // weight into +0 like the reference's "+ zero_point".
   const float rlo = rs * (1.0f - 0x1p-21f), rhi = rs * (1.0f + 0x1p-21f);
   float lo[8], hi[8];
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
     const float x0 = __uint_as_float(w[p] << 16), x1 = __uint_as_float(w[p] & 0xFFFF0000u);
-    lo[2 * p] = __fmaf_rn(x0, rlo, 0.0f); hi[2 * p] = __fmaf_rn(x0, rhi, 0.0f);
-    lo[2 * p + 1] = __fmaf_rn(x1, rlo, 0.0f); hi[2 * p + 1] = __fmaf_rn(x1, rhi, 0.0f);
+    fma2_f32(x0, x1, rlo, 0.0f, lo[2 * p], lo[2 * p + 1]);
+    fma2_f32(x0, x1, rhi, 0.0f, hi[2 * p], hi[2 * p + 1]);
   }
   const uint32_t c = cvt_e2m1x8(lo);
   unsafe = cvt_e2m1x8(hi) != c;
@@ -340,6 +394,31 @@ __device__ __forceinline__ void minmax8_bf16(const uint4& raw, float& lo, float&
   hi = fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y));
   lo = fminf(__bfloat162float(mn.x), __bfloat162float(mn.y));
 }
+// Range of a group for calculate_qparams, which clamps it to contain zero first: bf16 bit
+// patterns order like unsigned integers among negative values (the larger pattern is the more
+// negative number, and every negative pattern is above every positive one) and like signed
+// integers among positive values, so one packed unsigned maximum finds the minimum if it is
+// negative and one packed signed maximum finds the maximum if it is positive; whatever they
+// return otherwise has the other sign and is replaced by zero by the clamp.  Three inputs per
+// instruction (VIMNMX3): 4 instructions per chunk of 8 elements.
+struct RangeQ {
+  uint32_t umax, smax;
+  __device__ __forceinline__ void first(const uint4& raw) {
+    umax = __vimax3_u16x2(raw.x, raw.y, raw.z); umax = __vimax3_u16x2(umax, raw.w, raw.w);
+    smax = (uint32_t)__vimax3_s16x2(raw.x, raw.y, raw.z); smax = (uint32_t)__vimax3_s16x2(smax, raw.w, raw.w);
+  }
+  __device__ __forceinline__ void add(const uint4& raw) {
+    umax = __vimax3_u16x2(umax, raw.x, raw.y); umax = __vimax3_u16x2(umax, raw.z, raw.w);
+    smax = (uint32_t)__vimax3_s16x2(smax, raw.x, raw.y); smax = (uint32_t)__vimax3_s16x2(smax, raw.z, raw.w);
+  }
+  // (lo, hi): equal to the group's min / max after both are clamped to contain zero
+  __device__ __forceinline__ void finish(float& lo, float& hi) const {
+    const uint32_t u = max(umax & 0xFFFFu, umax >> 16);
+    const int sv = max((int)(short)(smax & 0xFFFFu), (int)(short)(smax >> 16));
+    lo = fminf(__uint_as_float(u << 16), 0.0f);
+    hi = fmaxf(__uint_as_float((uint32_t)sv << 16), 0.0f);
+  }
+};
 // min / max kept as bf16 pairs across several chunks, widened once at the end
 struct MinMax2 {
   __nv_bfloat162 mn, mx;
@@ -367,55 +446,91 @@ __device__ __forceinline__ void unpack8_bf16(const uint4& raw, float (&v)[8]) {
   }
 }
 
-// codes of one chunk with one (scale, zp): fast path, exact redo when flagged
-template <int MODE, bool GLOBAL, bool SCALE_BF16>
-__device__ __forceinline__ void chunk_codes_bf16(const uint4& raw, float se, float z, bool pow2_scale, QRange qr,
-                                                 uint32_t& w0, uint32_t& w1) {
-  constexpr bool CB = SCALE_BF16 && !GLOBAL;
-  const float rs = __frcp_rn(se);
-  bool unsafe = false;
-  if constexpr (!CB) {
-    if constexpr (MODE == kFp4) {
-      w0 = nvfp4_8(raw, rs, unsafe);
-    } else {
-      unsafe = true;
+// Codes of one chunk with one (scale, zp), exact element-wise path.
+// (out of line, arguments and result by value: the packed paths must not be forced onto the stack)
+template <int MODE, bool CB>
+__device__ __noinline__ uint2 chunk_codes_exact(uint4 raw, float se, float z, QRange qr) {
+  float x[8], q[8];
+  unpack8_bf16(raw, x);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = quant_code<CB>(x[i], se, z, qr);
+  uint32_t a = 0, b = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (MODE == kInt4) a |= ((uint32_t)((int)q[i] + 8) & 0xFu) << (4 * i);
+    else if (MODE == kFp4) a |= e2m1_nibble(q[i]) << (4 * i);
+    else {
+      uint32_t by = (qr.kind == kFp8) ? e4m3_bits(q[i])
+                  : (MODE == kInt8Word) ? ((uint32_t)((int)q[i] + 128) & 0xFFu) : ((uint32_t)(int)q[i] & 0xFFu);
+      if (i < 4) a |= by << (8 * i); else b |= by << (8 * (i - 4));
     }
-  } else if constexpr (MODE == kInt8Word || MODE == kByte) {
-    if (qr.kind == kFp8) {
-      uint32_t v[4];
-      const uint32_t lim = 0x43E043E0u;  // bf16x2 {448, 448}
-      if (pow2_scale) front8_bf16<true, true>(raw, rs, bf2_splat(z), lim ^ 0x80008000u, lim, v, unsafe);
-      else front8_bf16<false, true>(raw, rs, bf2_splat(z), lim ^ 0x80008000u, lim, v, unsafe);
-      tail8_fp8(v, w0, w1);
-    } else {
-      unsafe = true;  // int8 keeps the per-element path
-    }
-  } else {
-    uint32_t v[4];
-    const uint32_t lo2 = bf2_splat(qr.qmin), hi2 = bf2_splat(qr.qmax);
-    // integer codes do not see the sign of zero, so a zero zero-point need not be added
-    if (MODE == kInt4 && z == 0.0f) front8_bf16<false, false>(raw, rs, 0u, lo2, hi2, v, unsafe);
-    else if (pow2_scale) front8_bf16<true, true>(raw, rs, bf2_splat(z), lo2, hi2, v, unsafe);
-    else front8_bf16<false, true>(raw, rs, bf2_splat(z), lo2, hi2, v, unsafe);
-    w0 = (MODE == kInt4) ? tail8_int4(v) : tail8_fp4(v);
   }
-  if (unsafe) {
-    float x[8], q[8];
-    unpack8_bf16(raw, x);
+  return make_uint2(a, b);
+}
+
+// Codes of one chunk, packed path for a bf16 scale without a global scale (g.slow must be false).
+//   POW2    the scale is a power of two (MX formats)
+//   HAS_ZP  a zero point has to be added
+//   OWN_SYM the scale was derived from this very group's range by a symmetric scheme, so the
+//           quotients cannot fall below qmin - 1/2 and only the upper clamp is needed
+template <int MODE, bool POW2, bool HAS_ZP, bool OWN_SYM>
+__device__ __forceinline__ void chunk_codes_packed(const uint4& raw, const GroupQ& g, const QRange& qr, uint32_t& w0,
+                                                   uint32_t& w1) {
+  uint32_t v[4];
+  quot8_bf16<POW2>(raw, g, v);
+  if (HAS_ZP) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = quant_code<CB>(x[i], se, z, qr);
-    uint32_t a = 0, b = 0;
+    for (int p = 0; p < 4; ++p) v[p] = bf2_add(v[p], g.z2);
+  }
+  if constexpr (MODE == kFp4) {
+    w0 = tail8_fp4(v);             // the converter saturates at +-6
+  } else if constexpr (MODE == kInt4) {
+    const uint32_t lo2 = bf2_splat(qr.qmin), hi2 = bf2_splat(qr.qmax);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (MODE == kInt4) a |= ((uint32_t)((int)q[i] + 8) & 0xFu) << (4 * i);
-      else if (MODE == kFp4) a |= e2m1_nibble(q[i]) << (4 * i);
-      else {
-        uint32_t by = (qr.kind == kFp8) ? e4m3_bits(q[i])
-                    : (MODE == kInt8Word) ? ((uint32_t)((int)q[i] + 128) & 0xFFu) : ((uint32_t)(int)q[i] & 0xFFu);
-        if (i < 4) a |= by << (8 * i); else b |= by << (8 * (i - 4));
+    for (int p = 0; p < 4; ++p) {
+      if (!OWN_SYM) v[p] = bf2_max(v[p], lo2);
+      v[p] = bf2_min(v[p], hi2);
+    }
+    w0 = tail8_int4(v);
+  } else if (qr.kind == kFp8) {
+    tail8_fp8(v, w0, w1);          // the converter saturates at +-448
+  } else {
+    const uint32_t lo2 = bf2_splat(qr.qmin), hi2 = bf2_splat(qr.qmax);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) v[p] = bf2_min(bf2_max(v[p], lo2), hi2);
+    tail8_int8<MODE == kInt8Word>(v, w0, w1);
+  }
+}
+
+// R chunks of one lane that share (scale, zp) -> codes a[k] (and b[k] for byte codes).
+template <int MODE, bool GLOBAL, bool SCALE_BF16, int R, bool POW2, bool HAS_ZP, bool OWN_SYM>
+__device__ __forceinline__ void lane_codes(const uint4 (&raw)[R], const GroupQ& g, const QRange& qr, uint32_t (&a)[R],
+                                           uint32_t (&b)[R]) {
+  constexpr bool CB = SCALE_BF16 && !GLOBAL;
+#pragma unroll
+  for (int k = 0; k < R; ++k) { a[k] = 0; b[k] = 0; }
+  if (g.slow || (!CB && MODE != kFp4)) {
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const uint2 r = chunk_codes_exact<MODE, CB>(raw[k], g.se, g.z, qr);
+      a[k] = r.x; b[k] = r.y;
+    }
+    return;
+  }
+  if constexpr (!CB) {
+    // NVFP4: float32 effective scale, interval test per chunk
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      bool unsafe;
+      a[k] = nvfp4_8(raw[k], g.rs, unsafe);
+      if (unsafe) {
+        const uint2 r = chunk_codes_exact<MODE, CB>(raw[k], g.se, g.z, qr);
+        a[k] = r.x; b[k] = r.y;
       }
     }
-    w0 = a; w1 = b;
+  } else {
+#pragma unroll
+    for (int k = 0; k < R; ++k) chunk_codes_packed<MODE, POW2, HAS_ZP, OWN_SYM>(raw[k], g, qr, a[k], b[k]);
   }
 }
 
@@ -460,37 +575,57 @@ __device__ __forceinline__ void store_lane_codes(void* out, int64_t wi0, const u
   }
 }
 
-template <int MODE, bool GLOBAL, int R>
+// Stores of a lane's R code words (chunk c0 + k * L of the row) and of its R loads: with L known at
+// compile time every address is the slot's base plus an immediate.
+template <int MODE, int R, int L>
+__device__ __forceinline__ void store_lane_strided(void* out, int64_t wi0, const uint32_t (&a)[R], const uint32_t (&b)[R]) {
+  if constexpr (L == 1) {
+    store_lane_codes<MODE, R>(out, wi0, a, b);
+  } else if constexpr (MODE == kInt4 || MODE == kFp4) {
+    uint32_t* o = (uint32_t*)out + wi0;
+#pragma unroll
+    for (int k = 0; k < R; ++k) o[k * L] = a[k];
+  } else {
+    uint2* o = reinterpret_cast<uint2*>(out) + wi0;
+#pragma unroll
+    for (int k = 0; k < R; ++k) o[k * L] = make_uint2(a[k], b[k]);
+  }
+}
+
+// MODE, GLOBAL as above; R chunks per lane, L lanes per group (compile-time: g = 8 * R * L).
+template <int MODE, bool GLOBAL, int R, int L>
 __global__ void __launch_bounds__(kThreads) rtn_group_bf16_kernel(
-    const void* __restrict__ W, int N, int K, int64_t ldw, int g, int l_log2, int tx_log2, QParamCfg qc, QRange qr,
+    const void* __restrict__ W, int N, int K, int64_t ldw, int tx_log2, QParamCfg qc, QRange qr,
     const float* __restrict__ gscale, void* __restrict__ scale_out, void* __restrict__ zp_out,
     uint8_t* __restrict__ scale_store, void* __restrict__ out) {
   using T = __nv_bfloat16;
+  constexpr int cpg = R * L;                  // chunks per group
   const float gs = GLOBAL ? *gscale : 1.0f;
   const int TX = 1 << tx_log2, rows = kThreads >> tx_log2;
   const int tx = threadIdx.x & (TX - 1), ty = threadIdx.x >> tx_log2;
-  const int L = 1 << l_log2, cpg = g >> 3, cpr = K >> 3, gpr = K / g;
-  const int slots = gpr << l_log2;            // thread slots per row
+  const int cpr = K >> 3, gpr = cpr / cpg;
+  const int slots = gpr * L;                  // thread slots per row
   const int send = (slots + 31) & ~31;
-  const bool pow2_scale = qc.scale_kind == B200Q_SCALE_E8M0;
+  const bool mx = qc.scale_kind == B200Q_SCALE_E8M0, sym = qc.symmetric != 0;
   for (int row = blockIdx.x * rows + ty; row < N; row += gridDim.x * rows) {
     const T* wrow = (const T*)W + (int64_t)row * ldw;
     for (int t = tx; t < send; t += TX) {
       const bool live = t < slots;
-      const int grp = t >> l_log2, j = t & (L - 1);
+      const int grp = t / L, j = t % L;
       const int c0 = grp * cpg + j;           // first chunk of this lane
       uint4 raw[R];
+      {
+        const uint4* src = reinterpret_cast<const uint4*>(wrow) + c0;
 #pragma unroll
-      for (int k = 0; k < R; ++k)
-        raw[k] = live ? ldg_stream(wrow + (int64_t)(c0 + k * L) * 8) : make_uint4(0, 0, 0, 0);
-      float lo = INFINITY, hi = -INFINITY;
-      if (live) {
-        MinMax2 mm;
-        mm.first(raw[0]);
-#pragma unroll
-        for (int k = 1; k < R; ++k) mm.add(raw[k]);
-        mm.finish(lo, hi);
+        for (int k = 0; k < R; ++k) raw[k] = live ? ldg_stream(src + k * L) : make_uint4(0, 0, 0, 0);
       }
+      RangeQ mm;
+      mm.first(raw[0]);
+#pragma unroll
+      for (int k = 1; k < R; ++k) mm.add(raw[k]);
+      float lo, hi;
+      mm.finish(lo, hi);
+#pragma unroll
       for (int o = L >> 1; o > 0; o >>= 1) {
         lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
         hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
@@ -504,25 +639,13 @@ __global__ void __launch_bounds__(kThreads) rtn_group_bf16_kernel(
         if (zp_out) store_zp(zp_out, qc.zp_kind, gi, z);
         if (scale_store) scale_store[gi] = (qc.scale_kind == B200Q_SCALE_FP8) ? e4m3_bits(s) : e8m0_of(s);
       }
-      const float se = GLOBAL ? __fdiv_rn(s, gs) : s;
-      if (l_log2 == 0) {   // one lane per group: its R chunks are contiguous
-        uint32_t a[R], b[R];
-#pragma unroll
-        for (int k = 0; k < R; ++k) {
-          a[k] = 0; b[k] = 0;
-          chunk_codes_bf16<MODE, GLOBAL, true>(raw[k], se, z, pow2_scale, qr, a[k], b[k]);
-        }
-        store_lane_codes<MODE, R>(out, (int64_t)row * cpr + c0, a, b);
-        continue;
-      }
-#pragma unroll
-      for (int k = 0; k < R; ++k) {
-        uint32_t w0 = 0, w1 = 0;
-        chunk_codes_bf16<MODE, GLOBAL, true>(raw[k], se, z, pow2_scale, qr, w0, w1);
-        const int64_t wi = (int64_t)row * cpr + c0 + k * L;
-        if (MODE == kInt4 || MODE == kFp4) ((uint32_t*)out)[wi] = w0;
-        else reinterpret_cast<uint2*>(out)[wi] = make_uint2(w0, w1);
-      }
+      const GroupQ gq = make_group_q<!GLOBAL>(GLOBAL ? __fdiv_rn(s, gs) : s, z);
+      uint32_t a[R], b[R];
+      if (GLOBAL) lane_codes<MODE, true, true, R, false, false, false>(raw, gq, qr, a, b);
+      else if (mx) lane_codes<MODE, false, true, R, true, false, true>(raw, gq, qr, a, b);
+      else if (sym) lane_codes<MODE, false, true, R, false, false, true>(raw, gq, qr, a, b);
+      else lane_codes<MODE, false, true, R, false, true, false>(raw, gq, qr, a, b);
+      store_lane_strided<MODE, R, L>(out, (int64_t)row * cpr + c0, a, b);
     }
   }
 }
@@ -615,8 +738,14 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(
           const float z = zp ? load_zp(zp, zp_kind, pi) : 0.0f;
           if constexpr (XB && MODE != kFake) {
             uint32_t w0 = 0, w1 = 0;
-            const bool p2 = (__float_as_uint(s) & 0x7FFFFFu) == 0u;
-            chunk_codes_bf16<MODE, GLOBAL, ES::is_bf16>(raw[h], s, z, p2, qr, w0, w1);
+            {
+              const uint4 one[1] = {raw[h]};
+              uint32_t a1[1], b1[1];
+              const GroupQ gq = make_group_q<ES::is_bf16 && !GLOBAL>(s, z);
+              if (zp) lane_codes<MODE, GLOBAL, ES::is_bf16, 1, false, true, false>(one, gq, qr, a1, b1);
+              else lane_codes<MODE, GLOBAL, ES::is_bf16, 1, false, false, false>(one, gq, qr, a1, b1);
+              w0 = a1[0]; w1 = b1[0];
+            }
             if (MODE == kInt4 || MODE == kFp4) ((uint32_t*)out)[(int64_t)row * cpr + cc] = w0;
             else reinterpret_cast<uint2*>(out)[(int64_t)row * cpr + cc] = make_uint2(w0, w1);
             continue;
@@ -649,49 +778,39 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(
 // ---------------------------------------------------------------------------------------
 // quantise + pack bf16 weights with given per-group parameters (no g_idx, group a power of two
 // in 8..256): the lane / chunk split of the fused kernel, parameters read once per R chunks.
-template <int SDT, bool GLOBAL, int MODE, int R>
+template <int SDT, bool GLOBAL, int MODE, int R, int L>
 __global__ void __launch_bounds__(kThreads) quant_group_bf16_kernel(
-    const void* __restrict__ W, int N, int K, int64_t ldw, int g, int l_log2, int tx_log2,
+    const void* __restrict__ W, int N, int K, int64_t ldw, int tx_log2,
     const void* __restrict__ scale, const void* __restrict__ zp, int zp_kind, const float* __restrict__ gscale,
     QRange qr, void* __restrict__ out) {
   using T = __nv_bfloat16;
   using ES = Elem<SDT>;
+  constexpr int cpg = R * L;
   const float gs = GLOBAL ? *gscale : 1.0f;
   const int TX = 1 << tx_log2, rows = kThreads >> tx_log2;
   const int tx = threadIdx.x & (TX - 1), ty = threadIdx.x >> tx_log2;
-  const int L = 1 << l_log2, cpg = g >> 3, cpr = K >> 3, gpr = K / g;
-  const int slots = gpr << l_log2;
+  const int cpr = K >> 3, gpr = cpr / cpg;
+  const int slots = gpr * L;
   for (int row = blockIdx.x * rows + ty; row < N; row += gridDim.x * rows) {
     const T* wrow = (const T*)W + (int64_t)row * ldw;
     for (int t = tx; t < slots; t += TX) {
-      const int grp = t >> l_log2, j = t & (L - 1);
+      const int grp = t / L, j = t % L;
       const int c0 = grp * cpg + j;
       uint4 raw[R];
+      {
+        const uint4* src = reinterpret_cast<const uint4*>(wrow) + c0;
 #pragma unroll
-      for (int k = 0; k < R; ++k) raw[k] = ldg_stream(wrow + (int64_t)(c0 + k * L) * 8);
+        for (int k = 0; k < R; ++k) raw[k] = ldg_stream(src + k * L);
+      }
       const int64_t pi = (int64_t)row * gpr + grp;
       float s = ES::load((const typename ES::type*)scale + pi);
       if (GLOBAL) s = __fdiv_rn(s, gs);
       const float z = zp ? load_zp(zp, zp_kind, pi) : 0.0f;
-      const bool p2 = (__float_as_uint(s) & 0x7FFFFFu) == 0u;
-      if (l_log2 == 0) {
-        uint32_t a[R], b[R];
-#pragma unroll
-        for (int k = 0; k < R; ++k) {
-          a[k] = 0; b[k] = 0;
-          chunk_codes_bf16<MODE, GLOBAL, ES::is_bf16>(raw[k], s, z, p2, qr, a[k], b[k]);
-        }
-        store_lane_codes<MODE, R>(out, (int64_t)row * cpr + c0, a, b);
-        continue;
-      }
-#pragma unroll
-      for (int k = 0; k < R; ++k) {
-        uint32_t w0 = 0, w1 = 0;
-        chunk_codes_bf16<MODE, GLOBAL, ES::is_bf16>(raw[k], s, z, p2, qr, w0, w1);
-        const int64_t wi = (int64_t)row * cpr + c0 + k * L;
-        if (MODE == kInt4 || MODE == kFp4) ((uint32_t*)out)[wi] = w0;
-        else reinterpret_cast<uint2*>(out)[wi] = make_uint2(w0, w1);
-      }
+      const GroupQ gq = make_group_q<ES::is_bf16 && !GLOBAL>(s, z);
+      uint32_t a[R], b[R];
+      if (zp) lane_codes<MODE, GLOBAL, ES::is_bf16, R, false, true, false>(raw, gq, qr, a, b);
+      else lane_codes<MODE, GLOBAL, ES::is_bf16, R, false, false, false>(raw, gq, qr, a, b);
+      store_lane_strided<MODE, R, L>(out, (int64_t)row * cpr + c0, a, b);
     }
   }
 }
@@ -708,7 +827,6 @@ __global__ void __launch_bounds__(kThreads) rtn_channel_bf16_kernel(
   __shared__ float s_lo[2][kThreads / 32], s_hi[2][kThreads / 32];
   const int cpr = K >> 3;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool pow2_scale = qc.scale_kind == B200Q_SCALE_E8M0;
   int par = 0;
   for (int row = blockIdx.x; row < N; row += gridDim.x, par ^= 1) {
     const T* wrow = (const T*)W + (int64_t)row * ldw;
@@ -718,14 +836,14 @@ __global__ void __launch_bounds__(kThreads) rtn_channel_bf16_kernel(
       const int c = threadIdx.x + k * kThreads;
       raw[k] = (c < cpr) ? ldg_stream(wrow + (int64_t)c * 8) : make_uint4(0, 0, 0, 0);
     }
-    float lo = INFINITY, hi = -INFINITY;
+    // chunks beyond the row are zeros, which the range contains anyway
+    float lo, hi;
+    {
+      RangeQ mm;
+      mm.first(raw[0]);
 #pragma unroll
-    for (int k = 0; k < R; ++k) {
-      if (threadIdx.x + k * kThreads < cpr) {
-        float a, b;
-        minmax8_bf16(raw[k], a, b);
-        lo = fminf(lo, a); hi = fmaxf(hi, b);
-      }
+      for (int k = 1; k < R; ++k) mm.add(raw[k]);
+      mm.finish(lo, hi);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -742,15 +860,17 @@ __global__ void __launch_bounds__(kThreads) rtn_channel_bf16_kernel(
       ((T*)scale_out)[row] = __float2bfloat16_rn(s);
       if (zp_out) store_zp(zp_out, qc.zp_kind, row, z);
     }
+    const GroupQ gq = make_group_q<true>(s, z);
+    uint32_t a[R], b[R];
+    if (qc.symmetric) lane_codes<MODE, false, true, R, false, false, true>(raw, gq, qr, a, b);
+    else lane_codes<MODE, false, true, R, false, true, false>(raw, gq, qr, a, b);
 #pragma unroll
     for (int k = 0; k < R; ++k) {
       const int c = threadIdx.x + k * kThreads;
       if (c < cpr) {
-        uint32_t w0 = 0, w1 = 0;
-        chunk_codes_bf16<MODE, false, true>(raw[k], s, z, pow2_scale, qr, w0, w1);
         const int64_t wi = (int64_t)row * cpr + c;
-        if (MODE == kInt4 || MODE == kFp4) ((uint32_t*)out)[wi] = w0;
-        else reinterpret_cast<uint2*>(out)[wi] = make_uint2(w0, w1);
+        if (MODE == kInt4 || MODE == kFp4) ((uint32_t*)out)[wi] = a[k];
+        else reinterpret_cast<uint2*>(out)[wi] = make_uint2(a[k], b[k]);
       }
     }
   }

@@ -114,6 +114,17 @@ class QuantizationMixin(HooksMixin):
         self._resolved: Optional[dict] = None
         self._module_names: dict = {}
 
+    def recipe_args(self) -> dict:
+        """Constructor arguments for ``recipe.yaml`` (unset ones are left out by the writer)."""
+        args = dict(config_groups=self.config_groups, targets=self.targets, ignore=self.ignore, scheme=self.scheme,
+                    kv_cache_scheme=self.kv_cache_scheme, weight_observer=self.weight_observer,
+                    input_observer=self.input_observer, output_observer=self.output_observer,
+                    observer=self.observer,
+                    bypass_divisibility_checks=self.bypass_divisibility_checks or None)
+        if isinstance(args["config_groups"], dict):
+            args["config_groups"] = {k: (_plain_scheme(v)) for k, v in args["config_groups"].items()}
+        return args
+
     # ---- scheme resolution ---------------------------------------------------------------
     def _apply_observer_overrides(self, scheme: QuantizationScheme) -> QuantizationScheme:
         has_individual = any(o is not None for o in (self.weight_observer, self.input_observer,
@@ -322,6 +333,14 @@ class GPTQModifier(QuantizationMixin):
         self._hooked: list = []        # every module that got a calibration hook
         self._done: set = set()        # modules whose quantised weight has been written
         self.losses: dict = {}
+
+    def recipe_args(self) -> dict:
+        args = super().recipe_args()
+        args.update(block_size=self.block_size, dampening_frac=self.dampening_frac,
+                    offload_hessians=self.offload_hessians or None)
+        if self.actorder is not _UNSET:
+            args["actorder"] = self.actorder   # None is dropped by the writer, as the reference drops it
+        return args
 
     # ---- config ------------------------------------------------------------------------------
     def resolve_quantization_config(self) -> dict:
@@ -542,6 +561,23 @@ class GPTQModifier(QuantizationMixin):
                              f"compressed: {names}{' ...' if len(missed) > 8 else ''}")
         self._groups, self._num_samples, self._hooked = {}, {}, []
         return True
+
+
+def _plain_scheme(g):
+    """A config group as plain data for the recipe file."""
+    if isinstance(g, dict):
+        return {k: (_plain_scheme(v) if isinstance(v, (dict, QuantizationArgs, QuantizationScheme)) else v)
+                for k, v in g.items()}
+    out = {}
+    for k, v in vars(g).items():
+        if v is None or v == {} or v is False:
+            continue
+        if isinstance(v, (QuantizationArgs, QuantizationScheme)):
+            v = _plain_scheme(v)
+        elif isinstance(v, torch.dtype):
+            v = str(v)
+        out[k] = v
+    return out
 
 
 def _with_actorder(qargs: QuantizationArgs, actorder):

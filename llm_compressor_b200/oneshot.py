@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import json
 import os
+import re
 from typing import Iterable, Optional
 
 import torch
@@ -191,7 +192,7 @@ def oneshot(model, recipe=None, dataset=None, num_calibration_samples: int = 512
     for m in modifiers:
         m.on_finalize(model)
     if output_dir is not None:
-        save_compressed_model(model, output_dir, compress=save_compressed)
+        save_compressed_model(model, output_dir, compress=save_compressed, recipe=modifiers)
     return model
 
 
@@ -251,28 +252,119 @@ def compressed_state_dict(model, compress: bool = True):
     return state, qconfig
 
 
-def save_compressed_model(model, output_dir: str, compress: bool = True) -> dict:
-    """Write the compressed-tensors checkpoint layout: ``model.safetensors`` with
-    ``<module>.weight_packed`` / ``weight_scale`` / ``weight_shape`` / ... per quantised module,
-    and ``config.json`` carrying ``quantization_config`` (CT model_compressor.py:177-213).
-    Only rank 0 writes.  Returns the state dict that was written."""
+FORMAT_VERSION = "0.15.0.1"   # compressed-tensors layout this writer produces
+
+
+def _ct_version() -> str:
+    try:
+        import compressed_tensors
+        return str(compressed_tensors.__version__)
+    except Exception:  # noqa: BLE001 - the package is optional here
+        return FORMAT_VERSION
+
+
+def _parse_size(v) -> int:
+    if isinstance(v, (int, float)):
+        return int(v)
+    m = re.fullmatch(r"\s*([0-9.]+)\s*([KMGT]?)i?B?\s*", str(v), re.IGNORECASE)
+    if not m:
+        raise ValueError(f"cannot read max_shard_size {v!r}")
+    return int(float(m.group(1)) * {"": 1, "K": 10**3, "M": 10**6, "G": 10**9, "T": 10**12}[m.group(2).upper()])
+
+
+def recipe_dict(modifiers, stage: str = "default") -> dict:
+    """``{stage_stage: {stage_modifiers: {ModifierClass: args}}}``, the layout of the reference's
+    recipe.yaml (src/llmcompressor/recipe/utils.py:56-96)."""
+    group = {}
+    for m in modifiers:
+        args = m.recipe_args() if hasattr(m, "recipe_args") else {}
+        group[type(m).__name__] = {k: v for k, v in args.items() if v is not None}
+    return {f"{stage}_stage": {f"{stage}_modifiers": group}}
+
+
+def _drop_retied_output_embedding(model, state: dict, cfg: dict) -> None:
+    """An output embedding that holds exactly the input embedding's tensors is one table: write it
+    once and mark the config tied (compressed_tensors_utils.py:37-80)."""
+    get_in, get_out = getattr(model, "get_input_embeddings", None), getattr(model, "get_output_embeddings", None)
+    if not callable(get_in) or not callable(get_out):
+        return
+    try:
+        inp, out = get_in(), get_out()
+    except Exception:  # noqa: BLE001 - models without embeddings
+        return
+    if inp is None or out is None or inp is out:
+        return
+    names = {id(m): n for n, m in model.named_modules()}
+    ni, no = names.get(id(inp)), names.get(id(out))
+    if ni is None or no is None:
+        return
+    ti = {k[len(ni) + 1:]: v for k, v in state.items() if k.startswith(ni + ".")}
+    to = {k[len(no) + 1:]: v for k, v in state.items() if k.startswith(no + ".")}
+    if not ti or ti.keys() != to.keys():
+        return
+    if not all(ti[k].shape == to[k].shape and ti[k].dtype == to[k].dtype and
+               torch.equal(ti[k].view(torch.uint8) if ti[k].dtype.itemsize == 1 else ti[k],
+                           to[k].view(torch.uint8) if to[k].dtype.itemsize == 1 else to[k]) for k in ti):
+        return
+    for k in to:
+        del state[f"{no}.{k}"]
+    cfg["tie_word_embeddings"] = True
+
+
+def save_compressed_model(model, output_dir: str, compress: bool = True, recipe=None,
+                          max_shard_size="20GB") -> dict:
+    """Write the compressed-tensors checkpoint layout: safetensors with
+    ``<module>.weight_packed`` / ``weight_scale`` / ``weight_shape`` / ... per quantised module
+    (one ``model.safetensors``, or ``model-0000i-of-0000n.safetensors`` plus
+    ``model.safetensors.index.json`` once the tensors exceed ``max_shard_size``), ``config.json``
+    carrying ``quantization_config`` with its ``version`` (CT model_compressor.py:177-213) and, when
+    ``recipe`` (a list of modifiers) is given, ``recipe.yaml``
+    (src/llmcompressor/transformers/compression/compressed_tensors_utils.py:106-176,231-246).
+    Only rank 0 packs and writes.  Returns the state dict that was written (empty on other ranks)."""
     from safetensors.torch import save_file
 
-    state, qconfig = compressed_state_dict(model, compress)
+    state = {}
     if bdist.rank() == 0:
+        state, qconfig = compressed_state_dict(model, compress)
         os.makedirs(output_dir, exist_ok=True)
-        # tied tensors (embeddings / lm_head) share storage; safetensors wants distinct buffers
+        cfg = model.config.to_dict() if hasattr(model, "config") and hasattr(model.config, "to_dict") else {}
+        _drop_retied_output_embedding(model, state, cfg)
+        # tied tensors that remain share storage; safetensors wants distinct buffers
         seen = {}
         for k in list(state):
             p = state[k].data_ptr()
             if p in seen and state[k].numel():
                 state[k] = state[k].clone()
             seen[p] = k
-        save_file(state, os.path.join(output_dir, "model.safetensors"), metadata={"format": "pt"})
-        cfg = model.config.to_dict() if hasattr(model, "config") and hasattr(model.config, "to_dict") else {}
-        cfg["quantization_config"] = qconfig
+        limit = _parse_size(max_shard_size)
+        shards, cur, cur_bytes = [], {}, 0
+        for k, v in state.items():
+            nb = v.numel() * v.element_size()
+            if cur and cur_bytes + nb > limit:
+                shards.append(cur)
+                cur, cur_bytes = {}, 0
+            cur[k] = v
+            cur_bytes += nb
+        shards.append(cur)
+        if len(shards) == 1:
+            save_file(shards[0], os.path.join(output_dir, "model.safetensors"), metadata={"format": "pt"})
+        else:
+            weight_map = {}
+            for i, sh in enumerate(shards):
+                fname = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+                save_file(sh, os.path.join(output_dir, fname), metadata={"format": "pt"})
+                weight_map.update({k: fname for k in sh})
+            total = sum(v.numel() * v.element_size() for v in state.values())
+            with open(os.path.join(output_dir, "model.safetensors.index.json"), "w") as f:
+                json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f, indent=2)
+        cfg["quantization_config"] = {"version": _ct_version(), **qconfig}
         with open(os.path.join(output_dir, "config.json"), "w") as f:
-            json.dump(cfg, f, indent=2, default=str)
+            json.dump(cfg, f, indent=2, sort_keys=True, default=str)
+        if recipe:
+            import yaml
+            mods = list(recipe) if isinstance(recipe, (list, tuple)) else [recipe]
+            with open(os.path.join(output_dir, "recipe.yaml"), "w") as f:
+                yaml.dump(recipe_dict(mods), f, allow_unicode=True, sort_keys=False, default_flow_style=None, width=88)
     if bdist.is_distributed():
         torch.distributed.barrier()
     return state
