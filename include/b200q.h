@@ -65,6 +65,11 @@ const char* b200q_last_error(void);
 /* Number of kernels this library has launched in the process so far (diagnostic; no
  * counterpart in the reference). */
 long long b200q_launch_count(void);
+/* The streaming quantize / pack kernels that are fed by TMA copies wait for them with a bound.  If
+ * such a wait ever ran out on the current device since the last call, this returns
+ * B200Q_ERR_DEVICE once (the affected launch left its output incomplete), otherwise B200Q_OK.
+ * Synchronises the device.  No counterpart in the reference. */
+int b200q_take_wait_status(void);
 
 /* ------------------------------------------------------------------ observers */
 
@@ -89,6 +94,12 @@ int b200q_absmax_accumulate(const void* min_vals, const void* max_vals, int dtyp
                             float* absmax, void* stream);
 int b200q_global_scale_finalize(const float* absmax, int stat_dtype, float* global_scale,
                                 void* stream);
+/* Same accumulation straight from a weight matrix (bf16, K % 8 == 0, 16-byte aligned rows; other
+ * inputs return B200Q_ERR_UNSUPPORTED and go through b200q_observe_minmax): the first pass of
+ * NVFP4 weight quantisation when no per-group statistics are wanted
+ * (src/observers/base.py:78-96 followed by CT/quantization/utils/helpers.py:309-338). */
+int b200q_absmax_accumulate_weight(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw,
+                                   float* absmax, void* stream);
 
 /* scale / zero point from statistics.  Replaces calculate_qparams
  * (CT/quantization/utils/helpers.py:50-137) including the MX exponent rule

@@ -46,10 +46,12 @@ SIGNATURES = {
     "b200q_version": (C.c_char_p, []),
     "b200q_last_error": (C.c_char_p, []),
     "b200q_launch_count": (C.c_longlong, []),
+    "b200q_take_wait_status": (_i, []),
     "b200q_observe_minmax_workspace_bytes": (C.c_size_t, [_i64, _i64, _qa]),
     "b200q_observe_minmax": (_i, [_p, _i, _i64, _i64, _i64, _qa, _p, _p, _p, _p]),
     "b200q_absmax_accumulate": (_i, [_p, _p, _i, _i64, _p, _p]),
     "b200q_global_scale_finalize": (_i, [_p, _i, _p, _p]),
+    "b200q_absmax_accumulate_weight": (_i, [_p, _i, _i64, _i64, _i64, _p, _p]),
     "b200q_qparams": (_i, [_p, _p, _i, _i64, _qa, _p, _p, _p, _p]),
     "b200q_observe_mse_workspace_bytes": (C.c_size_t, [_i64, _i64, _qa, _i]),
     "b200q_observe_mse_steps": (_i, [_d, _d]),

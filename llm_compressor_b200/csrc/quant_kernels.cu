@@ -5,7 +5,9 @@
 // write packed codes with 4..16-byte stores.  Grids are whole multiples of the SM count.
 #include "common.cuh"
 
+#include <algorithm>
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -155,7 +157,40 @@ __device__ __forceinline__ void store8(void* base, int64_t off, const float (&v)
 
 }  // namespace b200q
 #include "stream_kernels.cuh"
+#include "stream_tma.cuh"
 namespace b200q {
+
+// ---- tensor map of a bf16 weight for the TMA-fed kernels: rows cut into 128-byte pieces -------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn tensor_map_encoder() {
+  static const EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      return (EncodeTiledFn)sym;
+    return (EncodeTiledFn) nullptr;
+  }();
+  return fn;
+}
+// dims (64 elements, K/64 pieces, N rows), box (64, 32, 1) = one 4 KiB tile, 128-byte swizzle
+static bool make_weight_tile_map(CUtensorMap* m, const void* W, int64_t N, int64_t K, int64_t ldw) {
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {64u, (cuuint64_t)(K / 64), (cuuint64_t)N};
+  cuuint64_t strides[2] = {128u, (cuuint64_t)ldw * 2u};
+  cuuint32_t box[3] = {64u, 32u, 1u};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(W), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+static bool tma_path_enabled() {
+  static const bool on = [] { const char* e = getenv("B200Q_STREAM_TMA"); return !(e && e[0] == '0'); }();
+  return on;
+}
 
 static bool vec_ok(const void* p, int64_t K, int64_t ld, int elem_bytes) {
   return (K % 8 == 0) && (ld % 8 == 0) && (((uintptr_t)p) % 16 == 0) && elem_bytes > 0;
@@ -360,6 +395,45 @@ __global__ void absmax_kernel(const void* __restrict__ mn, const void* __restric
   // non-negative floats order like their bit patterns
   if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(absmax), __float_as_int(a));
 }
+// largest magnitude of a whole bf16 matrix, folded into *absmax: 16-byte loads, four in flight,
+// sign bits cleared and a packed unsigned 16-bit maximum (bf16 magnitudes order like integers)
+__global__ void __launch_bounds__(256) absmax_weight_bf16_kernel(const void* __restrict__ W, int64_t N, int64_t K,
+                                                                 int64_t ldw, float* __restrict__ absmax) {
+  const int64_t cpr = K >> 3, total = N * cpr;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  uint32_t m = 0;
+  int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  auto chunk = [&](int64_t i) {
+    const int64_t row = i / cpr, cc = i - row * cpr;
+    return stream::ldg_stream((const __nv_bfloat16*)W + row * ldw + cc * 8);
+  };
+  for (; c + 3 * step < total; c += 4 * step) {
+    const uint4 a = chunk(c), b = chunk(c + step), d = chunk(c + 2 * step), e = chunk(c + 3 * step);
+    const uint4 v[4] = {a, b, d, e};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      m = __vimax3_u16x2(m, v[k].x & 0x7FFF7FFFu, v[k].y & 0x7FFF7FFFu);
+      m = __vimax3_u16x2(m, v[k].z & 0x7FFF7FFFu, v[k].w & 0x7FFF7FFFu);
+    }
+  }
+  for (; c < total; c += step) {
+    const uint4 a = chunk(c);
+    m = __vimax3_u16x2(m, a.x & 0x7FFF7FFFu, a.y & 0x7FFF7FFFu);
+    m = __vimax3_u16x2(m, a.z & 0x7FFF7FFFu, a.w & 0x7FFF7FFFu);
+  }
+  uint32_t h = max(m & 0xFFFFu, m >> 16);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) h = max(h, __shfl_xor_sync(0xffffffffu, h, o));
+  __shared__ uint32_t s_m[8];
+  if ((threadIdx.x & 31) == 0) s_m[threadIdx.x >> 5] = h;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) h = max(h, s_m[w]);
+    // non-negative floats order like their bit patterns
+    atomicMax(reinterpret_cast<int*>(absmax), (int)(h << 16));
+  }
+}
+
 __global__ void global_scale_kernel(const float* __restrict__ absmax, int stat_bf16,
                                     float* __restrict__ out) {
   float a = *absmax;
@@ -691,6 +765,15 @@ const char* b200q_version(void) { return "b200q 0.1 (sm_100a)"; }
 const char* b200q_last_error(void) { return g_last_error.c_str(); }
 long long b200q_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+int b200q_take_wait_status(void) {
+  int v = 0;
+  B200Q_TRY(cudaMemcpyFromSymbol(&v, tma::g_wait_expired, sizeof(int)));
+  if (v == 0) return B200Q_OK;
+  v = 0;
+  B200Q_TRY(cudaMemcpyToSymbol(tma::g_wait_expired, &v, sizeof(int)));
+  return B200Q_ERR_DEVICE;
+}
+
 size_t b200q_observe_minmax_workspace_bytes(int64_t, int64_t, const b200q_qargs* qa) {
   return (qa && qa->strategy == B200Q_TENSOR) ? sizeof(float) * 2 * kTensorPartialBlocks : 0;
 }
@@ -712,6 +795,16 @@ int b200q_absmax_accumulate(const void* mn, const void* mx, int dtype, int64_t c
   if (dtype == B200Q_BF16) absmax_kernel<B200Q_BF16><<<grid, 256, 0, st>>>(mn, mx, count, absmax);
   else if (dtype == B200Q_F32) absmax_kernel<B200Q_F32><<<grid, 256, 0, st>>>(mn, mx, count, absmax);
   else return B200Q_ERR_UNSUPPORTED;
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_absmax_accumulate_weight(const void* W, int wdtype, int64_t N, int64_t K, int64_t ldw, float* absmax,
+                                   void* stream) {
+  if (!W || !absmax || N <= 0 || K <= 0 || ldw < K) return B200Q_ERR_ARG;
+  if (wdtype != B200Q_BF16 || !vec_ok(W, K, ldw, 2)) return B200Q_ERR_UNSUPPORTED;
+  const int grid = grid_for((N * (K >> 3) + 1023) / 1024, 8);
+  absmax_weight_bf16_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(W, N, K, ldw, absmax);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
@@ -808,8 +901,44 @@ static int rtn_impl(const void* W, int64_t N, int64_t K, int64_t ldw, const b200
     if (!(pow2(g) && g >= 8 && g <= 256 && K % g == 0)) return B200Q_ERR_UNSUPPORTED;
     stream::RowTiling t = stream::make_tiling(N, K, 6);
     const int txl = __builtin_ctz(t.tx);
+    // bf16 weights whose rows are whole 2048-element tiles: the TMA-fed kernel
+    if constexpr (DT == B200Q_BF16) {
+      const bool aligned = (((uintptr_t)scale_out) % 16 == 0) && (!zp_out || ((uintptr_t)zp_out) % 4 == 0) &&
+                           (!scale_store || ((uintptr_t)scale_store) % 4 == 0) && (((uintptr_t)out) % 16 == 0);
+      if (tma_path_enabled() && aligned && K % tma::kTileElems == 0 && (g == 16 || g == 32 || g == 128) &&
+          N < (1 << 30) && (!gscale || (g == 16 && qr.kind == kFp4))) {
+        CUtensorMap wm;
+        if (make_weight_tile_map(&wm, W, N, K, ldw)) {
+          const int64_t tiles = N * (K / tma::kTileElems);
+          const int gridt = (int)std::min<int64_t>((tiles + tma::kWarps - 1) / tma::kWarps, 2 * kNumSMs);
+#define B200Q_T3(MODE, GL, GG)                                                                                   \
+  do {                                                                                                           \
+    B200Q_TRY(cudaFuncSetAttribute(tma::rtn_group_tma_kernel<stream::MODE, GL, GG>,                              \
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, tma::kSmemBytes));               \
+    tma::rtn_group_tma_kernel<stream::MODE, GL, GG><<<gridt, tma::kWarps * 32, tma::kSmemBytes, st>>>(           \
+        wm, (int)N, (int)K, qc, qr, gscale, scale_out, zp_out, scale_store, out);                                \
+  } while (0)
+#define B200Q_T2(MODE)                                     \
+  do {                                                     \
+    if (g == 16) B200Q_T3(MODE, false, 16);                \
+    else if (g == 32) B200Q_T3(MODE, false, 32);           \
+    else B200Q_T3(MODE, false, 128);                       \
+  } while (0)
+          if (gscale) B200Q_T3(kFp4, true, 16);
+          else if (qr.kind == kInt && qa->num_bits == 4) B200Q_T2(kInt4);
+          else if (qr.kind == kInt && qa->num_bits == 8) B200Q_T2(kInt8Word);
+          else if (qr.kind == kFp8) B200Q_T2(kByte);
+          else if (qr.kind == kFp4) B200Q_T2(kFp4);
+          else return B200Q_ERR_UNSUPPORTED;
+#undef B200Q_T2
+#undef B200Q_T3
+          B200Q_LAUNCH_CHECK();
+          return B200Q_OK;
+        }
+      }
+    }
     // bf16 weights: R chunks per lane, L lanes per group (both compile-time)
-    const stream::GroupSplit gsp = stream::make_group_split(g);
+    const stream::GroupSplit gsp = stream::make_group_split(g, 4);
     const int64_t slots = (K / g) * gsp.L;
     int tx2 = 32;
     while (tx2 < 256 && tx2 < slots) tx2 <<= 1;
@@ -824,8 +953,8 @@ static int rtn_impl(const void* W, int64_t N, int64_t K, int64_t ldw, const b200
       case 16: B200Q_RB3(MODE, GL, 2, 1); break;     \
       case 32: B200Q_RB3(MODE, GL, 4, 1); break;     \
       case 64: B200Q_RB3(MODE, GL, 4, 2); break;     \
-      case 128: B200Q_RB3(MODE, GL, 8, 2); break;    \
-      default: B200Q_RB3(MODE, GL, 8, 4); break;     \
+      case 128: B200Q_RB3(MODE, GL, 4, 4); break;    \
+      default: B200Q_RB3(MODE, GL, 4, 8); break;     \
     }                                                \
   } while (0)
 #define B200Q_RB(MODE)                                                            \

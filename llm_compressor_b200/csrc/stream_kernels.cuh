@@ -260,12 +260,12 @@ __device__ __forceinline__ uint32_t tail8_fp4(const uint32_t (&v)[4]) {
 // NVFP4: float32 arithmetic (the effective scale scale/global_scale is float32).  The code
 // is a monotone function of the quotient, so equal codes at both ends of a small interval
 // around x*(1/s) settle it; otherwise `unsafe`.
-__device__ __forceinline__ uint32_t nvfp4_8(const uint4& raw, float rs, bool& unsafe) {
+__device__ __forceinline__ uint32_t nvfp4_8(const uint4& raw, float rs, bool& unsafe, float margin = 0x1p-21f) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
   // both ends of an interval that holds the exact quotient (reciprocal, its scaling and the
-  // product each round by 2^-23 or less; the margin is 2^-21).  The fused "+ 0" turns a -0.0
-  // weight into +0 like the reference's "+ zero_point".
-  const float rlo = rs * (1.0f - 0x1p-21f), rhi = rs * (1.0f + 0x1p-21f);
+  // product each round by 2^-23 or less; the margin is 2^-21 unless the caller's reciprocal is
+  // looser).  The fused "+ 0" turns a -0.0 weight into +0 like the reference's "+ zero_point".
+  const float rlo = rs * (1.0f - margin), rhi = rs * (1.0f + margin);
   float lo[8], hi[8];
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
@@ -401,6 +401,25 @@ __device__ __forceinline__ void minmax8_bf16(const uint4& raw, float& lo, float&
 // negative and one packed signed maximum finds the maximum if it is positive; whatever they
 // return otherwise has the other sign and is replaced by zero by the clamp.  Three inputs per
 // instruction (VIMNMX3): 4 instructions per chunk of 8 elements.
+#ifdef B200Q_RANGE_HMNMX
+struct RangeQ {
+  __nv_bfloat162 mn, mx;
+  __device__ __forceinline__ void first(const uint4& raw) {
+    const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    mx = __hmax2(__hmax2(w[0], w[1]), __hmax2(w[2], w[3]));
+    mn = __hmin2(__hmin2(w[0], w[1]), __hmin2(w[2], w[3]));
+  }
+  __device__ __forceinline__ void add(const uint4& raw) {
+    const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    mx = __hmax2(__hmax2(mx, w[0]), __hmax2(__hmax2(w[1], w[2]), w[3]));
+    mn = __hmin2(__hmin2(mn, w[0]), __hmin2(__hmin2(w[1], w[2]), w[3]));
+  }
+  __device__ __forceinline__ void finish(float& lo, float& hi) const {
+    hi = fmaxf(fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y)), 0.0f);
+    lo = fminf(fminf(__bfloat162float(mn.x), __bfloat162float(mn.y)), 0.0f);
+  }
+};
+#else
 struct RangeQ {
   uint32_t umax, smax;
   __device__ __forceinline__ void first(const uint4& raw) {
@@ -419,6 +438,7 @@ struct RangeQ {
     hi = fmaxf(__uint_as_float((uint32_t)sv << 16), 0.0f);
   }
 };
+#endif
 // min / max kept as bf16 pairs across several chunks, widened once at the end
 struct MinMax2 {
   __nv_bfloat162 mn, mx;
@@ -543,9 +563,11 @@ inline GroupSplit make_group_split(int g, int rmax = 8) {
   GroupSplit s;
   // groups of up to 32 elements: one lane per group (no shuffles, contiguous wide stores); wider
   // groups are shared by lanes so that a load instruction stays dense (one lane per 128-element
-  // group measured 0.41 of the HBM peak against 0.60-0.65)
+  // group measured 0.41 of the HBM peak against 0.60-0.65).  For 128-element groups 4 lanes x 4
+  // chunks measured best (82 us for 8 x 2, 68 for 4 x 4, 75 for 2 x 8, 123 for 1 x 16 on a
+  // 16384 x 8192 matrix): a load instruction of 4 lanes covers half a 128-byte line.
   s.R = chunks >= 16 ? 8 : (chunks >= 8 ? 4 : chunks);
-  if (s.R > rmax) s.R = rmax;   // measured: 8 pays when statistics are computed, 4 when they are given
+  if (s.R > rmax) s.R = rmax;
   s.L = chunks / s.R;
   return s;
 }

@@ -249,9 +249,15 @@ def nvfp4_two_pass(w, partners=()):
     _need_cuda(w, *partners)
     targs = QuantizationArgs(num_bits=4, type="float", symmetric=True, strategy="tensor")
     absmax = torch.zeros(1, dtype=torch.float32, device=w.device)
+    lib = _lib.load()
     for t in (w, *partners):
-        mn, mx = observe_minmax(t, targs)
-        absmax_accumulate(mn, mx, absmax)
+        N, K, ld = _2d(t)
+        rc = lib.b200q_absmax_accumulate_weight(ptr(t), _dt(t), N, K, ld, ptr(absmax), stream_ptr())
+        if rc == -2:   # shape / dtype the streaming kernel does not take
+            mn, mx = observe_minmax(t, targs)
+            absmax_accumulate(mn, mx, absmax)
+        else:
+            check(rc, "b200q_absmax_accumulate_weight")
     gs = global_scale_from_absmax(absmax, w.dtype)
     out = nvfp4_quantize_pack(w, gs)
     out["global_scale"] = gs

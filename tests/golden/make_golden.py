@@ -1,9 +1,9 @@
 """Generate ``tests/golden/golden.pt`` from the real reference.
 
-Run in a container that has the llm-compressor checkout (LLMC_REFERENCE_ROOT,
-default /root/reference) and compressed-tensors installed:
+Run in a container that has an llm-compressor checkout and compressed-tensors installed, with
+LLMC_REFERENCE_ROOT pointing at the checkout:
 
-    TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py
+    LLMC_REFERENCE_ROOT=<checkout> TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py
 
 What goes into the file
   known_answers  vectors held by the reference's OWN tests for this path, read out of

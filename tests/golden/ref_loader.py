@@ -17,11 +17,12 @@ import types
 
 os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
 
-REF_ROOT = os.environ.get("LLMC_REFERENCE_ROOT", "/root/reference")
+# the llm-compressor checkout to load; fixture generation and the plug-in test need it set
+REF_ROOT = os.environ.get("LLMC_REFERENCE_ROOT", "")
 
 
 def reference_available() -> bool:
-    return os.path.isdir(os.path.join(REF_ROOT, "src", "llmcompressor"))
+    return bool(REF_ROOT) and os.path.isdir(os.path.join(REF_ROOT, "src", "llmcompressor"))
 
 
 def _install_shim():

@@ -267,3 +267,44 @@ def test_nvfp4_two_pass_equals_observer_then_compressor(N, K):
         assert bits_equal(r["global_scale"], qp["global_scale"])
         assert bits_equal(r["codes"], ref["weight_packed"])
         assert bits_equal(r["scale_store"], ref["weight_scale"])
+
+
+@pytest.mark.parametrize("name", ["w4a16_g128", "w4a16_g32", "w4a16_asym_g128", "w8_g128", "mxfp4", "mxfp8"])
+@pytest.mark.parametrize("N,K", [(5, 2048), (300, 4096), (64, 14336)])
+def test_fused_rtn_whole_tile_rows(golden, name, N, K):
+    """Rows made of whole 2048-element tiles take the TMA-fed kernel: same bits as the oracle."""
+    args = args_from(golden["ct_cases"][name]["args"])
+    spec = spec_from(golden["ct_cases"][name]["args"])
+    w = synth_weight(N, K, seed=N + K + 1)
+    oqp = oracle.WeightObserver(spec)(w).get_qparams()
+    ref = oracle.compress_weight({"weight": w, "weight_scale": oqp["scale"].to(w.dtype),
+                                  "weight_zero_point": oqp["zero_point"]}, spec)
+    r = ops.rtn_quantize_pack(w.to(DEV), args)
+    assert bits_equal(r["scale"], oqp["scale"].to(w.dtype))
+    assert bits_equal(r["zero_point"], oqp["zero_point"])
+    if "weight_packed" in ref:
+        assert bits_equal(r["codes"], ref["weight_packed"]), mismatch(r["codes"], ref["weight_packed"])
+    else:
+        exp = ref["weight"]
+        if exp.dtype == torch.int8:
+            exp = oracle.pack_int32(exp, 8)
+        assert bits_equal(r["codes"], exp), mismatch(r["codes"], exp)
+    if args.is_mx:
+        assert bits_equal(r["scale_store"], ref["weight_scale"])
+    from llm_compressor_b200 import _lib
+    assert _lib.load().b200q_take_wait_status() == 0
+
+
+@pytest.mark.parametrize("N,K", [(7, 2048), (130, 6144)])
+def test_fused_nvfp4_whole_tile_rows(N, K):
+    spec = oracle.preset("NVFP4A16")
+    w = synth_weight(N, K, seed=N + K)
+    obs = oracle.WeightObserver(spec)
+    obs(w)
+    qp = obs.get_qparams()
+    ref = oracle.compress_weight({"weight": w, "weight_scale": qp["scale"].to(w.dtype), "weight_zero_point": qp["zero_point"],
+                                  "weight_global_scale": qp["global_scale"]}, spec)
+    r = ops.nvfp4_quantize_pack(w.to(DEV), qp["global_scale"].to(DEV))
+    assert bits_equal(r["codes"], ref["weight_packed"])
+    assert bits_equal(r["scale_store"], ref["weight_scale"])
+    assert bits_equal(r["scale"], qp["scale"].to(w.dtype))
