@@ -578,6 +578,19 @@ def run_b200(args):
         sec, cores, desc = cpu_reference_step_seconds()
         cpu = {"value": sec * LAYERS, "unit": "s", "cores": cores, "kind": "port", "sample": desc}
 
+    # the whole oneshot() run on the 8B-architecture model (after everything above has been measured)
+    oneshot_line = None
+    if not args.no_oneshot:
+        results = None
+        del bench
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            oneshot_line = run_oneshot_arm(rank, world, dev, args.oneshot_seqs, args.oneshot_batch)
+        except Exception as e:  # noqa: BLE001 - the hot-path line must still be printed
+            oneshot_line = {"error": f"{type(e).__name__}: {e}"[:400]}
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -588,6 +601,7 @@ def run_b200(args):
                             "(llm_compressor_b200.dist owner assignment, reduction, broadcast)",
             "phases_ms": phases, "solve_ms_per_step": solve_steps, "solve_jobs_ms": jobs, "roofline": roofline,
             "parity_check": parity, "pack_gbs": pack, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "oneshot": oneshot_line,
             "clocks": clocks,
             "published_reference": {"value": 745.03, "unit": "s", "note": "whole oneshot incl. model forwards, "
                                     "GPU not stated (docs/guides/big_models_and_distributed/distributed_oneshot.md:107-111)"},
@@ -595,6 +609,73 @@ def run_b200(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_oneshot_arm(rank, world, dev, seqs, batch_size):
+    """The metric as BASELINE.json words it: wall seconds of ``oneshot()`` with ``GPTQModifier`` (W4A16,
+    g128, block 128, damp 0.01, no act-order, lm_head ignored, sequential pipeline) on a random-init
+    Llama-3-8B-architecture ``LlamaForCausalLM`` with 512 x 2048 random calibration tokens.  Under
+    torchrun every rank holds the model and calibrates its share of the sequences; Hessians are
+    reduced to their owners, owners solve, results are broadcast (the product path, as it is).
+    Returns the dict for the JSON line (rank 0) or None."""
+    import torch
+    import torch.distributed as dist
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from llm_compressor_b200 import GPTQModifier, oneshot
+    from llm_compressor_b200.oneshot import compressed_state_dict  # noqa: F401  (pack is timed below)
+    from llm_compressor_b200 import compressors
+
+    cfg = LlamaConfig(hidden_size=HIDDEN, intermediate_size=INTER, num_hidden_layers=LAYERS, num_attention_heads=32,
+                      num_key_value_heads=8, vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0,
+                      max_position_embeddings=8192, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = LlamaForCausalLM(cfg)
+    finally:
+        torch.set_default_dtype(old)
+    model.eval().requires_grad_(False)
+    data = torch.randint(0, cfg.vocab_size, (seqs, SEQ_LEN), generator=torch.Generator().manual_seed(1))
+    recipe = GPTQModifier(targets="Linear", scheme="W4A16", ignore=["lm_head"], actorder=None, block_size=128,
+                          dampening_frac=0.01)
+    phases = {}
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    oneshot(model, recipe=recipe, dataset=data, num_calibration_samples=seqs, batch_size=batch_size,
+            phase_times=phases)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    # packing of every quantised module on the device (what the checkpoint writer runs before it copies out)
+    t1 = time.perf_counter()
+    n_packed = 0
+    if rank == 0:
+        for _n, m in model.named_modules():
+            if hasattr(m, "quantization_scheme") and hasattr(m, "weight_scale"):
+                compressors.compress_state_dict({"weight": m.weight.data, "weight_scale": m.weight_scale.data,
+                                                 "weight_zero_point": m.weight_zero_point.data}, m.quantization_scheme)
+                n_packed += 1
+        torch.cuda.synchronize()
+    pack_s = time.perf_counter() - t1
+    t = torch.tensor([wall], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    losses = list(recipe.losses.values())
+    finite = all(v == v and v < float("inf") for v in losses)
+    if rank != 0:
+        return None
+    return {"metric": "gptq_w4a16_llama3_8b_oneshot_wall_s", "wall_s": float(t.item()), "unit": "s",
+            "phases_s": {k: round(v, 2) for k, v in phases.items()}, "pack_s": round(pack_s, 3),
+            "modules_packed": n_packed, "modules_solved_on_rank0": len(losses), "losses_finite": finite,
+            "config": {"workload": "configs[2] through oneshot(): random-init Llama-3-8B-architecture LlamaForCausalLM, "
+                                   "GPTQModifier W4A16 g128, %d x %d calibration tokens" % (seqs, SEQ_LEN),
+                       "batch_size": batch_size, "pipeline": "sequential, activations resident in HBM"},
+            "published_reference_s": {"1_gpu": 745.03, "2_gpu": 372.0, "4_gpu": 264.0,
+                                      "note": "docs/guides/big_models_and_distributed/distributed_oneshot.md:107-113, GPU not stated"}}
 
 
 def pack_micro(steps, peaks, timed, g, dev):
@@ -776,6 +857,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-pack", action="store_true", help="skip the quantize/pack kernel figures")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the last timed step")
+    ap.add_argument("--no-oneshot", action="store_true", help="skip the whole-model oneshot() run")
+    ap.add_argument("--oneshot-seqs", type=int, default=SEQS)
+    ap.add_argument("--oneshot-batch", type=int, default=8, help="sequences per calibration batch of the oneshot run")
     args = ap.parse_args()
     if args.micro:
         run_micro(args)

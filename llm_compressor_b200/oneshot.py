@@ -84,7 +84,30 @@ def _sequential_layers(model, sequential_targets):
     return out
 
 
-def _run_sequential(model, modifiers, batches, sequential_targets):
+class _PhaseClock:
+    """Wall seconds per phase, with a device synchronisation at every boundary (only when asked for)."""
+
+    def __init__(self, sink):
+        self.sink = sink
+        self.t = None
+        if sink is not None and torch.cuda.is_available():
+            torch.cuda.synchronize()
+        import time
+        self._now = time.perf_counter
+        self.t = self._now()
+
+    def mark(self, name):
+        if self.sink is None:
+            return
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        now = self._now()
+        self.sink[name] = self.sink.get(name, 0.0) + (now - self.t)
+        self.t = now
+
+
+def _run_sequential(model, modifiers, batches, sequential_targets, phase_times=None):
+    clock = _PhaseClock(phase_times)
     layers = _sequential_layers(model, sequential_targets)
     first = layers[0][1]
     captured = []
@@ -110,20 +133,25 @@ def _run_sequential(model, modifiers, batches, sequential_targets):
             model.config.use_cache = use_cache
     for m in modifiers:
         m.on_calibration_start(model)
+    clock.mark("capture")
     for _name, layer in layers:
         with torch.no_grad():
             for args, kwargs in captured:  # calibration pass: hooks fire
                 layer(*args, **kwargs)
+        clock.mark("calibrate")
         members = list(layer.modules())
         for m in modifiers:
             m.on_sequential_epoch_end(model, members)
+        clock.mark("compress")
         nxt = []
         with torch.no_grad(), HooksMixin.disable_hooks():
-            for args, kwargs in captured:  # propagation pass with the quantised weights
+            for i, (args, kwargs) in enumerate(captured):  # propagation pass with the quantised weights
                 out = layer(*args, **kwargs)
                 hidden = out[0] if isinstance(out, (tuple, list)) else out
                 nxt.append(_with_hidden(args, kwargs, hidden))
+                captured[i] = None   # this block's input is not needed again
         captured = nxt
+        clock.mark("propagate")
     del captured
     # targeted modules outside the blocks (an lm_head that is not ignored, a head or adapter behind
     # the stack): one more pass over the whole model, whose blocks now carry their quantised
@@ -135,6 +163,7 @@ def _run_sequential(model, modifiers, batches, sequential_targets):
                 model(**b)
         for m in modifiers:
             m.on_sequential_epoch_end(model, rest)
+        clock.mark("remainder")
     for m in modifiers:
         m.on_calibration_end(model)
 
@@ -162,12 +191,15 @@ def _run_data_free(model, modifiers):
 def oneshot(model, recipe=None, dataset=None, num_calibration_samples: int = 512,
             max_seq_length: Optional[int] = None, batch_size: int = 1, pipeline: str = "independent",
             sequential_targets=None, moe_calibrate_all_experts: bool = True,
-            output_dir: Optional[str] = None, save_compressed: bool = True, **_ignored):
+            output_dir: Optional[str] = None, save_compressed: bool = True, phase_times: Optional[dict] = None,
+            **_ignored):
     """Apply the recipe's modifiers to ``model`` in one calibration pass and return it.
 
     ``recipe`` is a modifier or a list of modifiers (GPTQModifier / QuantizationModifier);
     ``dataset`` is a DataLoader, a list of ``{"input_ids": ...}`` dicts / id tensors, or a
-    [samples, length] tensor of token ids; it may be None for data-free recipes."""
+    [samples, length] tensor of token ids; it may be None for data-free recipes.  ``phase_times``
+    (a dict) asks for wall seconds per phase of the sequential driver (capture, calibrate, compress,
+    propagate), at the price of a device synchronisation at every phase boundary."""
     if isinstance(model, str):
         raise NotImplementedError("pass an instantiated model; loading checkpoints is outside this package")
     if recipe is None:
@@ -186,7 +218,7 @@ def oneshot(model, recipe=None, dataset=None, num_calibration_samples: int = 512
             batches = _as_batches(dataset, num_calibration_samples, max_seq_length, batch_size, device)
             if not batches:
                 raise ValueError(f"{type(m).__name__} needs calibration data but no dataset was given")
-            _run_sequential(model, [m], batches, sequential_targets)
+            _run_sequential(model, [m], batches, sequential_targets, phase_times)
         else:
             _run_data_free(model, [m])
     for m in modifiers:

@@ -59,7 +59,9 @@ def candidate_errors(weight, spec, maxshrink=0.20, grid=100.0, norm=2.4, expand=
 
 def reachable(E, dtype, n_terms, patience_stop=None):
     """Indices of the candidates the search may end on for ONE group: E [steps] exact sums."""
-    delta = n_terms * 2.0 ** -24
+    # error bound of a float32 sum of positive terms in any reasonable order (blocked / pairwise
+    # sums grow with the block length, not with the term count)
+    delta = min(n_terms, 256) * 2.0 ** -24
     options = []
     for e in E.tolist():
         near, other = _round_to(dtype, e, True)

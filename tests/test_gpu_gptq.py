@@ -128,7 +128,7 @@ def run_gptq(weight, args, hessian, blocksize, percdamp, observer_name=None):
 
 GPTQ_CASES = ["w4a16_g128", "w4a16_g32_bs64", "w4a16_g128_actorder_weight", "w4a16_g128_actorder_group",
               "w4a16_asym_g128", "w4_channel", "w4_tensor", "w8a16_channel", "fp8_channel", "nvfp4", "mxfp4",
-              "w4a16_g128_dead_cols", "w4a16_g128_not_pd", "w4a16_g128_fp32w"]
+              "w4a16_g128_dead_cols", "w4a16_g128_not_pd", "w4a16_g128_fp32w", "w4a16_g128_mse"]
 
 
 @pytest.mark.parametrize("name", GPTQ_CASES)
@@ -205,28 +205,44 @@ def test_end_to_end_hessian_then_gptq_then_pack():
 
 
 # ------------------------------------------------------------------------------- MSE observer
+def _check_mse_picks(weight, spec, mn, mx, mn_ref, mx_ref, kw, reference_is_exact=True):
+    """Every group bit-identical to the reference's pick, except groups where the reference's own
+    criterion is undecided: see mse_ties.  Returns (groups, differing groups)."""
+    import mse_ties
+    mn, mx = mn.cpu(), mx.cpu()
+    diff = (mn != mn_ref) | (mx != mx_ref)
+    if not bool(diff.any()):
+        return diff.numel(), 0
+    E, mns, mxs, n = mse_ties.candidate_errors(weight, spec, **{k: v for k, v in kw.items()
+                                                                 if k in ("maxshrink", "grid", "norm", "expand")})
+    for idx in diff.nonzero().tolist():
+        idx = tuple(idx)
+        picks = mse_ties.reachable(E[(slice(None),) + idx], weight.dtype, n)
+        ours = any(mns[(i,) + idx] == mn[idx] and mxs[(i,) + idx] == mx[idx] for i in picks)
+        theirs = any(mns[(i,) + idx] == mn_ref[idx] and mxs[(i,) + idx] == mx_ref[idx] for i in picks)
+        assert ours and (theirs or not reference_is_exact), (idx, sorted(picks))
+    return diff.numel(), int(diff.sum())
+
+
 def test_mse_golden(golden):
-    worst = 0.0
+    """The reference observer's own outputs: identical, bit for bit, in every golden case."""
     for name, c in golden["mse_cases"].items():
         args = args_from(c["args"])
         obs = observers.Observer.load_from_registry("memoryless_mse", base_name="weight", args=args)
         obs(c["weight"].to(DEV))
-        mm = max(mismatch(obs.min_vals, c["min"]), mismatch(obs.max_vals, c["max"]))
-        worst = max(worst, mm)
-        # a differing group must still be within the 1e-3 relative scale tolerance of the path
+        assert bits_equal(obs.min_vals, c["min"]) and bits_equal(obs.max_vals, c["max"]), name
         qp = obs.get_qparams()
-        s, s_ref = qp["scale"].float().cpu(), c["scale"].float()
-        rel = ((s - s_ref).abs() / s_ref.abs().clamp_min(1e-30))
-        assert float((rel > 1e-3).float().mean()) <= 0.02, (name, float(rel.max()))
-    assert worst <= 0.05, worst
+        assert bits_equal(qp["scale"], c["scale"]), name
 
 
 @pytest.mark.parametrize("bits,symmetric,g,kw", [(4, True, 128, {}), (4, False, 128, {}), (8, True, 128, {}),
                                                  (8, False, 32, {}), (4, True, 64, {"maxshrink": 0.6, "grid": 50.0}),
-                                                 (4, True, 128, {"maxshrink": 1.0, "grid": 100.0, "norm": 2.0})])
+                                                 (4, True, 128, {"maxshrink": 1.0, "grid": 100.0, "norm": 2.0}),
+                                                 (4, True, 128, {"maxshrink": 0.7, "grid": 100.0})])
 def test_mse_packed_kernel_vs_oracle(bits, symmetric, g, kw):
-    """bf16 weights with integer codes take the packed bf16x2 kernel; same tolerance as the golden cases
-    (the oracle sums the errors of a group in torch's order, the kernel lane by lane)."""
+    """bf16 weights with integer codes take the packed bf16x2 kernel.  Groups may differ from the
+    oracle only where a candidate's exact error sum lies within the float32 summation error of a
+    bf16 rounding midpoint (the oracle sums a group in torch's order, the kernel lane by lane)."""
     spec = oracle.QSpec(num_bits=bits, type="int", symmetric=symmetric, strategy="group", group_size=g)
     args = QuantizationArgs(num_bits=bits, type="int", symmetric=symmetric, strategy="group", group_size=g,
                             observer="memoryless_mse", observer_kwargs=kw)
@@ -234,8 +250,35 @@ def test_mse_packed_kernel_vs_oracle(bits, symmetric, g, kw):
     mn_ref, mx_ref = oracle.observe_mse(w, spec, **kw)
     obs = observers.Observer.load_from_registry("memoryless_mse", base_name="weight", args=args)
     obs(w.to(DEV))
-    mm = max(mismatch(obs.min_vals, mn_ref), mismatch(obs.max_vals, mx_ref))
-    assert mm <= 0.05, mm
+    groups, differing = _check_mse_picks(w, spec, obs.min_vals, obs.max_vals, mn_ref, mx_ref, kw)
+    assert differing <= 0.02 * groups, (differing, groups)   # undecided groups are rare
+
+
+@pytest.mark.parametrize("strategy,extra", [("tensor", {}), ("block", {"block_structure": [64, 128]}),
+                                            ("block", {"block_structure": [48, 80]}), ("channel", {})])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("bits,typ", [(8, "float"), (4, "int")])
+def test_mse_tensor_block_channel_vs_oracle(strategy, extra, dtype, bits, typ):
+    spec = oracle.QSpec(num_bits=bits, type=typ, symmetric=True, strategy=strategy, **extra)
+    args = QuantizationArgs(num_bits=bits, type=typ, symmetric=True, strategy=strategy, observer="memoryless_mse", **extra)
+    w = synth_weight(200, 384, seed=bits, dtype=dtype)
+    mn_ref, mx_ref = oracle.observe_mse(w, spec)
+    obs = observers.Observer.load_from_registry("memoryless_mse", base_name="weight", args=args)
+    obs(w.to(DEV))
+    assert obs.min_vals.shape == mn_ref.shape
+    # One group of 76 800 bf16 terms: torch's CPU reduction carries bf16 partial sums there and is off
+    # by 1e-4 relative, more than the bf16 rounding step that decides between these candidates, so
+    # the oracle's pick itself is not reproducible; the kernel must pick what the exact sums allow.
+    exact_ref = not (strategy == "tensor" and dtype == torch.bfloat16)
+    _check_mse_picks(w, spec, obs.min_vals, obs.max_vals, mn_ref, mx_ref, {}, reference_is_exact=exact_ref)
+
+
+def test_mse_candidate_count_follows_python_float_arithmetic():
+    """int(0.7 * 100) is 70 (the float32 product would give 69): one more candidate changes picks."""
+    from llm_compressor_b200 import _lib
+    lib = _lib.load()
+    for ms, grid in [(0.7, 100.0), (0.9, 100.0), (0.2, 100.0), (0.6, 50.0), (1.0, 100.0), (1 - 0.8 / 1.8, 200.0)]:
+        assert lib.b200q_observe_mse_steps(ms, grid) == int(ms * grid)
 
 
 # ------------------------------------------------------------------------------- tensor-core GEMM
@@ -373,3 +416,19 @@ def test_sweep_and_hessian_status_words_stay_zero():
     scale, zp = ops.qparams(mn, mx, a)
     losses, st2 = ops.gptq_sweep(W, H, scale, zp, a, return_status=True)
     assert int(st.item()) == 0 and int(st2.item()) == 0 and bool(torch.isfinite(losses).all())
+
+
+@pytest.mark.parametrize("N,K,block", [(256, 512, [128, 128]), (200, 640, [64, 128])])
+def test_gptq_block_strategy_vs_oracle(N, K, block):
+    """FP8 with one scale per block (the FP8_BLOCK preset's weight side), ragged last row block."""
+    spec = oracle.QSpec(num_bits=8, type="float", symmetric=True, strategy="block", block_structure=block)
+    args = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="block", block_structure=block)
+    w = synth_weight(N, K, seed=N + K)
+    x = synth_acts(8, 256, K, seed=5)
+    H, n = oracle.accumulate_hessian(x, oracle.make_empty_hessian(K), 0)
+    Hn = H / n
+    loss_ref, ref = oracle.quantize_weight(w, spec, Hn.clone())
+    loss, out = run_gptq(w, args, Hn, 128, 0.01)
+    assert bits_equal(out["weight_scale"], ref["weight_scale"])
+    assert mismatch(out["weight"], ref["weight"]) <= 1 - CODE_MATCH
+    assert loss == pytest.approx(loss_ref, rel=LOSS_RTOL)
