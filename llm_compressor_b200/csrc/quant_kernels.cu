@@ -911,12 +911,15 @@ static int rtn_impl(const void* W, int64_t N, int64_t K, int64_t ldw, const b200
         if (make_weight_tile_map(&wm, W, N, K, ldw)) {
           const int64_t tiles = N * (K / tma::kTileElems);
           const int gridt = (int)std::min<int64_t>((tiles + tma::kWarps - 1) / tma::kWarps, 2 * kNumSMs);
+          // test hook: B200Q_TEST_DROP_TILE=n makes one warp skip its n-th tile request (see the kernel)
+          const char* drop_env = getenv("B200Q_TEST_DROP_TILE");
+          const int drop_request = drop_env ? atoi(drop_env) : -1;
 #define B200Q_T3(MODE, GL, GG)                                                                                   \
   do {                                                                                                           \
     B200Q_TRY(cudaFuncSetAttribute(tma::rtn_group_tma_kernel<stream::MODE, GL, GG>,                              \
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, tma::kSmemBytes));               \
     tma::rtn_group_tma_kernel<stream::MODE, GL, GG><<<gridt, tma::kWarps * 32, tma::kSmemBytes, st>>>(           \
-        wm, (int)N, (int)K, qc, qr, gscale, scale_out, zp_out, scale_store, out);                                \
+        wm, (int)N, (int)K, qc, qr, gscale, scale_out, zp_out, scale_store, out, drop_request);                  \
   } while (0)
 #define B200Q_T2(MODE)                                     \
   do {                                                     \

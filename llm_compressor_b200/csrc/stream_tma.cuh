@@ -28,7 +28,7 @@ constexpr int kStages = 3;
 constexpr int kTileBytes = 4096;
 constexpr int kTileElems = 2048;
 constexpr int kSmemBytes = kWarps * kStages * kTileBytes + 1024 + kWarps * kStages * 8;
-constexpr long long kWaitCycles = 2000000000LL;
+constexpr long long kWaitCycles = 2000000000LL;   // about one second
 
 __device__ int g_wait_expired;   // set by any streaming kernel whose bounded wait ran out
 
@@ -67,7 +67,9 @@ template <int MODE, bool GLOBAL, int G>
 __global__ void __launch_bounds__(kWarps * 32, 2) rtn_group_tma_kernel(
     const __grid_constant__ CUtensorMap wmap, int N, int K, QParamCfg qc, QRange qr,
     const float* __restrict__ gscale, void* __restrict__ scale_out, void* __restrict__ zp_out,
-    uint8_t* __restrict__ scale_store, void* __restrict__ out) {
+    uint8_t* __restrict__ scale_store, void* __restrict__ out, int drop_request) {
+  // drop_request >= 0 (test hook, -1 in normal use): warp 0 of CTA 0 leaves out its drop_request-th
+  // tile request, so that its wait for that tile runs into the bound and the status path is exercised
   using namespace stream;
   using T = __nv_bfloat16;
   constexpr int CPG = G / 8;                         // chunks per group
@@ -93,11 +95,13 @@ __global__ void __launch_bounds__(kWarps * 32, 2) rtn_group_tma_kernel(
   const int64_t total = (int64_t)N * tpr;
   const int64_t stride = (int64_t)gridDim.x * kWarps;
   const int64_t first = (int64_t)blockIdx.x * kWarps + warp;
+  const bool victim = drop_request >= 0 && blockIdx.x == 0 && warp == 0;
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < kStages - 1; ++s) {
       const int64_t t = first + s * stride;
-      if (t < total) tile_request(tiles0 + s * kTileBytes, &wmap, bars0 + 8u * s, (int)(t % tpr), (int)(t / tpr));
+      if (t < total && !(victim && drop_request == s))
+        tile_request(tiles0 + s * kTileBytes, &wmap, bars0 + 8u * s, (int)(t % tpr), (int)(t / tpr));
     }
   }
   int it = 0;
@@ -113,7 +117,8 @@ __global__ void __launch_bounds__(kWarps * 32, 2) rtn_group_tma_kernel(
     if (lane == 0) {
       const int64_t tn = t + (kStages - 1) * stride;
       const int sn = (it + kStages - 1) % kStages;
-      if (tn < total) tile_request(tiles0 + sn * kTileBytes, &wmap, bars0 + 8u * sn, (int)(tn % tpr), (int)(tn / tpr));
+      if (tn < total && !(victim && drop_request == it + kStages - 1))
+        tile_request(tiles0 + sn * kTileBytes, &wmap, bars0 + 8u * sn, (int)(tn % tpr), (int)(tn / tpr));
     }
     const int row = (int)(t / tpr), tc = (int)(t - (int64_t)row * tpr);
     uint4 raw[8];

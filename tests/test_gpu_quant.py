@@ -308,3 +308,24 @@ def test_fused_nvfp4_whole_tile_rows(N, K):
     assert bits_equal(r["codes"], ref["weight_packed"])
     assert bits_equal(r["scale_store"], ref["weight_scale"])
     assert bits_equal(r["scale"], qp["scale"].to(w.dtype))
+
+
+def test_bounded_wait_that_runs_out_is_reported_and_nothing_hangs(monkeypatch):
+    """Failure made on the host: one warp of the TMA-fed kernel is told to leave out one of its tile
+    requests, so its wait for that tile runs into the bound (about a second).  The kernel must
+    return, the library must report B200Q_ERR_DEVICE once, and the next call must work."""
+    from llm_compressor_b200 import _lib
+    lib = _lib.load()
+    args = args_from(dict(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128))
+    w = synth_weight(4096, 4096, seed=1).to(DEV)     # several tiles per warp
+    good = ops.rtn_quantize_pack(w, args)
+    assert lib.b200q_take_wait_status() == 0
+    monkeypatch.setenv("B200Q_TEST_DROP_TILE", "1")
+    bad = ops.rtn_quantize_pack(w, args)
+    torch.cuda.synchronize()
+    monkeypatch.delenv("B200Q_TEST_DROP_TILE")
+    assert lib.b200q_take_wait_status() == _lib.C.c_int(-4).value      # B200Q_ERR_DEVICE, once
+    assert lib.b200q_take_wait_status() == 0
+    del bad                                                             # incomplete by construction
+    again = ops.rtn_quantize_pack(w, args)
+    assert torch.equal(again["codes"], good["codes"]) and lib.b200q_take_wait_status() == 0

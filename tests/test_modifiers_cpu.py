@@ -143,3 +143,37 @@ def test_reduce_and_broadcast_world2_gloo():
         assert w == 6.0 and s == 1.0  # values of rank 1 everywhere
     assert merged[0] == (3.0, 6.0)    # 1 + 2, samples 3 + 3
     assert merged[1] == (30.0, 6.0)   # 10 + 20
+
+
+def _failing_worker(rank, world, port, q):
+    """Rank 1 raises before the reduction (a host-made failure); rank 0 must get an error from the
+    collective within the process group's timeout instead of waiting forever."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.distributed.init_process_group("gloo", rank=rank, world_size=world,
+                                         timeout=datetime.timedelta(seconds=5))
+    t0 = time.time()
+    try:
+        if rank == 1:
+            raise RuntimeError("calibration failed on this rank")
+        groups = [_G(8, 1.0)]
+        bdist.reduce_hessians(groups, {groups[0]: 0})
+        q.put((rank, "completed", time.time() - t0))
+    except RuntimeError as e:
+        q.put((rank, "error: " + str(e)[:80], time.time() - t0))
+
+
+def test_rank_that_fails_before_the_reduction_does_not_hang_the_others():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + 7) % 1000
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = dict((r, (what, dt)) for r, what, dt in [q.get(timeout=120) for _ in procs])
+    for p in procs:
+        p.join(timeout=60)
+    assert out[1][0].startswith("error: calibration failed")
+    assert out[0][0].startswith("error"), out[0]      # the survivor's collective ended with an error ...
+    assert out[0][1] < 60, out[0]                      # ... within the short timeout, not the default 30 minutes
