@@ -678,6 +678,241 @@ def run_oneshot_arm(rank, world, dev, seqs, batch_size):
                                       "note": "docs/guides/big_models_and_distributed/distributed_oneshot.md:107-113, GPU not stated"}}
 
 
+# ======================================================================================
+# configs[3]: GPTQ FP8 (per-channel scales) of one Qwen3-30B-A3B-shaped MoE decoder layer
+# ======================================================================================
+def run_moe(args):
+    """One layer of the MoE configuration through GPTQModifier: hidden 2048, 32 / 4 heads of 128
+    (q 4096 x 2048, k / v 512 x 2048, o 2048 x 4096), 128 experts with gate / up 768 x 2048 and
+    down 2048 x 768, 256 x 2048 calibration tokens, all-expert calibration (every expert sees every
+    token, so all 256 gate / up projections share ONE Hessian and every down projection has its
+    own), FP8 E4M3 weights with per-channel scales, act-order "static".  Under torchrun the token
+    shards are reduced, the experts' Hessians go to owners and the shared one to every rank."""
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from llm_compressor_b200 import GPTQModifier, compressors
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    H_, QO, KV, E, MI, MOE_LAYERS = 2048, 4096, 512, args.experts, 768, 48
+    seqs = args.seqs if args.seqs != SEQS else 256
+    lo, hi = (seqs * rank) // world, (seqs * (rank + 1)) // world
+    tokens = (hi - lo) * SEQ_LEN
+    chunk = min(args.tokens_per_call, tokens)
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+
+    def acts(K):
+        x = torch.empty(tokens + 8 * E, K, dtype=torch.bfloat16, device=dev)
+        cs = 0.25 + 2.0 * torch.rand(K, generator=g, device=dev)
+        for t0 in range(0, x.shape[0], 65536):
+            t1 = min(x.shape[0], t0 + 65536)
+            x[t0:t1] = (torch.randn(t1 - t0, K, generator=g, device=dev) * cs).to(torch.bfloat16)
+        return x
+    X = {"hidden": acts(H_), "o_in": acts(QO), "down_in": acts(MI)}
+    gw = torch.Generator(device=dev).manual_seed(0)
+    layer = torch.nn.Module()
+    mods = []   # (name, module, input key, row offset into the input buffer)
+
+    def add(name, n_out, k_in, key, off=0):
+        lin = torch.nn.Linear(k_in, n_out, bias=False, device=dev, dtype=torch.bfloat16)
+        lin.weight.data = (torch.randn(n_out, k_in, generator=gw, device=dev) * 0.02).to(torch.bfloat16)
+        lin.requires_grad_(False)
+        setattr(layer, name, lin)
+        mods.append((name, lin, key, off))
+    add("q_proj", QO, H_, "hidden"); add("k_proj", KV, H_, "hidden"); add("v_proj", KV, H_, "hidden")
+    add("o_proj", H_, QO, "o_in")
+    for e in range(E):
+        # every expert's gate / up see the block input; each down projection has its own input
+        # (a window of the shared buffer shifted by 8 rows per expert: distinct tensors)
+        add(f"experts_{e}_gate_proj", MI, H_, "mlp", 8); add(f"experts_{e}_up_proj", MI, H_, "mlp", 8)
+        add(f"experts_{e}_down_proj", H_, MI, "down_in", 8 * e)
+    W0 = {name: lin.weight.data.clone() for name, lin, _, _ in mods}
+    mod = GPTQModifier(targets="Linear", scheme="FP8_DYNAMIC", actorder="static", block_size=128, dampening_frac=0.01,
+                       parallel_streams=args.solve_streams, hessian_stage_tokens=chunk)
+    mod.on_initialize(layer)
+    events = {}
+
+    def trace(ev, _m):
+        if ev in ("reduce", "solve", "broadcast", "done"):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            events[ev] = e
+    mod.trace = trace
+
+    def step():
+        for name, lin, _, _ in mods:
+            lin.weight.data.copy_(W0[name])
+        e0 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        mod.on_calibration_start(layer)
+        for t0 in range(0, tokens, chunk):
+            t1 = min(tokens, t0 + chunk)
+            views = {}
+            for name, lin, key, off in mods:
+                src = X["hidden"] if key == "mlp" else X[key]
+                vk = (key, off)
+                if vk not in views:
+                    views[vk] = src[off + t0: off + t1].view((t1 - t0) // SEQ_LEN, SEQ_LEN, src.shape[1])
+                mod.calibrate_module(lin, (views[vk],), None)
+        mod.on_sequential_epoch_end(layer, list(layer.modules()))
+        mod.on_calibration_end(layer)
+        if rank == 0:
+            for name, lin, _, _ in mods:
+                compressors.compress_state_dict({"weight": lin.weight.data, "weight_scale": lin.weight_scale.data,
+                                                 "weight_zero_point": lin.weight_zero_point.data},
+                                                lin.quantization_scheme)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e1.record()
+        return e0, e1
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    t_wall = time.perf_counter()
+    marks = [step() for _ in range(args.steps)]
+    barrier()
+    wall_ms = (time.perf_counter() - t_wall) * 1e3 / args.steps
+    ms = sum(a.elapsed_time(b) for a, b in marks) / args.steps
+    first = events.get("reduce", events["solve"])
+    phases = {"hessian_ms": marks[-1][0].elapsed_time(first),
+              "reduce_ms": events["reduce"].elapsed_time(events["solve"]) if "reduce" in events else 0.0,
+              "solve_ms": events["solve"].elapsed_time(events.get("broadcast", events["done"])),
+              "rest_ms": events.get("broadcast", events["done"]).elapsed_time(marks[-1][1])}
+    tms = torch.tensor([ms, wall_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    # parity of one expert's down projection (K = 768, its own Hessian) against the CPU oracle
+    parity = None
+    if rank == 0 and world == 1:
+        from llm_compressor_b200 import gptq
+        name, lin, key, off = next(m for m in mods if m[0] == "experts_3_down_proj")
+        Hh = torch.zeros(MI, MI, device=dev)
+        for t0 in range(0, tokens, chunk):
+            t1 = min(tokens, t0 + chunk)
+            gptq.accumulate_hessian_lower(X["down_in"][off + t0: off + t1].view(-1, SEQ_LEN, MI), Hh, 0)
+        gptq.finalize_hessian(Hh, seqs)
+        spec = oracle.preset("FP8_DYNAMIC", actorder="static")
+        loss_ref, ref = oracle.quantize_weight(W0[name].cpu(), spec, Hh.cpu())
+        match = float((lin.weight.data.cpu().view(torch.int16) == ref["weight"].view(torch.int16)).float().mean())
+        parity = {"module": name, "code_match": round(match, 6),
+                  "scale_equal": bool(torch.equal(lin.weight_scale.data.cpu().view(torch.int16).flatten(),
+                                                  ref["weight_scale"].view(torch.int16).flatten())),
+                  "loss_rel": round(abs(mod.losses[name] - loss_ref) / abs(loss_ref), 6)}
+        parity["ok"] = parity["code_match"] >= 0.995 and parity["scale_equal"] and parity["loss_rel"] <= 0.01
+    if rank == 0:
+        print(json.dumps({
+            "metric": "gptq_fp8_qwen3_30b_a3b_layer_ms", "value": float(tms[0]), "unit": "ms", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(tms[0]), "host_wall_ms_per_step": float(tms[1]),
+            "model_estimate_s": float(tms[1]) * MOE_LAYERS / 1e3, "higher_is_better": False, "scaling": "strong",
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[3]: GPTQ FP8 E4M3 per-channel, act-order static, one Qwen3-30B-A3B-shaped MoE layer "
+                                   "(%d experts, all-expert calibration), %d x %d calibration tokens" % (E, seqs, SEQ_LEN),
+                       "modules": len(mods), "distinct_hessians": 3 + E, "layers_in_model": MOE_LAYERS},
+            "phases": {k: round(v, 2) for k, v in phases.items()}, "parity_check": parity,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ======================================================================================
+# configs[4]: the Llama-3-70B widths (8192 / 28672), act-order and the 100-step MSE observer
+# ======================================================================================
+def run_70b(args):
+    """Kernel-level figures at the widths of the 70B configuration, one module of each kind on one
+    GPU (the model itself is layer-sharded over 8 GPUs, so one GPU never holds more than this):
+    Hessian update at K = 8192 and 28672, the factorisation at both widths, act-order "group" GPTQ of
+    a 1024-row slice of down_proj (8192 x 28672) with the 100-candidate MSE observer, and that
+    observer on the full 8192 x 28672 weight.  The factor is checked through its defining property
+    (U^T U H v = v on random probes, in float64 on the device)."""
+    import torch
+
+    from llm_compressor_b200 import gptq, observers, ops
+    from llm_compressor_b200.quant_args import QuantizationArgs
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(8, dtype=torch.uint8, device=dev)
+    timed = make_timed(flush)
+    g = torch.Generator(device=dev).manual_seed(0)
+    out = {"metric": "gptq_w4a16_llama3_70b_module_ms", "config": {"workload": "configs[4]: Llama-3-70B widths, W4A16 g128, "
+           "act-order group, memoryless_mse with 100 candidates (maxshrink 1.0, grid 100, norm 2.4)"}, "results": {}}
+    peaks = load_peaks()
+    T = 32768
+    for K in (8192, 28672):
+        x = torch.randn(T, K, generator=g, device=dev).to(torch.bfloat16)
+        H = torch.zeros(K, K, device=dev)
+        ms = timed(lambda: ops.hessian_syrk(x, H, 2.0), args.steps, do_flush=False)
+        out["results"][f"syrk_K{K}_T{T}"] = {"ms": round(ms, 3), "tflops": round(f_syrk(T, K) / ms / 1e9, 1),
+                                             "frac_of_burst_peak": round(f_syrk(T, K) / ms / 1e9 / 1661.0, 3)}
+        # a well conditioned Hessian from 4 such calls, then the factorisation
+        H.zero_()
+        for i in range(4):
+            x.copy_(torch.randn(T, K, generator=g, device=dev).to(torch.bfloat16))
+            ops.hessian_syrk(x, H, 2.0)
+        del x
+        ops.hessian_finalize(H, 1.0 / 64)
+        ops.gptq_prepare(H, None, 0.01)
+        U = H.clone()
+        st = ops.gptq_factor_async(U)
+        assert ops.gptq_factor_status(st) == 0
+        v = torch.randn(K, 2, generator=g, device=dev, dtype=torch.float64)
+        r = U.double().t() @ (U.double() @ (H.double() @ v)) - v
+        resid = float(r.norm() / v.norm())
+        Hw = torch.empty_like(H)
+
+        def fac():
+            Hw.copy_(H)
+            ops.gptq_factor(Hw)
+        ms = timed(fac, max(2, args.steps // 2), do_flush=False)
+        out["results"][f"factor_K{K}"] = {"ms": round(ms, 2), "workspace_gb": round(_lib_ws(K) / 2**30, 2),
+                                          "residual_UtUH_minus_I": resid, "ok": resid < 1e-3}
+        if K == 28672:
+            a = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128, actorder="group",
+                                 observer="memoryless_mse", observer_kwargs={"maxshrink": 1.0, "grid": 100.0, "norm": 2.4})
+            rows = 1024
+            lin = torch.nn.Linear(K, rows, bias=False, device=dev, dtype=torch.bfloat16)
+            lin.weight.data = (torch.randn(rows, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+
+            def solve():
+                lin.weight_observer = observers.Observer.load_from_registry("memoryless_mse", base_name="weight", args=a)
+                lin.weight_observer(lin.weight.data)
+                return gptq.quantize_weight(lin, a, H.clone(), blocksize=128, percdamp=0.0)
+            loss, res = solve()
+            ms = timed(lambda: solve(), 2, do_flush=False)
+            out["results"]["gptq_actorder_group_mse100_down_proj_1024rows"] = {
+                "ms": round(ms, 2), "loss": loss, "g_idx_is_permutation_of_groups": bool(
+                    torch.equal(torch.sort(res["weight_g_idx"]).values.cpu(), (torch.arange(K) // 128).to(torch.int32)))}
+            del lin
+            w = (torch.randn(8192, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            for cand, kw in ((20, {}), (100, {"maxshrink": 1.0, "grid": 100.0, "norm": 2.4})):
+                am = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128,
+                                      observer="memoryless_mse", observer_kwargs=kw)
+                ms = timed(lambda: ops.observe_mse(w, am, **kw), 3, do_flush=False)
+                out["results"][f"observe_mse_8192x28672_{cand}cand"] = {
+                    "ms": round(ms, 2), "g_element_steps_per_s": round(8192 * K * cand / ms / 1e6, 1)}
+            del w
+        del H, U, Hw
+        torch.cuda.empty_cache()
+    out["peaks"] = peaks
+    print(json.dumps(out))
+
+
+def _lib_ws(K):
+    from llm_compressor_b200 import _lib
+    return _lib.load().b200q_gptq_factor_workspace_bytes(K)
+
+
 def pack_micro(steps, peaks, timed, g, dev):
     """Quantize / pack kernels on a 16384 x 8192 bf16 matrix, and the NVFP4 / MXFP4 weight path on
     the two large Llama-3-8B matrices with 0.1 % outliers: GB/s of ALGORITHMIC bytes (the weight
@@ -835,15 +1070,39 @@ def run_micro(args):
         ms = timed(f, args.steps)
         out["results"].append({"kernel": "gptq_factor", "K": K, "ms": ms,
                                "tflops_fp32": (2.0 / 3.0) * K ** 3 / (ms * 1e-3) / 1e12})
+    if args.micro == "sweep":
+        # the column sweep of one module (N = 4096 rows) with its tensor-core trailing updates
+        K = args.micro_k
+        N = 4096
+        xx = torch.randn(2 * K, K, generator=g, device=dev)
+        U = (xx.t() @ xx) / K + 0.01 * torch.eye(K, device=dev)
+        del xx
+        assert ops.gptq_factor(U) == 0
+        a4 = QuantizationArgs(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128)
+        w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        mn, mx = ops.observe_minmax(w, a4)
+        scale, zp = ops.qparams(mn, mx, a4)
+        wf = torch.empty(N, K, device=dev)
+
+        def f():
+            wf.copy_(w)
+            ops.gptq_sweep(wf, U, scale, zp, a4)
+        ms = timed(f, args.steps)
+        out["results"].append({"kernel": "gptq_sweep", "N": N, "K": K, "ms": ms,
+                               "tflops_fp32": (float(N) * K * K + 128.0 * N * K) / (ms * 1e-3) / 1e12})
     print(json.dumps(out))
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["syrk", "pack", "factor", "mse", "all"],
+    ap.add_argument("--micro", default=None, choices=["syrk", "pack", "factor", "sweep", "mse", "all"],
                     help="kernel-level micro benchmark instead of the layer step")
     ap.add_argument("--micro-k", type=int, default=4096)
     ap.add_argument("--micro-t", type=int, default=32768)
+    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "moe", "70b"],
+                    help="llama8b: the headline layer step (configs[2]); moe: one Qwen3-30B-A3B-shaped layer "
+                         "(configs[3]); 70b: module-level figures at the Llama-3-70B widths (configs[4])")
+    ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
@@ -861,7 +1120,11 @@ def main():
     ap.add_argument("--oneshot-seqs", type=int, default=SEQS)
     ap.add_argument("--oneshot-batch", type=int, default=8, help="sequences per calibration batch of the oneshot run")
     args = ap.parse_args()
-    if args.micro:
+    if args.workload == "moe":
+        run_moe(args)
+    elif args.workload == "70b":
+        run_70b(args)
+    elif args.micro:
         run_micro(args)
     elif args.impl == "reference":
         run_reference(args)

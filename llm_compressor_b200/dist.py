@@ -57,7 +57,9 @@ def partition_samples(num_samples: int, r: int, world: int) -> range:
 
 def reduce_hessians(groups: Sequence, group_to_rank: dict) -> None:
     """Sum each group's partial Hessian and sample count onto its owner; other ranks drop
-    theirs.  ``groups`` have attributes ``H`` (float32 [K,K]) and ``n``."""
+    theirs.  A group whose ``group_to_rank`` entry is None is wanted by every rank (its member
+    modules are spread over all of them) and is all-reduced instead.  ``groups`` have attributes
+    ``H`` (float32 [K,K]) and ``n``."""
     me = rank()
     pending = []
     if not groups:
@@ -68,14 +70,17 @@ def reduce_hessians(groups: Sequence, group_to_rank: dict) -> None:
         H = g.H if g.H.device.type != "cpu" or dist.get_backend() == "gloo" else g.H.to(g.device)
         g.H = H
         dev = H.device
-        pending.append(dist.reduce(H, dst=dst, op=dist.ReduceOp.SUM, async_op=True))
+        if dst is None:
+            pending.append(dist.all_reduce(H, op=dist.ReduceOp.SUM, async_op=True))
+        else:
+            pending.append(dist.reduce(H, dst=dst, op=dist.ReduceOp.SUM, async_op=True))
     # every sample count in one collective and one read
     counts = torch.tensor([float(g.n) for g in groups], dtype=torch.float32, device=dev)
     pending.append(dist.all_reduce(counts, op=dist.ReduceOp.SUM, async_op=True))
     wait_for_comms(pending)
     totals = counts.tolist()
     for g, n in zip(groups, totals):
-        if group_to_rank[g] == me:
+        if group_to_rank[g] in (me, None):
             g.n = n
         else:
             g.H = None

@@ -444,15 +444,27 @@ class GPTQModifier(QuantizationMixin):
             self.compress_module_list(modules)
             self._trace("done")
             return
-        # owners by Hessian width over the distinct Hessians (base.py:306-318)
+        # owners by Hessian width over the distinct Hessians (base.py:306-318).  A Hessian shared by
+        # many modules (the gate / up projections of every expert under all-expert calibration)
+        # would make its owner sweep all of them alone: such a Hessian is summed onto every rank
+        # instead, every rank factors it, and its modules are dealt out round robin.
+        world = bdist.world_size()
         groups = list({id(self._groups[m]): self._groups[m] for m in modules}.values())
-        items, rank_to, to_rank = bdist.greedy_bin_packing(groups, bdist.world_size(),
-                                                           item_weight_fn=lambda g: g.H.shape[0])
+        members = {id(g): [m for m in modules if self._groups[m] is g] for g in groups}
+        spread = [g for g in groups if len(members[id(g)]) >= 2 * world]
+        owned = [g for g in groups if len(members[id(g)]) < 2 * world]
+        items, rank_to, to_rank = bdist.greedy_bin_packing(owned, world, item_weight_fn=lambda g: g.H.shape[0])
+        for g in spread:
+            to_rank[g] = None
+        items = items + spread
         for g in items:
             g.flush()   # staged calibration tokens
         self._trace("reduce")
         bdist.reduce_hessians(items, to_rank)
-        mod_rank = {m: to_rank[self._groups[m]] for m in modules}   # before the solve drops the groups
+        mod_rank = {}    # before the solve drops the groups
+        for g in items:
+            for i, m in enumerate(members[id(g)]):
+                mod_rank[m] = to_rank[g] if to_rank[g] is not None else i % world
         mine = [m for m in modules if mod_rank[m] == bdist.rank()]
         self._trace("solve")
         self.compress_module_list(mine)

@@ -109,7 +109,10 @@ def _worker(rank, world, port, q):
         groups = [_G(8, rank + 1), _G(16, 10 * (rank + 1))]
         items, bins, where = bdist.greedy_bin_packing(list(groups), world, item_weight_fn=lambda g: g.H.shape[0])
         order = {id(g): i for i, g in enumerate(groups)}
-        bdist.reduce_hessians(items, where)
+        everyone = _G(4, 100 * (rank + 1))      # a Hessian every rank wants (owner None): all-reduced
+        where[everyone] = None
+        bdist.reduce_hessians(items + [everyone], where)
+        assert float(everyone.H[0, 0]) == 300.0 and everyone.n == 6.0
         res = {}
         for g in groups:
             owner = where[g]
