@@ -41,11 +41,15 @@ GROUP_K = {"attn_in": HIDDEN, "o_in": HIDDEN, "mlp_in": HIDDEN, "down_in": INTER
 
 
 # DRAM traffic of one rank-k update launch (dram__bytes_read.sum + dram__bytes_write.sum of ncu
-# captures of 32768-token launches); a step runs 96 launches of width 4096 and 32 of width 14336.
+# captures): 620 MB at K = 4096 (32768 tokens); 6.7 GB at K = 14336 with 16384 tokens, i.e. about
+# 12.6 GB with the 32768 tokens a launch of the layer step holds (the re-read X panels scale with the
+# tokens, the 0.8 GB of H does not).  A step runs 96 launches of width 4096 and 32 of width 14336.
 SYRK_TRAFFIC = {
-    "K4096": 620.0e6, "K14336": None,
-    "per_launch_weighted": 620.0e6,
-    "note": "bytes per K=4096 launch of 32768 tokens, from the ncu capture; algorithmic 2TK + 4K(K+1) = 336e6",
+    "K4096": 0.62e9, "K14336": 12.6e9,
+    "per_launch_weighted": (96 * 0.62e9 + 32 * 12.6e9) / 128,
+    "note": "mean bytes per launch over a step's 96 K=4096 launches (0.62e9 each, algorithmic 0.34e9) and 32 "
+            "K=14336 launches (12.6e9 each, scaled from a 16384-token capture; algorithmic 1.76e9): X panels are "
+            "re-read by every band of 8 block rows; DRAM stays at 19-32 % of its peak, the kernel is tensor bound",
 }
 
 
