@@ -69,6 +69,23 @@ def validate_scheme(scheme) -> QuantizationScheme:
     return scheme
 
 
+def _group_scheme(g) -> QuantizationScheme:
+    """One entry of a config's ``config_groups``: a scheme object, a dict in the scheme's field
+    names, or a preset name with targets (``{"scheme": "W4A16", "targets": [...]}``)."""
+    from .quant_args import QuantizationArgs
+    if isinstance(g, QuantizationScheme):
+        return validate_scheme(g)
+    if isinstance(g, dict) and "scheme" in g:
+        s = validate_scheme(g["scheme"])
+        s.targets = list(g.get("targets") or s.targets)
+        return s
+    get = g.get if isinstance(g, dict) else (lambda k, d=None: getattr(g, k, d))
+    w, a = get("weights"), get("input_activations")
+    return validate_scheme(QuantizationScheme(targets=list(get("targets") or []),
+                                              weights=None if w is None else QuantizationArgs.of(w),
+                                              input_activations=None if a is None else QuantizationArgs.of(a)))
+
+
 def split_fused_moe_experts(tensors: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
     """3-D ``...gate_up_proj`` [E, 2I, H] and ``...down_proj`` [E, H, I] tensors become 2-D
     ``...{e}.gate_proj.weight`` / ``{e}.up_proj.weight`` / ``{e}.down_proj.weight`` views
@@ -136,9 +153,10 @@ def _is_weight_candidate(name: str, t: torch.Tensor) -> bool:
     return not name[: -len(".weight")].endswith("norm")   # norms are ignored automatically
 
 
-def process_shard(tensors: Dict[str, torch.Tensor], scheme: QuantizationScheme, ignore: Iterable[str],
+def process_shard(tensors: Dict[str, torch.Tensor], scheme, ignore: Iterable[str],
                   own: Optional[set] = None, run: Optional[Callable] = None):
     """Quantise and compress the selected weights among ``tensors`` (already on the device).
+    ``scheme``: one QuantizationScheme or ``{group name: QuantizationScheme}``.
     ``own``: names to keep in the result (default all); the others were only loaded as fused
     partners.  Returns ``(state_dict on cpu, quantization_config or None)``.
 
@@ -148,8 +166,9 @@ def process_shard(tensors: Dict[str, torch.Tensor], scheme: QuantizationScheme, 
     tensors = split_fused_moe_experts(tensors)
     weights = {n: t for n, t in tensors.items() if _is_weight_candidate(n, t)}
     model = build_module_tree(weights)
-    modifier = QuantizationModifier(targets=list(scheme.targets), ignore=list(ignore),
-                                    config_groups={"group_0": scheme})
+    groups = dict(scheme) if isinstance(scheme, dict) else {"group_0": scheme}
+    targets = sorted({t for g in groups.values() for t in g.targets})
+    modifier = QuantizationModifier(targets=targets, ignore=list(ignore), config_groups=groups)
     modifier.on_initialize(model)
     (run or (lambda m, mod: _run_data_free(m, [mod])))(model, modifier)
     modifier.on_finalize(model)
@@ -189,21 +208,29 @@ def model_free_ptq(model_stub, save_directory, scheme=None, config=None, ignore:
                    max_workers: int = 1, device=None, converter=None):
     """Quantise the safetensors checkpoint in directory ``model_stub`` into ``save_directory``.
 
-    ``scheme``: preset name or QuantizationScheme (``config`` with several groups is not
-    supported here); ``ignore``: module names / ``re:`` patterns left alone (names ending in
-    "norm" always are); ``device``: one device or a list (default: every visible GPU)."""
+    ``scheme``: preset name or QuantizationScheme, or ``config``: several schemes at once, given as
+    ``{"config_groups": {name: scheme or preset name with "targets"}, "ignore": [...]}`` or an
+    object with those attributes (a compressed-tensors ``QuantizationConfig``); the first group
+    whose targets select a module applies to it.  ``ignore``: module names / ``re:`` patterns left
+    alone (names ending in "norm" always are); ``device``: one device or a list (default: every
+    visible GPU).  Checkpoint converters are not supported."""
     from safetensors import safe_open
     from safetensors.torch import load_file, save_file
 
-    if config is not None:
-        raise NotImplementedError("pass `scheme`; multi-group configs are outside this package's path")
     if converter is not None:
         raise NotImplementedError("checkpoint converters are outside this package's path")
-    if scheme is None:
+    if (scheme is None) == (config is None):
         raise ValueError("Please specify either `config` or `scheme`")
     if not os.path.isdir(model_stub):
         raise ValueError(f"{model_stub} is not a directory (hub downloads are not available)")
-    scheme = validate_scheme(scheme)
+    if config is not None:
+        get = config.get if isinstance(config, dict) else (lambda k, d=None: getattr(config, k, d))
+        scheme = {name: _group_scheme(g) for name, g in dict(get("config_groups") or {}).items()}
+        if not scheme:
+            raise ValueError("`config` holds no config_groups")
+        ignore = list(ignore) + [i for i in (get("ignore") or []) if i not in ignore]
+    else:
+        scheme = validate_scheme(scheme)
     if device is None:
         n = torch.cuda.device_count()
         if n == 0:
@@ -222,7 +249,8 @@ def model_free_ptq(model_stub, save_directory, scheme=None, config=None, ignore:
 
     # fused sets that straddle shards: every owner's job also reads the partners
     partners = defaultdict(dict)   # shard -> {name: source shard}
-    if scheme.weights.strategy == "tensor_group":
+    all_schemes = list(scheme.values()) if isinstance(scheme, dict) else [scheme]
+    if any(sc.weights.strategy == "tensor_group" for sc in all_schemes):
         for members in fused_sets(wmap.keys()):
             for m in members:
                 for other in members:
@@ -260,7 +288,8 @@ def model_free_ptq(model_stub, save_directory, scheme=None, config=None, ignore:
         if os.path.exists(cfg_path):
             with open(cfg_path) as f:
                 cfg = json.load(f)
-        cfg["quantization_config"] = qconfig
+        from .oneshot import _ct_version
+        cfg["quantization_config"] = {"version": _ct_version(), **qconfig}
         with open(cfg_path, "w") as f:
             json.dump(cfg, f, indent=2, default=str)
     if len(shards) > 1 or os.path.exists(os.path.join(model_stub, INDEX_NAME)):

@@ -208,6 +208,18 @@ class QuantizationMixin(HooksMixin):
                 reg("weight_zero_point", torch.zeros(shape, dtype=w.zp_dtype, device=dev))
                 if w.actorder == "group":
                     reg("weight_g_idx", torch.full((K,), -1, dtype=torch.int32, device=dev))
+                a = scheme.input_activations
+                if a is not None and a.dynamic is not True:
+                    # statically calibrated input activations (CT lifecycle/initialize.py:164-254):
+                    # a per-tensor scale / zero point, or (dynamic "local") only the global scale
+                    if a.strategy == "tensor_group":
+                        reg("input_global_scale", torch.empty(1, dtype=torch.float32, device=dev))
+                    if a.dynamic is False:
+                        if a.strategy != "tensor":
+                            raise NotImplementedError("static input activations are supported per tensor")
+                        reg("input_scale", torch.empty(1, dtype=dt if dt.is_floating_point else torch.float16,
+                                                       device=dev))
+                        reg("input_zero_point", torch.zeros(1, dtype=a.zp_dtype, device=dev))
         if bad:
             lines = "\n".join(f"  {n}: columns {k} not divisible by group_size {g}" for n, k, g in bad)
             raise ValueError(
@@ -224,13 +236,46 @@ class QuantizationMixin(HooksMixin):
             w = module.quantization_scheme.weights
             module.weight_observer = Observer.load_from_registry(
                 w.observer or "memoryless_minmax", base_name="weight", args=w)
+            a = module.quantization_scheme.input_activations
+            if a is not None and a.dynamic is not True:
+                name = a.observer if a.observer not in (None, "memoryless_minmax") else "minmax"
+                module.input_observer = Observer.load_from_registry(name, base_name="input", args=a)
+                self.register_hook(module, _calibrate_input_hook, "forward_pre")
         fuse_weight_observers(model)
+
+    @property
+    def calibrates_activations(self) -> bool:
+        """True when some resolved scheme has statically calibrated input activations."""
+        groups = self._resolved if self._resolved is not None else self.resolve_quantization_config()
+        return any(s.input_activations is not None and s.input_activations.dynamic is not True
+                   for s in groups.values())
+
+    def update_activation_qparams(self, modules) -> None:
+        """Epoch end for activation observers: combine the ranks' statistics, then write
+        ``input_scale`` / ``input_zero_point`` / ``input_global_scale``
+        (quantization/base.py:83-108, calibration.py:109-162)."""
+        mods = [m for m in modules if getattr(m, "input_observer", None) is not None
+                and m.input_observer.has_statistics]
+        if not mods:
+            return
+        if bdist.is_distributed():
+            pending = []
+            for m in mods:
+                pending.extend(m.input_observer.sync_activation_stats())
+            bdist.wait_for_comms(pending)
+        update_qparams(mods, "input")
 
     def end_calibration(self, model: torch.nn.Module) -> None:
         self.remove_hooks()
         for _, module in self.quantized_modules(model):
-            if hasattr(module, "weight_observer"):
-                del module.weight_observer
+            for name in ("weight_observer", "input_observer"):
+                if hasattr(module, name):
+                    delattr(module, name)
+
+
+def _calibrate_input_hook(module, args):
+    """calibration.py:165-170: the input observer sees every calibration batch."""
+    module.input_observer(args[0] if isinstance(args, tuple) else args)
 
 
 def observe(modules: Iterable[torch.nn.Module], base_name: str = "weight") -> None:
@@ -251,9 +296,10 @@ def update_qparams(modules: Iterable[torch.nn.Module], base_name: str = "weight"
             warnings.warn(f"Observer of {type(m).__name__} has no statistics; qparams not updated")
             continue
         qp = obs.get_qparams()
-        getattr(m, f"{base_name}_scale").data.copy_(qp["scale"].reshape(getattr(m, f"{base_name}_scale").shape))
-        getattr(m, f"{base_name}_zero_point").data.copy_(qp["zero_point"].reshape(
-            getattr(m, f"{base_name}_zero_point").shape))
+        if hasattr(m, f"{base_name}_scale"):    # absent for locally dynamic activations (global scale only)
+            getattr(m, f"{base_name}_scale").data.copy_(qp["scale"].reshape(getattr(m, f"{base_name}_scale").shape))
+            getattr(m, f"{base_name}_zero_point").data.copy_(qp["zero_point"].reshape(
+                getattr(m, f"{base_name}_zero_point").shape))
         if qp["global_scale"] is not None and hasattr(m, f"{base_name}_global_scale"):
             getattr(m, f"{base_name}_global_scale").data.copy_(qp["global_scale"])
         if base_name == "weight":
@@ -265,7 +311,9 @@ class QuantizationModifier(QuantizationMixin):
     """Round-to-nearest weight quantisation: observe weights, write qparams; the weight is
     left as is until it is packed at save time (quantization/base.py:24-110)."""
 
-    requires_calibration_data = False
+    @property
+    def requires_calibration_data(self) -> bool:
+        return self.calibrates_activations
 
     def on_initialize(self, model, **_):
         self.initialize_quantization(model)
@@ -275,7 +323,9 @@ class QuantizationModifier(QuantizationMixin):
         self.start_calibration(model)
 
     def on_sequential_epoch_end(self, model, modules: Iterable[torch.nn.Module], **_):
-        modules = [m for m in modules if hasattr(m, "weight_observer")]
+        modules = [m for m in modules if hasattr(m, "weight_observer")
+                   and getattr(m, "quantization_status", None) != "frozen"]
+        self.update_activation_qparams(modules)
         if bdist.is_distributed():
             # owners by weight size; each rank observes its share, scales are broadcast
             items, rank_to, to_rank = bdist.greedy_bin_packing(
@@ -290,6 +340,12 @@ class QuantizationModifier(QuantizationMixin):
         else:
             observe(modules)
             update_qparams(modules)
+
+    def pending_modules(self):
+        """Targeted modules whose parameters have not been written yet (modules behind the
+        sequential blocks)."""
+        return [m for m in self._module_names if hasattr(m, "weight_observer")
+                and getattr(m, "quantization_status", None) != "frozen"]
 
     def on_calibration_end(self, model, **_):
         self.end_calibration(model)
@@ -430,6 +486,7 @@ class GPTQModifier(QuantizationMixin):
 
     def on_sequential_epoch_end(self, model, modules: Iterable[torch.nn.Module], **_):
         mods = [m for m in modules if m in self._num_samples]
+        self.update_activation_qparams(mods)
         observe(mods, "weight")
         self.compress_modules(mods)
 

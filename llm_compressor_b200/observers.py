@@ -15,8 +15,8 @@ import torch
 from . import ops
 from .quant_args import QuantizationArgs
 
-__all__ = ["Observer", "MemorylessMinMaxObserver", "MemorylessMSEObserver",
-           "NVFP4ExpandedMSEObserver", "fuse_weight_observers", "FUSED_LAYER_NAMES"]
+__all__ = ["Observer", "MemorylessMinMaxObserver", "MemorylessMSEObserver", "NVFP4ExpandedMSEObserver",
+           "StaticMinMaxObserver", "MinMaxObserver", "fuse_weight_observers", "FUSED_LAYER_NAMES"]
 
 _REGISTRY: dict = {}
 
@@ -28,6 +28,10 @@ _WEIGHT_ALIASES = {"minmax": "memoryless_minmax", "static_minmax": "memoryless_m
 
 class Observer:
     """Base class: statistics -> qparams."""
+
+    # statistic attribute -> how ranks combine it when activation statistics are synchronised
+    # ("min" / "max" / "avg"; src/llmcompressor/observers/base.py:147-162)
+    _act_sync_dict: dict = {}
 
     def __init__(self, base_name: str, args, **observer_kwargs):
         self.base_name = base_name
@@ -71,15 +75,38 @@ class Observer:
     def update_statistics_from_weight(self, weight: torch.Tensor) -> None:
         raise NotImplementedError
 
+    def update_statistics_from_activation(self, value: torch.Tensor) -> None:
+        raise NotImplementedError(f"{type(self).__name__} observes weights only")
+
     @torch.no_grad()
     def __call__(self, observed: torch.Tensor) -> "Observer":
         if observed.numel() == 0:
             return self
-        if self.is_weight_obs and self.has_statistics:
+        if not self.is_weight_obs:
+            self.update_statistics_from_activation(observed)
+            return self
+        if self.has_statistics:
             return self
         self.update_statistics_from_weight(observed)
         self._observe_partners()
         return self
+
+    def sync_activation_stats(self) -> list:
+        """All-reduce the accumulated activation statistics across ranks (weights are identical on
+        every rank, only the calibration data differs).  Returns async work handles."""
+        import torch.distributed as dist
+        work = []
+        for attr, how in self._act_sync_dict.items():
+            val = getattr(self, attr, None)
+            if val is None:
+                continue
+            if how == "avg":   # (gloo has no AVG)
+                val.div_(dist.get_world_size())
+                work.append(dist.all_reduce(val, op=dist.ReduceOp.SUM, async_op=True))
+            else:
+                op = dist.ReduceOp.MIN if how == "min" else dist.ReduceOp.MAX
+                work.append(dist.all_reduce(val, op=op, async_op=True))
+        return work
 
     forward = __call__
 
@@ -152,6 +179,57 @@ class MemorylessMSEObserver(Observer):
 @Observer.register("nvfp4_expanded_mse")
 class NVFP4ExpandedMSEObserver(MemorylessMSEObserver):
     _defaults = dict(maxshrink=1 - 0.8 / 1.8, patience=1000, grid=200.0, norm=2.4, expand=1.8)
+
+
+def _activation_minmax(value: torch.Tensor, args: QuantizationArgs):
+    """Statistics of an activation [..., hidden] for a static scheme: one (min, max) over
+    everything (TENSOR, and TENSOR_GROUP whose only calibrated quantity is the global scale)."""
+    if args.strategy not in ("tensor", "tensor_group"):
+        raise NotImplementedError(f"static activation quantisation with strategy {args.strategy}")
+    x = value.reshape(-1, value.shape[-1])
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        x = x.to(torch.float32)
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    targs = QuantizationArgs(num_bits=args.num_bits, type=args.type, symmetric=args.symmetric, strategy="tensor")
+    return ops.observe_minmax(x, targs)
+
+
+@Observer.register("static_minmax")
+class StaticMinMaxObserver(Observer):
+    """Min / max over every batch seen (src/llmcompressor/observers/min_max.py:22-40).  Weight
+    observers of this name are memoryless (see ``load_from_registry``)."""
+    _act_sync_dict = {"min_vals": "min", "max_vals": "max"}
+
+    def update_statistics_from_weight(self, weight):
+        self.min_vals, self.max_vals = ops.observe_minmax(weight, self.args)
+
+    def update_statistics_from_activation(self, value):
+        mn, mx = _activation_minmax(value, self.args)
+        if self.has_statistics:
+            mn, mx = torch.minimum(mn, self.min_vals), torch.maximum(mx, self.max_vals)
+        self.min_vals, self.max_vals = mn, mx
+
+
+@Observer.register("minmax")
+class MinMaxObserver(Observer):
+    """Moving average of the per-batch min / max with ``averaging_constant`` (default 0.01;
+    min_max.py:43-67)."""
+    _act_sync_dict = {"min_vals": "avg", "max_vals": "avg"}
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.avg_constant = self.args.observer_kwargs.get("averaging_constant", 0.01)
+
+    def update_statistics_from_weight(self, weight):
+        self.min_vals, self.max_vals = ops.observe_minmax(weight, self.args)
+
+    def update_statistics_from_activation(self, value):
+        mn, mx = _activation_minmax(value, self.args)
+        if self.has_statistics and self.avg_constant != 1.0:
+            mn = torch.lerp(self.min_vals, mn, self.avg_constant)
+            mx = torch.lerp(self.max_vals, mx, self.avg_constant)
+        self.min_vals, self.max_vals = mn, mx
 
 
 # layer names whose NVFP4 global scale is shared (helpers.py:162-171)

@@ -69,7 +69,7 @@ class QuantizationArgs:
         if self.actorder is not None and self.strategy not in ("group", "tensor_group"):
             raise ValueError("Must use group or tensor_group quantization strategy in order to "
                              "apply activation ordering")
-        if self.observer is None and not self.dynamic:
+        if self.observer is None and self.dynamic is not True:
             self.observer = "memoryless_minmax"
         if self.zp_dtype is None:
             if self.type == "float":
@@ -148,31 +148,46 @@ def _w(**kw):
     return dict(kw)
 
 
-# weight side of the presets; `act` marks presets that also quantise input activations
-# (that half is outside this package; it only affects the inferred checkpoint format)
+# weight side of the presets and, where a preset also quantises input activations, that side:
+# "dynamic" ones (per token / per group at run time) need no calibration and only decide the
+# checkpoint format; FP8 calibrates a static per-tensor scale, NVFP4 a static global scale
+# (CT/quantization/quant_scheme.py:145-428)
+def _act(**kw):
+    return dict(kw)
+
+
+_TOKEN8 = _act(num_bits=8, type="int", symmetric=True, strategy="token", dynamic=True)
 PRESET_SCHEMES = {
-    "W4A16": (_w(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128), False),
-    "W4A16_ASYM": (_w(num_bits=4, type="int", symmetric=False, strategy="group", group_size=128), False),
-    "W8A16": (_w(num_bits=8, type="int", symmetric=True, strategy="channel"), False),
-    "W8A8": (_w(num_bits=8, type="int", symmetric=True, strategy="channel"), True),
-    "INT8": (_w(num_bits=8, type="int", symmetric=True, strategy="channel"), True),
-    "W4A8": (_w(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128), True),
-    "FP8": (_w(num_bits=8, type="float", symmetric=True, strategy="tensor"), True),
-    "FP8_DYNAMIC": (_w(num_bits=8, type="float", symmetric=True, strategy="channel"), True),
-    "FP8_BLOCK": (_w(num_bits=8, type="float", symmetric=True, strategy="block",
-                     block_structure=[128, 128]), True),
+    "W4A16": (_w(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128), None),
+    "W4A16_ASYM": (_w(num_bits=4, type="int", symmetric=False, strategy="group", group_size=128), None),
+    "W8A16": (_w(num_bits=8, type="int", symmetric=True, strategy="channel"), None),
+    "W8A8": (_w(num_bits=8, type="int", symmetric=True, strategy="channel"), _TOKEN8),
+    "INT8": (_w(num_bits=8, type="int", symmetric=True, strategy="channel"), _TOKEN8),
+    "W4A8": (_w(num_bits=4, type="int", symmetric=True, strategy="group", group_size=128), _TOKEN8),
+    "FP8": (_w(num_bits=8, type="float", symmetric=True, strategy="tensor"),
+            _act(num_bits=8, type="float", symmetric=True, strategy="tensor", dynamic=False, observer="minmax")),
+    "FP8_DYNAMIC": (_w(num_bits=8, type="float", symmetric=True, strategy="channel"),
+                    _act(num_bits=8, type="float", symmetric=True, strategy="token", dynamic=True)),
+    "FP8_BLOCK": (_w(num_bits=8, type="float", symmetric=True, strategy="block", block_structure=[128, 128]),
+                  _act(num_bits=8, type="float", symmetric=True, strategy="group", group_size=128, dynamic=True)),
     "NVFP4A16": (_w(num_bits=4, type="float", symmetric=True, strategy="tensor_group", group_size=16,
-                    scale_dtype=torch.float8_e4m3fn, zp_dtype=torch.float8_e4m3fn), False),
+                    scale_dtype=torch.float8_e4m3fn, zp_dtype=torch.float8_e4m3fn), None),
     "NVFP4": (_w(num_bits=4, type="float", symmetric=True, strategy="tensor_group", group_size=16,
-                 scale_dtype=torch.float8_e4m3fn, zp_dtype=torch.float8_e4m3fn), True),
+                 scale_dtype=torch.float8_e4m3fn, zp_dtype=torch.float8_e4m3fn),
+              _act(num_bits=4, type="float", symmetric=True, strategy="tensor_group", group_size=16, dynamic="local",
+                   observer="static_minmax", scale_dtype=torch.float8_e4m3fn, zp_dtype=torch.float8_e4m3fn)),
     "MXFP4A16": (_w(num_bits=4, type="float", symmetric=True, strategy="group", group_size=32,
-                    scale_dtype=torch.uint8, zp_dtype=torch.uint8), False),
+                    scale_dtype=torch.uint8, zp_dtype=torch.uint8), None),
     "MXFP4": (_w(num_bits=4, type="float", symmetric=True, strategy="group", group_size=32,
-                 scale_dtype=torch.uint8, zp_dtype=torch.uint8), True),
+                 scale_dtype=torch.uint8, zp_dtype=torch.uint8),
+              _act(num_bits=4, type="float", symmetric=True, strategy="group", group_size=32, dynamic=True,
+                   scale_dtype=torch.uint8, zp_dtype=torch.uint8)),
     "MXFP8A16": (_w(num_bits=8, type="float", symmetric=True, strategy="group", group_size=32,
-                    scale_dtype=torch.uint8, zp_dtype=torch.uint8), False),
+                    scale_dtype=torch.uint8, zp_dtype=torch.uint8), None),
     "MXFP8": (_w(num_bits=8, type="float", symmetric=True, strategy="group", group_size=32,
-                 scale_dtype=torch.uint8, zp_dtype=torch.uint8), True),
+                 scale_dtype=torch.uint8, zp_dtype=torch.uint8),
+              _act(num_bits=8, type="float", symmetric=True, strategy="group", group_size=32, dynamic=True,
+                   scale_dtype=torch.uint8, zp_dtype=torch.uint8)),
 }
 
 
@@ -183,8 +198,6 @@ def preset_name_to_scheme(name: str, targets: list) -> QuantizationScheme:
         raise KeyError(f"Unknown preset scheme name {name}, available names: {list(PRESET_SCHEMES)}")
     w, act = PRESET_SCHEMES[key]
     scheme = QuantizationScheme(targets=list(targets), weights=QuantizationArgs(**w))
-    if act:
-        # marker only: activation quantisation is applied by the serving stack
-        scheme.input_activations = QuantizationArgs(num_bits=w["num_bits"], type=w["type"],
-                                                    dynamic=True, strategy="tensor")
+    if act is not None:
+        scheme.input_activations = QuantizationArgs(**act)
     return scheme

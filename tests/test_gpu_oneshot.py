@@ -347,3 +347,54 @@ def test_targeted_module_behind_the_blocks_is_calibrated_and_unreached_ones_are_
     with pytest.raises(ValueError, match="never received calibration data"):
         oneshot(broken, recipe=GPTQModifier(targets="Linear", scheme="W8A16", ignore=["lm_head"], actorder=None),
                 dataset=data)
+
+
+def _capture_inputs(model, data, names):
+    """{module name: [input of every calibration batch]} from a plain forward of the model."""
+    got = {n: [] for n in names}
+    mods = dict(model.named_modules())
+    hooks = [mods[n].register_forward_pre_hook(lambda m, a, n=n: got[n].append(a[0].detach().float().cpu()))
+             for n in names]
+    with torch.no_grad():
+        for row in data:
+            model(input_ids=row[None].to(DEV))
+    for h in hooks:
+        h.remove()
+    return got
+
+
+def test_static_input_activation_scales_fp8_and_nvfp4(tmp_path):
+    """Schemes that calibrate input activations: FP8 (static per-tensor scale from the moving
+    average of the batches' min / max) and NVFP4 (global scale from the min / max over all batches)."""
+    base = tiny_llama(seed=11)
+    data = calib(6, 48)
+    names = ["model.layers.0.self_attn.q_proj", "model.layers.0.mlp.down_proj", "model.layers.1.self_attn.o_proj"]
+    acts = _capture_inputs(base, data, names)     # round-to-nearest leaves the weights as they are
+
+    model = oneshot(copy.deepcopy(base), recipe=QuantizationModifier(targets="Linear", scheme="FP8", ignore=["lm_head"]),
+                    dataset=data, output_dir=str(tmp_path / "fp8"))
+    for n in names:
+        m = dict(model.named_modules())[n]
+        mn = mx = None
+        for x in acts[n]:
+            lo, hi = x.min().to(torch.bfloat16), x.max().to(torch.bfloat16)
+            mn, mx = (lo, hi) if mn is None else (torch.lerp(mn, lo, 0.01), torch.lerp(mx, hi, 0.01))
+        spec = oracle.QSpec(num_bits=8, type="float", symmetric=True, strategy="tensor")
+        scale, _zp = oracle.calculate_qparams(mn.reshape(1), mx.reshape(1), spec)
+        got = m.input_scale.data.float().cpu()
+        assert abs(float(got) - float(scale)) <= 2.0 ** -7 * float(scale), (n, float(got), float(scale))
+        assert not hasattr(m, "input_observer")
+    from safetensors.torch import load_file
+    sd = load_file(str(tmp_path / "fp8" / "model.safetensors"))
+    assert "model.layers.0.self_attn.q_proj.input_scale" in sd
+    assert sd["model.layers.0.self_attn.q_proj.weight"].dtype == torch.float8_e4m3fn
+
+    model = oneshot(copy.deepcopy(base), recipe=QuantizationModifier(targets="Linear", scheme="NVFP4", ignore=["lm_head"]),
+                    dataset=data)
+    for n in names:
+        m = dict(model.named_modules())[n]
+        lo = min(float(x.min().to(torch.bfloat16)) for x in acts[n])
+        hi = max(float(x.max().to(torch.bfloat16)) for x in acts[n])
+        ref = oracle.generate_gparam(torch.tensor([lo], dtype=torch.bfloat16), torch.tensor([hi], dtype=torch.bfloat16))
+        assert torch.equal(m.input_global_scale.data.cpu(), ref), n
+        assert not hasattr(m, "input_scale")

@@ -147,3 +147,45 @@ def test_model_free_moe_experts(tmp_path):
     assert got["mlp.experts.0.down_proj.weight_scale"].shape == (128, 1)
     assert torch.equal(got["mlp.gate.weight"], t["mlp.gate.weight"])
     assert "mlp.experts.gate_up_proj" not in got
+
+
+@pytest.mark.gpu
+def test_model_free_against_the_oracle_and_with_two_groups(tmp_path):
+    """Every tensor the shard jobs write equals what the CPU oracle makes of the same weight
+    (observer -> qparams -> compressor), for a config with two groups: attention W4A16, MLP FP8."""
+    from safetensors.torch import load_file, save_file
+
+    import oracle
+
+    torch.manual_seed(2)
+    model = _Model().to(torch.bfloat16)
+    sd = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    src = tmp_path / "src"
+    src.mkdir()
+    save_file(sd, str(src / "model.safetensors"))
+    config = {"config_groups": {"attn": {"scheme": "W4A16", "targets": ["re:.*self_attn\\..*_proj"]},
+                                "mlp": {"scheme": "FP8_DYNAMIC", "targets": ["re:.*mlp\\..*_proj"]}},
+              "ignore": ["lm_head"]}
+    out = tmp_path / "out"
+    mf.model_free_ptq(str(src), str(out), config=config, device="cuda:0")
+    got = load_file(str(out / "model.safetensors"))
+    specs = {"self_attn": (oracle.preset("W4A16"), None), "mlp": (oracle.preset("FP8_DYNAMIC"), "float-quantized")}
+    checked = 0
+    for name, w in sd.items():
+        kind = "self_attn" if "self_attn" in name else ("mlp" if "mlp" in name else None)
+        if kind is None or not name.endswith("_proj.weight"):
+            assert torch.equal(got[name], w), name     # untouched (norms, lm_head)
+            continue
+        spec, fmt = specs[kind]
+        qp = oracle.WeightObserver(spec)(w).get_qparams()
+        ref = oracle.compress_weight({"weight": w, "weight_scale": qp["scale"].to(w.dtype),
+                                      "weight_zero_point": qp["zero_point"]}, spec, fmt=fmt)
+        base = name[: -len(".weight")]
+        for k, v in ref.items():
+            g = got[f"{base}.{k}"]
+            assert g.dtype == v.dtype and g.shape == v.shape, (name, k)
+            assert torch.equal(g.view(torch.uint8), v.view(torch.uint8)), (name, k)
+        checked += 1
+    assert checked == 14
+    qc = json.loads((out / "config.json").read_text())["quantization_config"]
+    assert len(qc["config_groups"]) == 2 and qc["format"] == "mixed-precision" and "version" in qc

@@ -120,6 +120,16 @@ def _worker(rank, world, port, q):
                 res[order[id(g)]] = (float(g.H[0, 0]), g.n)
             else:
                 assert g.H is None
+        # activation statistics: min / max observers combine with MIN / MAX, moving averages with AVG
+        from llm_compressor_b200.observers import MinMaxObserver, StaticMinMaxObserver
+        from llm_compressor_b200.quant_args import QuantizationArgs
+        act = QuantizationArgs(num_bits=8, type="float", strategy="tensor", dynamic=False)
+        so, mo = StaticMinMaxObserver("input", act), MinMaxObserver("input", act)
+        for o in (so, mo):
+            o.min_vals, o.max_vals = torch.tensor([-1.0 - rank]), torch.tensor([2.0 + 2 * rank])
+        bdist.wait_for_comms(so.sync_activation_stats() + mo.sync_activation_stats())
+        assert (float(so.min_vals), float(so.max_vals)) == (-2.0, 4.0)
+        assert (float(mo.min_vals), float(mo.max_vals)) == (-1.5, 3.0)
         lin = torch.nn.Linear(4, 4, bias=False)
         lin.weight.data.fill_(float(rank + 5))
         lin.weight_scale = torch.nn.Parameter(torch.full((4, 1), float(rank)), requires_grad=False)
