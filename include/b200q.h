@@ -281,6 +281,30 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
                      const float* global_scale, const b200q_qargs* qa, int blocksize,
                      float* losses, void* workspace, void* stream);
 
+/* Many small problems of one shape per launch (the experts of a mixture-of-experts layer, whose
+ * per-module calls of gptq_quantize.py:67-264 are otherwise bound by launch overhead).  Every
+ * pointer argument is a DEVICE array of `count` device pointers.
+ *
+ * b200q_gptq_factor_batched: H[i] (K x K floats, leading dimension ldh) -> U[i] in place, as
+ * b200q_gptq_factor does, one thread block per problem; K <= 4096 (meant for K <= 2048).
+ * scratch[i]: K*K floats each (b200q_gptq_factor_batched_workspace_bytes(K, count) in total).
+ * status: int32 [count][4], cleared by the call; status[i][0] = B200Q_NOT_POSITIVE_DEFINITE and
+ * status[i][1] = first bad column + 1 (in reversed column order) when problem i failed.
+ *
+ * b200q_gptq_sweep_batched: the sweep of b200q_gptq_sweep for `count` weights of one shape
+ * [N, K], one quantisation scheme and one scale dtype, blocksize 128.  A thread block carries 128
+ * rows of one weight through every column block, trailing updates included (float32 FMA).
+ * U may be NULL (identity for all) and so may zp, col_group and global_scale (absent for all);
+ * losses[i]: float [N]. */
+size_t b200q_gptq_factor_batched_workspace_bytes(int64_t K, int count);
+int b200q_gptq_factor_batched(float* const* H, float* const* scratch, int count, int64_t K, int64_t ldh,
+                              int* status, void* stream);
+int b200q_gptq_sweep_batched(float* const* W, const float* const* U, const void* const* scale, int sdtype,
+                             const void* const* zp, const int32_t* const* col_group,
+                             const float* const* global_scale, float* const* losses, int count, int64_t N,
+                             int64_t K, int64_t ldw, int64_t ldu, const b200q_qargs* qa, int blocksize,
+                             void* stream);
+
 #ifdef __cplusplus
 }
 #endif

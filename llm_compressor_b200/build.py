@@ -25,6 +25,7 @@ SOURCES = [
     "hessian_syrk.cu",
     "gptq_solve.cu",
     "gptq_sweep.cu",
+    "gptq_small.cu",
     "tgemm_tf32.cu",
 ]
 

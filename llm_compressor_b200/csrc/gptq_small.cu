@@ -1,0 +1,293 @@
+// GPTQ solve for MANY SMALL modules at once (the experts of a mixture-of-experts layer).
+//
+// The blocked kernels of gptq_solve.cu / gptq_sweep.cu spend one launch per step of every chain;
+// a layer with hundreds of small modules then needs tens of thousands of launches and is bound by
+// the host.  Here one launch serves a whole batch of equally shaped problems, given as device
+// arrays of pointers:
+//   * sweep_fused_kernel: a CTA owns 128 rows of one module through ALL column blocks - the
+//     128-column block sweep (the lane-per-row scheme of sweep_block_kernel) followed by the
+//     trailing update of those rows, W[rows, after] -= Err * U[block, after], as a float32 FMA
+//     tile product inside the CTA (error panel and the streamed slices of U in shared memory);
+//   * factor_small_kernel (gptq_solve.cu): a CTA factors one small Hessian completely.
+#include "common.cuh"
+
+namespace b200q {
+namespace small {
+
+constexpr int NB = 128;
+constexpr int kRows = 128;                 // rows of a module per CTA (4 row-owning warps)
+constexpr int kThreads = 256;
+constexpr int kSub = 16;
+constexpr int kWLD = kRows + 1;
+constexpr int kColChunk = 64;              // columns of the trailing update per pass
+
+struct SweepBatch {
+  float* const* W; const float* const* U; const void* const* scale; const void* const* zp;
+  const int32_t* const* col_group; const float* const* gscale; float* const* losses;
+  int64_t N, K, ldw, ldu;
+  int strategy, group_size, block_h, zp_kind;
+  int64_t groups_per_row;
+  QRange qr;
+};
+
+__host__ __device__ constexpr size_t sweep_smem_bytes() {
+  return ((size_t)NB * NB + (size_t)NB * kWLD + (size_t)NB * kRows) * sizeof(float);
+}
+
+template <bool SB>
+__device__ __noinline__ float quant_one(float wi, float s, float rs, float z, const QRange qr) {
+  const float q = quant_code_fast<false>(wi, s, rs, z, qr);
+  return dequant_code<SB>(q, s, z);
+}
+
+template <int SDT, bool GLOBAL>
+__global__ void __launch_bounds__(kThreads, 1) sweep_fused_kernel(SweepBatch b) {
+  constexpr bool SB = Elem<SDT>::is_bf16 && !GLOBAL;
+  extern __shared__ float sm[];
+  float* sU = sm;                          // [128][128] diagonal block, later [128][64] slices of U
+  float* sW = sU + NB * NB;                // [128 cols][kWLD]: the block's columns of this CTA's rows
+  float* sErrT = sW + NB * kWLD;           // [128 cols][128 rows]: scaled errors of the block
+  __shared__ float s_rd[NB];
+  __shared__ int s_grp[NB];
+  const int job = blockIdx.y;
+  float* __restrict__ W = b.W[job];
+  const float* __restrict__ U = b.U ? b.U[job] : nullptr;
+  const void* scale = b.scale[job];
+  const void* zp = b.zp ? b.zp[job] : nullptr;
+  const int32_t* col_group = b.col_group ? b.col_group[job] : nullptr;
+  const float g = GLOBAL ? *b.gscale[job] : 1.0f;
+  const bool has_zp = zp != nullptr;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row_base = (int64_t)blockIdx.x * kRows;
+  const int64_t row = row_base + warp * 32 + lane;          // meaningful for warps 0..3
+  const bool live = warp < 4 && row < b.N;
+  int64_t pbase = 0;
+  if (warp < 4) {
+    switch (b.strategy) {
+      case B200Q_TENSOR: pbase = 0; break;
+      case B200Q_CHANNEL: pbase = row; break;
+      case B200Q_BLOCK: pbase = (row / b.block_h) * b.groups_per_row; break;
+      default: pbase = row * b.groups_per_row; break;
+    }
+  }
+  float loss = 0.0f;
+  for (int64_t i1 = 0; i1 < b.K; i1 += NB) {
+    const int bs = (int)((b.K - i1) < NB ? (b.K - i1) : NB);
+    const int64_t i2 = i1 + bs;
+    // ---- diagonal block of U, reciprocal pivots, parameter column of every column
+    for (int idx = threadIdx.x; idx < NB * NB / 4; idx += kThreads) {
+      const int r = idx >> 5, c = (idx & 31) << 2;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < bs && c + 3 >= r) {
+        if (!U) {
+          v.x = (r == c) ? 1.0f : 0.0f; v.y = (r == c + 1) ? 1.0f : 0.0f;
+          v.z = (r == c + 2) ? 1.0f : 0.0f; v.w = (r == c + 3) ? 1.0f : 0.0f;
+        } else {
+          const float* src = U + (i1 + r) * b.ldu + (i1 + c);
+          if (c < bs) v.x = src[0];
+          if (c + 1 < bs) v.y = src[1];
+          if (c + 2 < bs) v.z = src[2];
+          if (c + 3 < bs) v.w = src[3];
+        }
+      }
+      *reinterpret_cast<float4*>(sU + idx * 4) = v;
+    }
+    for (int i = threadIdx.x; i < NB; i += kThreads) {
+      float d = 1.0f;
+      int grp = 0;
+      if (i < bs) {
+        if (U) d = U[(i1 + i) * b.ldu + (i1 + i)];
+        const int col = (int)i1 + i;
+        grp = (b.strategy == B200Q_TENSOR || b.strategy == B200Q_CHANNEL)
+                  ? 0 : (col_group ? col_group[col] : col / b.group_size);
+      }
+      s_rd[i] = __frcp_rn(d);
+      s_grp[i] = grp;
+    }
+    __syncthreads();
+    // ---- the block's columns, swept by the four row-owning warps
+    if (warp < 4) {
+      float* myW = sW + warp * 32;
+      const int64_t row0 = row_base + warp * 32;
+#pragma unroll 4
+      for (int r = 0; r < 32; ++r) {
+        const int64_t rr = row0 + r;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = lane + 32 * k;
+          float v = 0.0f;
+          if (rr < b.N && c < bs) v = W[rr * b.ldw + i1 + c];
+          myW[c * kWLD + r] = v;
+        }
+      }
+      __syncwarp();
+      int cur_grp = -1;
+      float s = 1.0f, z = 0.0f, rs = 1.0f;
+#pragma unroll 1
+      for (int sub = 0; sub * kSub < bs; ++sub) {
+        const int c0 = sub * kSub;
+        float w[kSub], e[kSub];
+#pragma unroll
+        for (int t = 0; t < kSub; ++t) w[t] = myW[(c0 + t) * kWLD + lane];
+#pragma unroll
+        for (int t = 0; t < kSub; ++t) {
+          const int i = c0 + t;
+          e[t] = 0.0f;
+          if (i < bs) {   // uniform
+            const int grp = s_grp[i];
+            if (grp != cur_grp) {   // uniform
+              cur_grp = grp;
+              if (live) {
+                const int64_t pi = pbase + grp;
+                s = Elem<SDT>::load((const typename Elem<SDT>::type*)scale + pi);
+                if (GLOBAL) s = __fdiv_rn(s, g);
+                rs = __frcp_rn(s);
+                if (has_zp) z = load_zp(zp, b.zp_kind, pi);
+              }
+            }
+            const float wi = w[t];
+            const float q = quant_one<SB>(wi, s, rs, z, b.qr);
+            const float diff = __fsub_rn(wi, q);
+            const float tt = __fmul_rn(diff, s_rd[i]);
+            loss = fmaf(tt, tt, loss);
+            e[t] = tt;
+            w[t] = q;
+            const float4* urow = reinterpret_cast<const float4*>(sU + i * NB + c0);
+#pragma unroll
+            for (int k4 = (t + 1) / 4; k4 < kSub / 4; ++k4) {
+              const float4 u = urow[k4];
+              if (4 * k4 + 0 > t) w[4 * k4 + 0] = __fsub_rn(w[4 * k4 + 0], __fmul_rn(tt, u.x));
+              if (4 * k4 + 1 > t) w[4 * k4 + 1] = __fsub_rn(w[4 * k4 + 1], __fmul_rn(tt, u.y));
+              if (4 * k4 + 2 > t) w[4 * k4 + 2] = __fsub_rn(w[4 * k4 + 2], __fmul_rn(tt, u.z));
+              if (4 * k4 + 3 > t) w[4 * k4 + 3] = __fsub_rn(w[4 * k4 + 3], __fmul_rn(tt, u.w));
+            }
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < kSub; ++t) {
+          myW[(c0 + t) * kWLD + lane] = w[t];
+          sErrT[(c0 + t) * kRows + warp * 32 + lane] = e[t];
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int c = c0 + kSub; c < bs; c += 4) {
+          float v0 = myW[(c + 0) * kWLD + lane], v1 = myW[(c + 1) * kWLD + lane];
+          float v2 = myW[(c + 2) * kWLD + lane], v3 = myW[(c + 3) * kWLD + lane];
+#pragma unroll
+          for (int t = 0; t < kSub; ++t) {
+            const float4 u = *reinterpret_cast<const float4*>(sU + (c0 + t) * NB + c);
+            v0 = __fsub_rn(v0, __fmul_rn(e[t], u.x));
+            v1 = __fsub_rn(v1, __fmul_rn(e[t], u.y));
+            v2 = __fsub_rn(v2, __fmul_rn(e[t], u.z));
+            v3 = __fsub_rn(v3, __fmul_rn(e[t], u.w));
+          }
+          myW[(c + 0) * kWLD + lane] = v0; myW[(c + 1) * kWLD + lane] = v1;
+          myW[(c + 2) * kWLD + lane] = v2; myW[(c + 3) * kWLD + lane] = v3;
+        }
+      }
+      __syncwarp();
+      for (int r = 0; r < 32; ++r) {
+        const int64_t rr = row0 + r;
+        if (rr >= b.N) break;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = lane + 32 * k;
+          if (c < bs) W[rr * b.ldw + i1 + c] = myW[c * kWLD + r];
+        }
+      }
+    }
+    __syncthreads();
+    // ---- trailing update of this CTA's rows: W[rows, i2:] -= Err[rows, bs] * U[i1:i2, i2:]
+    if (U && i2 < b.K) {
+      const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;     // 16 x 16 threads, 8 rows x 4 columns each
+      float* sUc = sU;                                            // [128][64]
+      for (int64_t j0 = i2; j0 < b.K; j0 += kColChunk) {
+        for (int idx = threadIdx.x; idx < NB * kColChunk / 4; idx += kThreads) {
+          const int k = idx >> 4, c = (idx & 15) << 2;
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (k < bs) {
+            const float* src = U + (i1 + k) * b.ldu + j0 + c;
+            if (j0 + c + 3 < b.K && ((b.ldu & 3) == 0) && ((((uintptr_t)U) & 15) == 0) && (((j0 + c) & 3) == 0)) {
+              v = *reinterpret_cast<const float4*>(src);
+            } else {
+              if (j0 + c < b.K) v.x = src[0];
+              if (j0 + c + 1 < b.K) v.y = src[1];
+              if (j0 + c + 2 < b.K) v.z = src[2];
+              if (j0 + c + 3 < b.K) v.w = src[3];
+            }
+          }
+          *reinterpret_cast<float4*>(sUc + k * kColChunk + c) = v;
+        }
+        __syncthreads();
+        float acc[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0f;
+#pragma unroll 4
+        for (int k = 0; k < bs; ++k) {
+          const float4 a0 = *reinterpret_cast<const float4*>(sErrT + k * kRows + ty * 8);
+          const float4 a1 = *reinterpret_cast<const float4*>(sErrT + k * kRows + ty * 8 + 4);
+          const float4 u = *reinterpret_cast<const float4*>(sUc + k * kColChunk + tx * 4);
+          const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            acc[i][0] = fmaf(a[i], u.x, acc[i][0]); acc[i][1] = fmaf(a[i], u.y, acc[i][1]);
+            acc[i][2] = fmaf(a[i], u.z, acc[i][2]); acc[i][3] = fmaf(a[i], u.w, acc[i][3]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int64_t rr = row_base + ty * 8 + i;
+          if (rr >= b.N) continue;
+          float* dst = W + rr * b.ldw + j0 + tx * 4;
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            if (j0 + tx * 4 + jj < b.K) dst[jj] = __fsub_rn(dst[jj], acc[i][jj]);
+        }
+        __syncthreads();
+      }
+    }
+  }
+  if (live) b.losses[job][row] = loss * 0.5f;
+}
+
+}  // namespace small
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_gptq_sweep_batched(float* const* W, const float* const* U, const void* const* scale, int sdtype,
+                             const void* const* zp, const int32_t* const* col_group, const float* const* gscale,
+                             float* const* losses, int count, int64_t N, int64_t K, int64_t ldw, int64_t ldu,
+                             const b200q_qargs* qa, int blocksize, void* stream) {
+  using namespace b200q::small;
+  if (!W || !scale || !losses || !qa || count <= 0 || N <= 0 || K <= 0 || ldw < K || (U && ldu < K)) return B200Q_ERR_ARG;
+  if (blocksize != NB) return B200Q_ERR_UNSUPPORTED;
+  if (count > 65535) return B200Q_ERR_ARG;
+  SweepBatch b;
+  int rc = make_qrange(qa, &b.qr); if (rc) return rc;
+  ParamMap pm;
+  rc = make_param_map(qa, N, K, nullptr, &pm); if (rc) return rc;
+  b.W = W; b.U = U; b.scale = scale; b.zp = zp; b.col_group = col_group; b.gscale = gscale; b.losses = losses;
+  b.N = N; b.K = K; b.ldw = ldw; b.ldu = ldu;
+  b.strategy = qa->strategy;
+  b.group_size = (qa->strategy == B200Q_BLOCK) ? qa->block_w : qa->group_size;
+  if (b.group_size <= 0) b.group_size = 1;
+  b.block_h = qa->block_h > 0 ? qa->block_h : 1;
+  b.zp_kind = qa->zp_kind;
+  b.groups_per_row = pm.groups_per_row;
+  void (*kern)(SweepBatch) = nullptr;
+  if (sdtype == B200Q_BF16) kern = gscale ? sweep_fused_kernel<B200Q_BF16, true> : sweep_fused_kernel<B200Q_BF16, false>;
+  else if (sdtype == B200Q_F32) kern = gscale ? sweep_fused_kernel<B200Q_F32, true> : sweep_fused_kernel<B200Q_F32, false>;
+  else return B200Q_ERR_UNSUPPORTED;
+  B200Q_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sweep_smem_bytes()));
+  dim3 grid((unsigned)((N + kRows - 1) / kRows), (unsigned)count, 1);
+  kern<<<grid, kThreads, sweep_smem_bytes(), (cudaStream_t)stream>>>(b);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+}  // extern "C"

@@ -282,6 +282,228 @@ __global__ void __launch_bounds__(kDiagThreads, 1) chol_diag_kernel(float* __res
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Whole factorisation of one SMALL Hessian per CTA, many Hessians per launch.
+//
+// The same one-pass block algorithm as b200q_gptq_factor - A = J H J (index reversal), a
+// right-looking Cholesky A = L L^T carried out together with the forward substitution for
+// X = L^-1, U = J X J - but with every step of a problem inside one CTA: the diagonal blocks go
+// through chol_diag_steps, the 128 x 128 tile products run on the CTA's FMA units from slices
+// staged in shared memory.  A layer with hundreds of small Hessians (the experts of a
+// mixture-of-experts layer) then costs one launch instead of dozens per Hessian.
+//
+// Storage: A (K x K, this problem's scratch) holds, on and below the diagonal, first the
+// remaining part of J H J, then per block column k the panel L[i,k], and finally X; block row k
+// left of the diagonal holds S'[k,j] = -sum_m L[k,m] X[m,j] until step k turns it into
+// X[k,j] = X[k,k] S'[k,j].
+constexpr int kTP = NB + 4;   // stride of a staged operand slice: 16-byte aligned rows, conflict-free transposing stores
+
+struct FactorBatch {
+  float* const* H;     // per problem: the matrix, K x K, leading dimension ldh (in: H, out: U)
+  float* const* A;     // per problem: K * K floats of scratch
+  int* status;         // [count][4], zeroed by the caller
+  int64_t K, ldh;
+};
+
+// C[rows x cols] = beta * C + alpha * P[rows x kk] * Q, all operands with their own leading
+// dimension, rows / cols / kk <= 128.  QT = false: Q = Qm^T with Qm [cols x kk]; QT = true:
+// Q = Qm [kk x cols].  Operands may live in global or shared memory and may have been written
+// earlier by this CTA (no read-only loads).  All 256 threads; thread (ty, tx) owns rows
+// {ty*4 .. +3, 64 + ty*4 .. +3} and columns {tx*4 .. +3, 64 + tx*4 .. +3}.
+template <bool QT>
+__device__ void tile_product(float* C, int64_t ldc, const float* P, int64_t ldp, const float* Qm, int64_t ldq,
+                             int rows, int cols, int kk, float alpha, float beta, float* sP, float* sQ) {
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+  for (int k0 = 0; k0 < kk; k0 += 32) {
+    // slices [32 k][128] of P^T and of Q; a lane per row so that the transposing stores spread over the banks
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int r = tid & 127, k = 4 * ((tid >> 7) + 2 * it);
+      float x[4] = {0.f, 0.f, 0.f, 0.f};
+      if (r < rows) {
+        const float* src = P + (int64_t)r * ldp + k0 + k;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (k0 + k + e < kk) x[e] = src[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sP[(k + e) * kTP + r] = x[e];
+      if (!QT) {
+        float y[4] = {0.f, 0.f, 0.f, 0.f};
+        if (r < cols) {
+          const float* src = Qm + (int64_t)r * ldq + k0 + k;
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (k0 + k + e < kk) y[e] = src[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sQ[(k + e) * kTP + r] = y[e];
+      }
+    }
+    if (QT) {
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int idx = tid + kDiagThreads * it;     // 32 k x 32 column quads
+        const int k = idx >> 5, c = (idx & 31) << 2;
+        float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k0 + k < kk) {
+          const float* src = Qm + (int64_t)(k0 + k) * ldq + c;
+          if (c < cols) y.x = src[0];
+          if (c + 1 < cols) y.y = src[1];
+          if (c + 2 < cols) y.z = src[2];
+          if (c + 3 < cols) y.w = src[3];
+        }
+        *reinterpret_cast<float4*>(sQ + k * kTP + c) = y;
+      }
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int k = 0; k < 32; ++k) {
+      const float4 a0 = *reinterpret_cast<const float4*>(sP + k * kTP + ty * 4);
+      const float4 a1 = *reinterpret_cast<const float4*>(sP + k * kTP + 64 + ty * 4);
+      const float4 b0 = *reinterpret_cast<const float4*>(sQ + k * kTP + tx * 4);
+      const float4 b1 = *reinterpret_cast<const float4*>(sQ + k * kTP + 64 + tx * 4);
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float q[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], q[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = (i < 4) ? ty * 4 + i : 64 + ty * 4 + (i - 4);
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = (j < 4) ? tx * 4 + j : 64 + tx * 4 + (j - 4);
+      if (c >= cols) continue;
+      float* d = C + (int64_t)r * ldc + c;
+      const float prod = alpha * acc[i][j];
+      *d = (beta == 0.0f) ? prod : fmaf(beta, *d, prod);
+    }
+  }
+  __syncthreads();
+}
+
+constexpr size_t kFactorSmallSmem = ((size_t)kDiagSmemFloats + 2 * 32 * kTP) * sizeof(float);
+
+__global__ void __launch_bounds__(kDiagThreads, 1) factor_small_kernel(FactorBatch fb) {
+  extern __shared__ float sm[];
+  float* Lt = sm;                      // diagonal-block scratch; between diagonal blocks a 128 x 129 staging tile
+  float* rowbuf = Lt + NB * kDiagLD;
+  float* rinvs = rowbuf + 2 * NB;
+  float* sP = sm + kDiagSmemFloats;
+  float* sQ = sP + 32 * kTP;
+  const int job = blockIdx.x;
+  float* H = fb.H[job];
+  float* A = fb.A[job];
+  int* status = fb.status + 4 * job;
+  const int64_t K = fb.K, ld = fb.K;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  for (int64_t i = tid; i < K * K; i += kDiagThreads) {
+    const int64_t r = i / K, c = i - r * K;
+    A[i] = H[(K - 1 - r) * fb.ldh + (K - 1 - c)];
+  }
+  __syncthreads();
+  const int nb = (int)((K + NB - 1) / NB);
+  for (int k = 0; k < nb; ++k) {
+    const int k0 = k * NB;
+    const int n = (int)((K - k0) < NB ? (K - k0) : NB);
+    const int rem = (int)(K - k0 - n);
+    float* Xkk = A + (int64_t)k0 * ld + k0;
+    {
+      float v[8][8];
+#pragma unroll
+      for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          const int i = ty + 16 * a, c = tx + 16 * b;
+          float x = (i == c) ? 1.0f : 0.0f;
+          if (i < n && c < n) x = (c <= i) ? Xkk[(int64_t)i * ld + c] : 0.0f;
+          v[a][b] = x;
+        }
+      chol_diag_steps<0>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+      chol_diag_steps<1>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+      chol_diag_steps<2>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+      chol_diag_steps<3>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+      chol_diag_steps<4>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+      chol_diag_steps<5>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+      chol_diag_steps<6>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+      chol_diag_steps<7>(v, Lt, rowbuf, rinvs, n, k0, status, tx, ty);
+      __syncthreads();
+#pragma unroll
+      for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          const int i = ty + 16 * a, c = tx + 16 * b;
+          if (i < n && c < n) Xkk[(int64_t)i * ld + c] = (c <= i) ? v[a][b] : 0.0f;
+        }
+    }
+    __syncthreads();
+    float* tmp = Lt;   // [128][kDiagLD]
+    // X[k, j] = X[k,k] * S'[k, j] for the block columns left of the diagonal
+    for (int j = 0; j < k; ++j) {
+      float* Skj = A + (int64_t)k0 * ld + j * NB;
+      for (int idx = tid; idx < NB * NB; idx += kDiagThreads) {
+        const int r = idx >> 7, c = idx & 127;
+        if (r < n) tmp[r * kDiagLD + c] = Skj[(int64_t)r * ld + c];
+      }
+      __syncthreads();
+      tile_product<true>(Skj, ld, Xkk, ld, tmp, kDiagLD, n, NB, n, 1.0f, 0.0f, sP, sQ);
+    }
+    if (rem <= 0) break;
+    const int nrem = (rem + NB - 1) / NB;
+    // panel: L[i,k] = A[i,k] * X[k,k]^T
+    for (int i = 0; i < nrem; ++i) {
+      const int ri = (rem - i * NB) < NB ? (rem - i * NB) : NB;
+      float* Pi = A + (int64_t)(k0 + n + i * NB) * ld + k0;
+      for (int idx = tid; idx < NB * NB; idx += kDiagThreads) {
+        const int r = idx >> 7, c = idx & 127;
+        if (r < ri && c < n) tmp[r * kDiagLD + c] = Pi[(int64_t)r * ld + c];
+      }
+      __syncthreads();
+      tile_product<false>(Pi, ld, tmp, kDiagLD, Xkk, ld, ri, n, n, 1.0f, 0.0f, sP, sQ);
+    }
+    // trailing updates:  S'[i,j] -= L[i,k] X[k,j] (j < k),  A[i,j] -= L[i,k] L[j,k]^T (k < j <= i)
+    for (int i = 0; i < nrem; ++i) {
+      const int ri = (rem - i * NB) < NB ? (rem - i * NB) : NB;
+      const float* Pi = A + (int64_t)(k0 + n + i * NB) * ld + k0;
+      float* rowi = A + (int64_t)(k0 + n + i * NB) * ld;
+      for (int j = 0; j < k; ++j)
+        tile_product<true>(rowi + j * NB, ld, Pi, ld, A + (int64_t)k0 * ld + j * NB, ld, ri, NB, n, -1.0f, 1.0f, sP, sQ);
+      for (int j = 0; j <= i; ++j) {
+        const int rj = (rem - j * NB) < NB ? (rem - j * NB) : NB;
+        const float* Pj = A + (int64_t)(k0 + n + j * NB) * ld + k0;
+        tile_product<false>(rowi + (k0 + n + j * NB), ld, Pi, ld, Pj, ld, ri, rj, n, -1.0f, 1.0f, sP, sQ);
+      }
+    }
+    // S'[i,k] = -L[i,k] * X[k,k], in place of the panel
+    for (int i = 0; i < nrem; ++i) {
+      const int ri = (rem - i * NB) < NB ? (rem - i * NB) : NB;
+      float* Pi = A + (int64_t)(k0 + n + i * NB) * ld + k0;
+      for (int idx = tid; idx < NB * NB; idx += kDiagThreads) {
+        const int r = idx >> 7, c = idx & 127;
+        if (r < ri && c < n) tmp[r * kDiagLD + c] = Pi[(int64_t)r * ld + c];
+      }
+      __syncthreads();
+      tile_product<true>(Pi, ld, tmp, kDiagLD, Xkk, ld, ri, n, n, -1.0f, 0.0f, sP, sQ);
+    }
+  }
+  __syncthreads();
+  for (int64_t i = tid; i < K * K; i += kDiagThreads) {
+    const int64_t r = i / K, c = i - r * K;
+    H[r * fb.ldh + c] = (c >= r) ? A[(K - 1 - r) * ld + (K - 1 - c)] : 0.0f;
+  }
+}
+
 static inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
 }  // namespace solve
@@ -461,6 +683,26 @@ int b200q_gptq_factor(float* H, int64_t K, int64_t ldh, void* workspace, int* st
 #undef B200Q_RC
 
   reverse_out_kernel<<<grid_for((K * K + 255) / 256, 8), 256, 0, st>>>(A, K, lda, H, ldh);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+size_t b200q_gptq_factor_batched_workspace_bytes(int64_t K, int count) {
+  if (K <= 0 || count <= 0) return 0;
+  return (size_t)K * (size_t)K * sizeof(float) * (size_t)count;
+}
+
+int b200q_gptq_factor_batched(float* const* H, float* const* scratch, int count, int64_t K, int64_t ldh, int* status,
+                              void* stream) {
+  if (!H || !scratch || !status || count <= 0 || K <= 0 || ldh < K) return B200Q_ERR_ARG;
+  if (K > 4096) return B200Q_ERR_UNSUPPORTED;
+  FactorBatch fb;
+  fb.H = H; fb.A = scratch; fb.status = status; fb.K = K; fb.ldh = ldh;
+  cudaStream_t st = (cudaStream_t)stream;
+  B200Q_TRY(cudaMemsetAsync(status, 0, sizeof(int) * 4 * (size_t)count, st));
+  B200Q_TRY(cudaFuncSetAttribute(factor_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kFactorSmallSmem));
+  factor_small_kernel<<<count, kDiagThreads, kFactorSmallSmem, st>>>(fb);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

@@ -22,8 +22,8 @@ from .observers import Observer
 from .quant_args import QuantizationArgs
 
 __all__ = ["make_empty_hessian", "accumulate_hessian", "accumulate_hessian_lower",
-           "finalize_hessian", "factor_hessian", "HessianFactor", "quantize_weight",
-           "GPTQ_PRECISION"]
+           "finalize_hessian", "factor_hessian", "factor_hessians_batched", "resolve_factors",
+           "HessianFactor", "quantize_weight", "quantize_weights_batched", "GPTQ_PRECISION"]
 
 GPTQ_PRECISION = torch.float32
 
@@ -129,6 +129,14 @@ def factor_hessian(hessian: torch.Tensor, percdamp: float = 0.01, actorder=None,
                    defer: bool = False) -> HessianFactor:
     """Permute (act-order), patch dead columns, dampen and factor ``hessian`` (consumed).
     ``defer``: do not wait for the factorisation's status (see ``HessianFactor.resolve``)."""
+    H, perm, diag = _factor_prologue(hessian, percdamp, actorder)
+    factor = HessianFactor(H.shape[0], perm, diag, H, None, ops.gptq_factor_async(H))
+    return factor if defer else factor.resolve()
+
+
+def _factor_prologue(hessian: torch.Tensor, percdamp: float, actorder):
+    """Everything of ``factor_hessian`` before the factorisation itself: (H ready to factor,
+    permutation or None, diagonal before the dead-column patch)."""
     H = hessian
     K = H.shape[0]
     if H.shape != (K, K) or H.dtype != torch.float32:
@@ -139,31 +147,52 @@ def factor_hessian(hessian: torch.Tensor, percdamp: float = 0.01, actorder=None,
         H = ops.permute_hessian(H, perm)
     diag = H.diagonal().clone()
     ops.gptq_prepare(H, None, percdamp)
-    factor = HessianFactor(K, perm, diag, H, None, ops.gptq_factor_async(H))
-    return factor if defer else factor.resolve()
+    return H, perm, diag
 
 
-def quantize_weight(module, quant_args, hessian: Optional[torch.Tensor], blocksize: int = 128,
-                    percdamp: float = 0.01, factor: Optional[HessianFactor] = None, defer: bool = False):
-    """GPTQ-quantise ``module.weight`` given its Hessian (already divided by the sample
-    count).  Returns ``(loss, dict)`` with the fake-quantised weight in the original dtype,
-    ``weight_scale``, ``weight_zero_point`` and, where they apply, ``weight_global_scale`` and
-    ``weight_g_idx``.  ``hessian`` is consumed.  ``module.weight_observer`` must hold
-    statistics unless act-order "group" re-observes; ``module.weight`` is not touched.
+def factor_hessians_batched(hessians, percdamp: float = 0.01, actorder=None):
+    """``factor_hessian(..., defer=True)`` for a list of small Hessians of one size, with all the
+    factorisations in one launch (one thread block per matrix).  The matrices are consumed.
+    Returns the deferred factors; ``resolve_factors`` reads all their status words at once."""
+    parts = [_factor_prologue(H, percdamp, actorder) for H in hessians]
+    status = ops.gptq_factor_batched([H for H, _, _ in parts])
+    return [HessianFactor(H.shape[0], perm, diag, H, None, status[i]) for i, (H, perm, diag) in enumerate(parts)]
 
-    ``factor`` (from ``factor_hessian`` with the same ``percdamp`` and act-order setting) may
-    be passed instead of ``hessian`` when several modules share one Hessian.
 
-    ``defer``: nothing waits for the device; the loss comes back as a 0-dim device tensor, a
-    deferred ``factor`` is used as it is, and the dict carries one extra entry ``"_status"``
-    (the sweep's int32 device status word, non-zero after an expired bounded wait) that the
-    caller must pop and check.  The caller must also ``factor.resolve()`` afterwards and repeat
-    the call without ``defer`` (after re-observing the weight) if the factorisation turned out
-    to have failed."""
+def resolve_factors(factors) -> None:
+    """``HessianFactor.resolve`` for many factors with one wait for the device."""
+    pending = [f for f in factors if f.ok is None]
+    if not pending:
+        return
+    words = torch.stack([f.status.reshape(-1)[:4] for f in pending]).tolist()
+    for f, st in zip(pending, words):
+        if st[2] != 0:
+            raise _lib.B200QError("b200q_gptq_factor: a bounded wait inside the GEMM kernel expired")
+        f.ok = st[0] != _lib.NOT_POSITIVE_DEFINITE
+        if not f.ok:
+            warnings.warn(_NOT_PD_MESSAGE)
+            f.U = None
+
+
+@dataclass
+class _SweepInput:
+    """One module's operands of the column sweep, and what the epilogue needs."""
+    args: QuantizationArgs
+    actorder: Optional[str]
+    factor: HessianFactor
+    W: torch.Tensor
+    scale: torch.Tensor
+    zero_point: torch.Tensor
+    global_scale: Optional[torch.Tensor]
+    col_group: Optional[torch.Tensor]
+    g_idx: Optional[torch.Tensor]
+    final_dtype: torch.dtype
+
+
+def _sweep_input(module, quant_args, hessian, percdamp, factor) -> _SweepInput:
     args = QuantizationArgs.of(quant_args)
     strategy, actorder = args.strategy, args.actorder
     weight = module.weight.data if isinstance(module.weight, torch.nn.Parameter) else module.weight
-    final_dtype = weight.dtype
     observer: Observer = module.weight_observer
     N, K = weight.shape
     if strategy not in ("tensor", "channel", "group", "tensor_group", "block"):
@@ -198,30 +227,77 @@ def quantize_weight(module, quant_args, hessian: Optional[torch.Tensor], blocksi
             col_group = g_idx
 
     qparams = observer.get_qparams()
-    scale, zero_point, global_scale = qparams["scale"], qparams["zero_point"], qparams["global_scale"]
-
     ops.gptq_zero_dead_columns(factor.diag, W)
-    losses, status = ops.gptq_sweep(W, factor.U, scale, zero_point, args, blocksize=blocksize,
-                                    col_group=col_group, global_scale=global_scale, return_status=True)
+    return _SweepInput(args, actorder, factor, W, qparams["scale"], qparams["zero_point"], qparams["global_scale"],
+                       col_group, g_idx, weight.dtype)
 
-    Wq = ops.scatter_columns_cast(W, final_dtype, perm)
+
+def _sweep_output(inp: _SweepInput) -> dict:
+    perm = inp.factor.perm
+    out = {
+        "weight": ops.scatter_columns_cast(inp.W, inp.final_dtype, perm),
+        "weight_scale": inp.scale.to(inp.final_dtype),
+        "weight_zero_point": inp.zero_point.to(inp.args.zp_dtype),
+    }
+    if inp.global_scale is not None:
+        out["weight_global_scale"] = inp.global_scale.to(inp.final_dtype)
+    if inp.actorder == "group":
+        K = inp.W.shape[1]
+        invperm = torch.empty_like(perm)
+        invperm[perm.long()] = torch.arange(K, device=perm.device, dtype=perm.dtype)
+        out["weight_g_idx"] = inp.g_idx[invperm.long()]
+    return out
+
+
+def quantize_weight(module, quant_args, hessian: Optional[torch.Tensor], blocksize: int = 128,
+                    percdamp: float = 0.01, factor: Optional[HessianFactor] = None, defer: bool = False):
+    """GPTQ-quantise ``module.weight`` given its Hessian (already divided by the sample
+    count).  Returns ``(loss, dict)`` with the fake-quantised weight in the original dtype,
+    ``weight_scale``, ``weight_zero_point`` and, where they apply, ``weight_global_scale`` and
+    ``weight_g_idx``.  ``hessian`` is consumed.  ``module.weight_observer`` must hold
+    statistics unless act-order "group" re-observes; ``module.weight`` is not touched.
+
+    ``factor`` (from ``factor_hessian`` with the same ``percdamp`` and act-order setting) may
+    be passed instead of ``hessian`` when several modules share one Hessian.
+
+    ``defer``: nothing waits for the device; the loss comes back as a 0-dim device tensor, a
+    deferred ``factor`` is used as it is, and the dict carries one extra entry ``"_status"``
+    (the sweep's int32 device status word, non-zero after an expired bounded wait) that the
+    caller must pop and check.  The caller must also ``factor.resolve()`` afterwards and repeat
+    the call without ``defer`` (after re-observing the weight) if the factorisation turned out
+    to have failed."""
+    inp = _sweep_input(module, quant_args, hessian, percdamp, factor)
+    losses, status = ops.gptq_sweep(inp.W, inp.factor.U, inp.scale, inp.zero_point, inp.args, blocksize=blocksize,
+                                    col_group=inp.col_group, global_scale=inp.global_scale, return_status=True)
+    out = _sweep_output(inp)
     if defer:
         loss = losses.sum()
+        out["_status"] = status   # the sweep's device status word; the caller checks and removes it
     else:
         loss, st = torch.stack([losses.sum(), status[0].to(torch.float32)]).tolist()
         if st != 0:
             raise _lib.B200QError("b200q_gptq_sweep: a bounded wait inside the GEMM kernel expired")
-    out = {
-        "weight": Wq,
-        "weight_scale": scale.to(final_dtype),
-        "weight_zero_point": zero_point.to(args.zp_dtype),
-    }
-    if global_scale is not None:
-        out["weight_global_scale"] = global_scale.to(final_dtype)
-    if actorder == "group":
-        invperm = torch.empty_like(perm)
-        invperm[perm.long()] = torch.arange(K, device=perm.device, dtype=perm.dtype)
-        out["weight_g_idx"] = g_idx[invperm.long()]
-    if defer:
-        out["_status"] = status   # the sweep's device status word; the caller checks and removes it
     return loss, out
+
+
+def quantize_weights_batched(modules, quant_args, factors, blocksize: int = 128, percdamp: float = 0.01):
+    """``quantize_weight(..., defer=True)`` for many small modules of one weight shape and one
+    quantisation scheme, each with its own (deferred) factor, with all the column sweeps in one
+    launch.  Returns ``[(loss, dict), ...]`` in the order of ``modules``: the losses are 0-dim
+    device tensors and the dicts carry no ``"_status"`` (the batched sweep has no bounded wait).
+    As with the deferred single call, the caller resolves the factors afterwards and redoes the
+    modules whose factorisation failed."""
+    inputs = [_sweep_input(m, quant_args, None, percdamp, f) for m, f in zip(modules, factors)]
+    first = inputs[0]
+
+    def column(name):
+        vals = [getattr(i, name) for i in inputs]
+        if any((v is None) != (vals[0] is None) for v in vals):
+            raise ValueError(f"{name} must be present for all modules of a batch or for none")
+        return None if vals[0] is None else vals
+
+    losses = ops.gptq_sweep_batched([i.W for i in inputs], [i.factor.U for i in inputs], column("scale"),
+                                    column("zero_point"), first.args, col_groups=column("col_group"),
+                                    global_scales=column("global_scale"), blocksize=blocksize)
+    sums = losses.sum(dim=1)
+    return [(sums[k], _sweep_output(i)) for k, i in enumerate(inputs)]

@@ -10,6 +10,7 @@ checkpoint format, nothing is calibrated for it.
 """
 from __future__ import annotations
 
+import collections
 import contextlib
 import re
 import time
@@ -365,14 +366,18 @@ class GPTQModifier(QuantizationMixin):
     Hessians run concurrently on up to ``parallel_streams`` CUDA streams (1: one after another
     on the current stream, like the reference).  Calibration batches smaller than
     ``hessian_stage_tokens`` tokens are gathered and added to the Hessian together (0: one kernel
-    call per batch).
+    call per batch).  When an epoch holds ``batch_small_hessians`` or more Hessians of one width of
+    at most ``small_hessian_columns`` columns (the experts of a mixture-of-experts layer), their
+    factorisations and sweeps run as batched launches, one thread block per problem, instead of
+    dozens of launches per module (0 switches this off).
     """
 
     requires_calibration_data = True
 
     def __init__(self, block_size: int = 128, dampening_frac: Optional[float] = 0.01,
                  actorder: Any = _UNSET, offload_hessians: bool = False, share_hessians: bool = True,
-                 parallel_streams: int = 4, hessian_stage_tokens: int = 32768, **quant_kwargs):
+                 parallel_streams: int = 4, hessian_stage_tokens: int = 32768,
+                 batch_small_hessians: int = 16, small_hessian_columns: int = 2048, **quant_kwargs):
         kw = dict(quant_kwargs)
         kw.setdefault("targets", "Linear")
         super().__init__(**kw)
@@ -383,6 +388,8 @@ class GPTQModifier(QuantizationMixin):
         self.share_hessians = share_hessians
         self.parallel_streams = parallel_streams
         self.hessian_stage_tokens = hessian_stage_tokens
+        self.batch_small_hessians = batch_small_hessians
+        self.small_hessian_columns = small_hessian_columns
         self._groups: dict = {}        # module -> _HessianGroup
         self._num_samples: dict = {}   # module -> None (membership: modules awaiting compression)
         self.trace = None              # optional callback(event: str, module | None) for instrumentation
@@ -545,44 +552,54 @@ class GPTQModifier(QuantizationMixin):
         if not jobs:
             return
         device = jobs[0][0].weight.device
-        run_concurrent([lambda mods=mods: self._compress_group(mods) for mods in jobs], device,
-                       max_streams=self.parallel_streams)
+        if self.batch_small_hessians and self.block_size == 128:
+            # small problems that come in numbers: many Hessians of one width, or one Hessian
+            # shared by many modules (the gate / up projections under all-expert calibration)
+            width = collections.Counter()
+            for mods in jobs:
+                width[mods[0].weight.shape[1]] += len(mods)
+            small = [mods for mods in jobs if mods[0].weight.shape[1] <= self.small_hessian_columns
+                     and width[mods[0].weight.shape[1]] >= self.batch_small_hessians]
+            if small:
+                taken = {id(mods) for mods in small}
+                jobs = [mods for mods in jobs if id(mods) not in taken]
+                self._compress_small_jobs(small)
+        if jobs:
+            run_concurrent([lambda mods=mods: self._compress_group(mods) for mods in jobs], device,
+                           max_streams=self.parallel_streams)
 
-    def _compress_group(self, module_list):
-        """Everything is queued on the current stream without waiting for the device; the
-        factorisation status and the losses are read once at the end.  A Hessian that turned
-        out not to be positive definite gets its modules redone with the identity, as the
-        reference falls back (gptq_quantize.py:157-164)."""
+    def _queue_factors(self, module_list, make_factor):
+        """Take the modules of one Hessian out of the pending tables and give each the factor of its
+        act-order setting, made by ``make_factor(H, actorder)`` once per distinct setting.
+        Returns ([(module, qargs, factor)], the Hessian's device status word or None)."""
         factors = {}
-        # the distinct act-order settings that still need this Hessian
         left = {module.quantization_scheme.weights.actorder for module in module_list}
-        queued = []
-        hess_status = {}
-        t0 = time.perf_counter()
-        self._trace("job_start", module_list[0])
+        taken, status = [], None
         for module in module_list:
             group = self._groups.pop(module)
-            hess_status[id(group)] = group.status
+            status = group.status
             self._num_samples.pop(module, None)
             qargs = module.quantization_scheme.weights
             if qargs.actorder not in factors:
                 left.discard(qargs.actorder)
-                H = group.finalized(keep=bool(left))  # factor_hessian consumes its argument
-                factors[qargs.actorder] = gptq.factor_hessian(H, self.dampening_frac, qargs.actorder, defer=True)
+                H = group.finalized(keep=bool(left))  # the factorisation consumes its argument
+                factors[qargs.actorder] = make_factor(H, qargs.actorder)
                 self._trace("job_factored", module)
-            factor = factors[qargs.actorder]
-            with torch.no_grad():
-                loss, out = gptq.quantize_weight(module, qargs, None, blocksize=self.block_size,
-                                                 percdamp=self.dampening_frac, factor=factor, defer=True)
-            queued.append((module, qargs, factor, loss, out))
-        self._trace("job_swept", module_list[0])
-        # one read for every device status word of the job (the first wait for the device)
-        words = [s for s in (out.pop("_status", None) for _, _, _, _, out in queued) if s is not None]
-        words += [s for s in hess_status.values() if s is not None]
+            taken.append((module, qargs, factors[qargs.actorder]))
+        return taken, status
+
+    @staticmethod
+    def _check_status_words(words):
+        words = [w for w in words if w is not None]
         if words and int(torch.cat([w.reshape(-1)[:1] for w in words]).abs().amax().item()) != 0:
             raise B200QError("a bounded wait inside the Hessian or GEMM kernels of this job expired; "
                              "its results are incomplete")
-        redo = [q for q in queued if not q[2].resolve().ok]
+
+    def _finish_queued(self, queued, t0):
+        """``queued``: [(module, qargs, factor, loss, out)] of deferred solves whose factors have been
+        resolved.  Redo the modules whose Hessian was not positive definite with the identity, as
+        the reference falls back (gptq_quantize.py:157-164), then write every result to its module."""
+        redo = [q for q in queued if not q[2].ok]
         # the deferred call consumed the observers' statistics: observe again before the
         # round-to-nearest redo (act-order "group" re-observes the permuted weight itself)
         for module, qargs, *_ in redo:
@@ -591,11 +608,20 @@ class GPTQModifier(QuantizationMixin):
         for module, qargs, *_ in redo:
             if qargs.actorder != "group":
                 module.weight_observer(module.weight.data)
+        results = []
         for module, qargs, factor, loss, out in queued:
             if not factor.ok:
                 with torch.no_grad():
                     loss, out = gptq.quantize_weight(module, qargs, None, blocksize=self.block_size,
                                                      percdamp=self.dampening_frac, factor=factor)
+            results.append((module, loss, out))
+        # one read for all the losses that are still on the device
+        on_device = [i for i, (_, loss, _) in enumerate(results) if isinstance(loss, torch.Tensor)]
+        if on_device:
+            values = torch.stack([results[i][1].reshape(()) for i in on_device]).tolist()
+            for i, v in zip(on_device, values):
+                results[i] = (results[i][0], v, results[i][2])
+        for module, loss, out in results:
             loss = float(loss)
             name = self._module_names.get(module, type(module).__name__)
             self.losses[name] = loss
@@ -610,6 +636,75 @@ class GPTQModifier(QuantizationMixin):
                     module.register_parameter(attr, torch.nn.Parameter(val, requires_grad=False))
             module.quantization_status = "frozen"
             self._done.add(module)
+
+    def _compress_group(self, module_list):
+        """Everything is queued on the current stream without waiting for the device; the
+        factorisation status and the losses are read once at the end."""
+        t0 = time.perf_counter()
+        self._trace("job_start", module_list[0])
+        taken, hess_status = self._queue_factors(
+            module_list, lambda H, actorder: gptq.factor_hessian(H, self.dampening_frac, actorder, defer=True))
+        queued = []
+        for module, qargs, factor in taken:
+            with torch.no_grad():
+                loss, out = gptq.quantize_weight(module, qargs, None, blocksize=self.block_size,
+                                                 percdamp=self.dampening_frac, factor=factor, defer=True)
+            queued.append((module, qargs, factor, loss, out))
+        self._trace("job_swept", module_list[0])
+        # one read for every device status word of the job (the first wait for the device)
+        self._check_status_words([out.pop("_status", None) for *_, out in queued] + [hess_status])
+        gptq.resolve_factors([q[2] for q in queued])
+        self._finish_queued(queued, t0)
+
+    def _compress_small_jobs(self, jobs):
+        """Many Hessians of few columns: the same steps as ``_compress_group`` for every job, but the
+        factorisations of one width and the sweeps of one weight shape and scheme are gathered
+        into batched launches (one thread block per problem) on the current stream."""
+        t0 = time.perf_counter()
+        self._trace("job_start", jobs[0][0])
+        requests = []   # (H, actorder, holder): the holder receives the factor once it exists
+
+        def ask(H, actorder):
+            holder = []
+            requests.append((H, actorder, holder))
+            return holder
+
+        taken, words = [], []
+        for mods in jobs:
+            part, status = self._queue_factors(mods, ask)
+            taken += part
+            words.append(status)
+        by_kind: dict = {}
+        for H, actorder, holder in requests:
+            by_kind.setdefault((H.shape[0], H.stride(0), actorder), []).append((H, holder))
+        for (_, _, actorder), items in by_kind.items():
+            if len(items) >= self.batch_small_hessians:
+                factors = gptq.factor_hessians_batched([H for H, _ in items], self.dampening_frac, actorder)
+            else:   # a few matrices: the tensor-core factorisation, one after another
+                factors = [gptq.factor_hessian(H, self.dampening_frac, actorder, defer=True) for H, _ in items]
+            for (_, holder), factor in zip(items, factors):
+                holder.append(factor)
+        del requests, by_kind
+        by_shape: dict = {}
+        for module, qargs, holder in taken:
+            key = (tuple(module.weight.shape), module.weight.dtype, repr(qargs))
+            by_shape.setdefault(key, []).append((module, qargs, holder[0]))
+        queued = []
+        for items in by_shape.values():
+            with torch.no_grad():
+                if len(items) >= 4:
+                    done = gptq.quantize_weights_batched([m for m, _, _ in items], items[0][1],
+                                                         [f for _, _, f in items], blocksize=self.block_size,
+                                                         percdamp=self.dampening_frac)
+                else:
+                    done = [gptq.quantize_weight(m, q, None, blocksize=self.block_size, percdamp=self.dampening_frac,
+                                                 factor=f, defer=True) for m, q, f in items]
+                    words += [out.pop("_status", None) for _, out in done]
+            queued += [(m, q, f, loss, out) for (m, q, f), (loss, out) in zip(items, done)]
+        self._trace("job_swept", jobs[0][0])
+        self._check_status_words(words)
+        gptq.resolve_factors([q[2] for q in queued])
+        self._finish_queued(queued, t0)
 
     @staticmethod
     def _log_metric(name, seconds, loss):

@@ -404,6 +404,74 @@ def gptq_sweep(wf, U, scale, zp, args: QuantizationArgs, blocksize=128, col_grou
     return losses
 
 
+def _pointer_table(rows) -> torch.Tensor:
+    """Device int64 [len(rows), count]: row r holds the addresses of the tensors in rows[r]
+    (a row that is None becomes a row of zeros and is passed to the library as NULL)."""
+    first = next(r for r in rows if r is not None)
+    table = [[0] * len(first) if r is None else [t.data_ptr() for t in r] for r in rows]
+    return torch.tensor(table, dtype=torch.int64, device=first[0].device)
+
+
+def gptq_factor_batched(Hs) -> torch.Tensor:
+    """In place H -> U for a list of small Hessians of one size, one thread block each, in one
+    launch.  Returns the device status words, int32 [count, 4] (see ``gptq_factor_async``)."""
+    _need_cuda(*Hs)
+    lib = _lib.load()
+    K, ld = Hs[0].shape[0], Hs[0].stride(0)
+    for H in Hs:
+        if H.shape != (K, K) or H.stride(0) != ld or H.stride(1) != 1 or H.dtype != torch.float32:
+            raise ValueError("batched factorisation needs float32 Hessians of one size and one layout")
+    count = len(Hs)
+    scratch = torch.empty((count, K * K), dtype=torch.float32, device=Hs[0].device)
+    status = torch.empty((count, 4), dtype=torch.int32, device=Hs[0].device)
+    table = _pointer_table([Hs, list(scratch.unbind(0))])
+    check(lib.b200q_gptq_factor_batched(ptr(table[0]), ptr(table[1]), count, K, ld, ptr(status), stream_ptr()),
+          "b200q_gptq_factor_batched")
+    return status
+
+
+def gptq_sweep_batched(wfs, Us, scales, zps, args: QuantizationArgs, col_groups=None, global_scales=None,
+                       blocksize=128) -> torch.Tensor:
+    """The column sweep, in place, on a list of float32 weights of one shape that share the
+    quantisation scheme, in one launch.  ``Us``, ``zps``, ``col_groups``, ``global_scales``: a list
+    with one tensor per weight, or None for all.  Returns the per-row losses [count, N]."""
+    count = len(wfs)
+    N, K, ld = _2d(wfs[0])
+    dev = wfs[0].device
+    scales = [s.contiguous() for s in scales]
+    sdt = _dt(scales[0])
+    zps = None if zps is None else [z.contiguous() for z in zps]
+    col_groups = None if col_groups is None else [c.to(torch.int32).contiguous() for c in col_groups]
+    global_scales = None if global_scales is None else [g.to(torch.float32).contiguous() for g in global_scales]
+    for lst in (wfs, Us, scales, zps, col_groups, global_scales):
+        if lst is not None:
+            if len(lst) != count:
+                raise ValueError("one tensor per weight, or None for all")
+            _need_cuda(*lst)
+    for w in wfs:
+        if _2d(w) != (N, K, ld) or w.dtype != torch.float32:
+            raise ValueError("batched sweep needs float32 weights of one shape and one layout")
+    ldu = 0
+    if Us is not None:
+        ldu = Us[0].stride(0)
+        for U in Us:
+            if U.shape != (K, K) or U.stride(0) != ldu or U.stride(1) != 1:
+                raise ValueError("batched sweep needs factors of one size and one layout")
+    if any(_dt(s) != sdt or s.numel() != scales[0].numel() for s in scales):
+        raise ValueError("batched sweep needs scales of one dtype and one shape")
+    losses = torch.empty((count, N), dtype=torch.float32, device=dev)
+    table = _pointer_table([wfs, Us, scales, zps, col_groups, global_scales, list(losses.unbind(0))])
+
+    def row(i, present):
+        return ptr(table[i]) if present is not None else None
+
+    check(_lib.load().b200q_gptq_sweep_batched(
+        ptr(table[0]), row(1, Us), ptr(table[2]), sdt, row(3, zps), row(4, col_groups), row(5, global_scales),
+        ptr(table[6]), count, N, K, ld, ldu, args.c_struct(), int(blocksize), stream_ptr()),
+        "b200q_gptq_sweep_batched")
+    return losses
+
+
 def gemm_tf32x3(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, trans_b: bool, alpha=1.0, beta=0.0,
                 lower_tiles=False, workspace: "torch.Tensor | None" = None) -> torch.Tensor:
     """c = beta*c + alpha * a @ (b.T if trans_b else b) on the tensor cores with float32 accuracy;
