@@ -68,8 +68,19 @@ def compress_mx_scale(scale: torch.Tensor) -> torch.Tensor:
     return ops.compress_scale(scale, "e8m0")
 
 
-def pack_fp4_to_uint8(*_a, **_k):
-    raise NotImplementedError("FP4 codes are produced packed by quantize_pack / nvfp4_quantize_pack")
+def pack_fp4_to_uint8(x: torch.Tensor) -> torch.Tensor:
+    """E2M1-valued floats [..., K] -> uint8 [..., K/2]: 3-bit magnitude index with the sign bit on
+    top (-0.0 packs as 0x8), element 2i in the low nibble (nvfp4/helpers.py:34-74).  Runs the
+    packing kernel with a unit scale, under which E2M1 values quantise to themselves."""
+    if x.shape[-1] % 2:
+        raise ValueError("tensor must have an even number of columns for nibble packing")
+    flat = x.reshape(-1, x.shape[-1])
+    if flat.dtype not in (torch.bfloat16, torch.float32):
+        flat = flat.to(torch.float32)
+    args = QuantizationArgs(num_bits=4, type="float", symmetric=True, strategy="tensor")
+    one = torch.ones(1, dtype=flat.dtype, device=flat.device)
+    packed = ops.quantize_pack(flat.contiguous(), one, None, args)
+    return packed.reshape(*x.shape[:-1], x.shape[-1] // 2)
 
 
 def compress_state_dict(state_dict: dict, scheme, fmt: str | None = None) -> dict:

@@ -401,25 +401,6 @@ __device__ __forceinline__ void minmax8_bf16(const uint4& raw, float& lo, float&
 // negative and one packed signed maximum finds the maximum if it is positive; whatever they
 // return otherwise has the other sign and is replaced by zero by the clamp.  Three inputs per
 // instruction (VIMNMX3): 4 instructions per chunk of 8 elements.
-#ifdef B200Q_RANGE_HMNMX
-struct RangeQ {
-  __nv_bfloat162 mn, mx;
-  __device__ __forceinline__ void first(const uint4& raw) {
-    const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    mx = __hmax2(__hmax2(w[0], w[1]), __hmax2(w[2], w[3]));
-    mn = __hmin2(__hmin2(w[0], w[1]), __hmin2(w[2], w[3]));
-  }
-  __device__ __forceinline__ void add(const uint4& raw) {
-    const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    mx = __hmax2(__hmax2(mx, w[0]), __hmax2(__hmax2(w[1], w[2]), w[3]));
-    mn = __hmin2(__hmin2(mn, w[0]), __hmin2(__hmin2(w[1], w[2]), w[3]));
-  }
-  __device__ __forceinline__ void finish(float& lo, float& hi) const {
-    hi = fmaxf(fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y)), 0.0f);
-    lo = fminf(fminf(__bfloat162float(mn.x), __bfloat162float(mn.y)), 0.0f);
-  }
-};
-#else
 struct RangeQ {
   uint32_t umax, smax;
   __device__ __forceinline__ void first(const uint4& raw) {
@@ -438,7 +419,6 @@ struct RangeQ {
     hi = fmaxf(__uint_as_float((uint32_t)sv << 16), 0.0f);
   }
 };
-#endif
 // min / max kept as bf16 pairs across several chunks, widened once at the end
 struct MinMax2 {
   __nv_bfloat162 mn, mx;

@@ -19,3 +19,11 @@ def golden():
 
     path = os.path.join(ROOT, "tests", "golden", "golden.pt")
     return torch.load(path, weights_only=False)
+
+
+@pytest.fixture(scope="session")
+def sgpt_golden():
+    import torch
+
+    path = os.path.join(ROOT, "tests", "golden", "sgpt_hessian.pt")
+    return torch.load(path, weights_only=False)

@@ -17,6 +17,10 @@ What goes into the file
   mse_cases      the reference ``memoryless_mse`` observer on seeded weights.
   hessian_cases  ``accumulate_hessian`` of gptq_quantize.py, unmodified.
   gptq_cases     ``quantize_weight`` of gptq_quantize.py, unmodified.
+
+``sgpt_hessian.pt`` (a separate small file; ``--sgpt-only`` writes it alone) holds the
+running-mean Hessian of modifiers/pruning/sparsegpt/sgpt_sparsify.py:20-56 after each of three
+calls on seeded activations.
 """
 from __future__ import annotations
 
@@ -279,6 +283,39 @@ def _gptq_cases(ref):
     return cases
 
 
+def _sgpt_hessian_cases():
+    """Outputs of ``accumulate_hessian`` of modifiers/pruning/sparsegpt/sgpt_sparsify.py (the
+    running-mean Hessian of SparseGPT / Wanda), loaded from the reference checkout unmodified."""
+    import importlib.util
+
+    path = os.path.join(ref_loader.REF_ROOT, "src", "llmcompressor", "modifiers", "pruning", "sparsegpt",
+                        "sgpt_sparsify.py")
+    spec = importlib.util.spec_from_file_location("ref_sgpt_sparsify", path)
+    sg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sg)
+    cases = {}
+    for name, (B, S, K) in {"b2_s96_k64": (2, 96, 64), "b3_s50_k160": (3, 50, 160), "2d_s33_k48": (0, 33, 48)}.items():
+        lin = torch.nn.Linear(K, 8, bias=False)
+        x = synth_acts(max(B, 1), S, K, seed=710)
+        if B == 0:
+            x = x[0]
+        H = sg.make_empty_hessian(lin)
+        n = 0
+        steps = []
+        for factor in (1.0, 0.5, 2.0):
+            H, n = sg.accumulate_hessian(x * factor, lin, H, n)
+            steps.append(dict(H=H.clone(), n=n))
+        cases[name] = dict(x=x, factors=(1.0, 0.5, 2.0), steps=steps)
+    return cases
+
+
+def write_sgpt_fixture():
+    assert ref_loader.reference_available(), "set LLMC_REFERENCE_ROOT to the llm-compressor checkout"
+    path = os.path.join(HERE, "sgpt_hessian.pt")
+    torch.save(dict(meta=dict(torch=torch.__version__), cases=_sgpt_hessian_cases()), path)
+    print("wrote", path, os.path.getsize(path) // 1024, "KiB")
+
+
 def main():
     ref = ref_loader.load_reference()
     import compressed_tensors
@@ -298,4 +335,8 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    if "--sgpt-only" in sys.argv:
+        write_sgpt_fixture()     # the small separate fixture, without regenerating golden.pt
+    else:
+        main()
+        write_sgpt_fixture()

@@ -75,6 +75,18 @@ def test_hessian_running_mean_variant():
         assert torch.equal(H, H.t())
 
 
+def test_hessian_running_mean_golden(sgpt_golden):
+    """Against outputs of the reference's sgpt_sparsify.accumulate_hessian after each call."""
+    for name, c in sgpt_golden["cases"].items():
+        K = c["x"].shape[-1]
+        lin = torch.nn.Linear(K, 8, bias=False)
+        H, n = torch.zeros(K, K, device=DEV), 0
+        for factor, step in zip(c["factors"], c["steps"]):
+            H, n = gptq.accumulate_hessian_running_mean((c["x"] * factor).to(DEV), lin, H, n)
+            assert n == step["n"], name
+            assert rel_fro(H, step["H"]) < HESSIAN_RTOL, name
+
+
 def test_hessian_noncontiguous_and_3d():
     x = synth_acts(3, 100, 136, seed=9)  # [B,S,K] with K % 8 == 0
     H_ref, n_ref = oracle.accumulate_hessian(x, oracle.make_empty_hessian(136), 0)

@@ -246,6 +246,21 @@ def test_nvfp4_on_rounding_boundaries():
     assert bits_equal(r["scale_store"], ref["weight_scale"])
 
 
+def test_pack_fp4_to_uint8_helper():
+    """The stand-alone packing helper on every E2M1 value of both signs (-0.0 included)."""
+    from llm_compressor_b200 import compressors
+    vals = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+    vals = torch.cat([vals, -vals])
+    g = torch.Generator().manual_seed(3)
+    x = vals[torch.randint(0, 16, (37, 96), generator=g)]
+    for dtype in (torch.bfloat16, torch.float32):
+        got = compressors.pack_fp4_to_uint8(x.to(dtype).to(DEV))
+        assert got.dtype == torch.uint8 and tuple(got.shape) == (37, 48)
+        assert torch.equal(got.cpu(), oracle.pack_fp4(x.to(dtype)))
+    with pytest.raises(ValueError, match="even number of columns"):
+        compressors.pack_fp4_to_uint8(x[:, :5].to(DEV))
+
+
 @pytest.mark.parametrize("N,K", [(64, 512), (300, 1024)])
 def test_nvfp4_two_pass_equals_observer_then_compressor(N, K):
     """amax pass + fused NVFP4 pass (alone, and with fused partners sharing the global scale) equals

@@ -135,6 +135,17 @@ def test_hessian_cases(golden):
         assert torch.equal(H, c["H"]), name
 
 
+def test_running_mean_hessian_cases(sgpt_golden):
+    """The oracle's running-mean Hessian against outputs of the reference's sgpt_sparsify.py."""
+    for name, c in sgpt_golden["cases"].items():
+        K = c["x"].shape[-1]
+        H, n = oracle.make_empty_hessian(K), 0
+        for factor, step in zip(c["factors"], c["steps"]):
+            H, n = oracle.accumulate_hessian_running_mean(c["x"] * factor, H, n)
+            assert n == step["n"], name
+            assert same(H, step["H"]), name
+
+
 def test_gptq_cases(golden):
     for name, c in golden["gptq_cases"].items():
         args = spec_from(c["args"])
