@@ -70,17 +70,15 @@ def compress_mx_scale(scale: torch.Tensor) -> torch.Tensor:
 
 def pack_fp4_to_uint8(x: torch.Tensor) -> torch.Tensor:
     """E2M1-valued floats [..., K] -> uint8 [..., K/2]: 3-bit magnitude index with the sign bit on
-    top (-0.0 packs as 0x8), element 2i in the low nibble (nvfp4/helpers.py:34-74).  Runs the
-    packing kernel with a unit scale, under which E2M1 values quantise to themselves."""
+    top (-0.0 packs as 0x8), element 2i in the low nibble (nvfp4/helpers.py:34-74).  A stand-alone
+    helper in tensor operations for callers that already hold E2M1 values; the save path never
+    calls it, its kernels emit packed codes directly."""
     if x.shape[-1] % 2:
         raise ValueError("tensor must have an even number of columns for nibble packing")
-    flat = x.reshape(-1, x.shape[-1])
-    if flat.dtype not in (torch.bfloat16, torch.float32):
-        flat = flat.to(torch.float32)
-    args = QuantizationArgs(num_bits=4, type="float", symmetric=True, strategy="tensor")
-    one = torch.ones(1, dtype=flat.dtype, device=flat.device)
-    packed = ops.quantize_pack(flat.contiguous(), one, None, args)
-    return packed.reshape(*x.shape[:-1], x.shape[-1] // 2)
+    mag = x.abs().to(torch.float32)
+    steps = torch.tensor([0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], device=x.device)
+    nibble = (mag.unsqueeze(-1) >= steps).sum(-1).to(torch.uint8) | (torch.signbit(x).to(torch.uint8) << 3)
+    return nibble[..., 0::2] | (nibble[..., 1::2] << 4)
 
 
 def compress_state_dict(state_dict: dict, scheme, fmt: str | None = None) -> dict:

@@ -77,12 +77,13 @@ class HooksMixin:
         finally:
             HooksMixin._HOOKS_DISABLED = prev
 
-    def register_hook(self, module: torch.nn.Module, fn, kind: str = "forward"):
+    def register_hook(self, module: torch.nn.Module, fn, kind: str = "forward", with_kwargs: bool = False):
         def wrapped(*a, **k):
             if HooksMixin._HOOKS_DISABLED:
                 return None
             return fn(*a, **k)
-        handle = getattr(module, f"register_{kind}_hook")(wrapped)
+        register = getattr(module, f"register_{kind}_hook")
+        handle = register(wrapped, with_kwargs=True) if with_kwargs else register(wrapped)
         self._hooks.append(handle)
         return handle
 
@@ -104,21 +105,26 @@ class QuantizationMixin(HooksMixin):
         self.targets = [targets] if isinstance(targets, str) else list(targets)
         self.ignore = list(ignore or [])
         self.scheme = scheme
-        self.kv_cache_scheme = kv_cache_scheme
+        self.kv_cache_scheme = None if kv_cache_scheme is None else QuantizationArgs.of(kv_cache_scheme)
         self.weight_observer = weight_observer
         self.input_observer = input_observer
         self.output_observer = output_observer
         self.observer = observer
         self.bypass_divisibility_checks = bypass_divisibility_checks
-        if kv_cache_scheme is not None:
-            raise NotImplementedError("kv-cache quantisation is outside this package's path")
+        if self.kv_cache_scheme is not None:
+            kv = self.kv_cache_scheme
+            if kv.strategy != "tensor" or kv.dynamic is not False:
+                raise NotImplementedError("kv-cache scales are calibrated per tensor and statically "
+                                          f"(got strategy {kv.strategy!r}, dynamic {kv.dynamic!r})")
         self._resolved: Optional[dict] = None
         self._module_names: dict = {}
+        self._attention_names: dict = {}   # attention modules that carry kv-cache scales
 
     def recipe_args(self) -> dict:
         """Constructor arguments for ``recipe.yaml`` (unset ones are left out by the writer)."""
         args = dict(config_groups=self.config_groups, targets=self.targets, ignore=self.ignore, scheme=self.scheme,
-                    kv_cache_scheme=self.kv_cache_scheme, weight_observer=self.weight_observer,
+                    kv_cache_scheme=None if self.kv_cache_scheme is None else _plain_args(self.kv_cache_scheme),
+                    weight_observer=self.weight_observer,
                     input_observer=self.input_observer, output_observer=self.output_observer,
                     observer=self.observer,
                     bypass_divisibility_checks=self.bypass_divisibility_checks or None)
@@ -221,6 +227,28 @@ class QuantizationMixin(HooksMixin):
                         reg("input_scale", torch.empty(1, dtype=dt if dt.is_floating_point else torch.float16,
                                                        device=dev))
                         reg("input_zero_point", torch.zeros(1, dtype=a.zp_dtype, device=dev))
+        if self.kv_cache_scheme is not None:
+            # attention modules get k_scale / v_scale (CT lifecycle/initialize.py:255-310); the scheme
+            # sits on the module as its input_activations, as the reference's config resolution puts it
+            kv = self.kv_cache_scheme
+            attn = match_named_modules(model, KV_CACHE_TARGETS, self.ignore)
+            if not attn:
+                raise ValueError(f"kv_cache_scheme given but no module matches {KV_CACHE_TARGETS}")
+            for name, module in attn:
+                first = next(module.parameters(), None)
+                if first is None:
+                    raise ValueError(f"attention module {name} has no parameters to take device and dtype from")
+                module.quantization_scheme = QuantizationScheme(targets=list(KV_CACHE_TARGETS), weights=None,
+                                                                input_activations=kv)
+                module.quantization_status = "initialized"
+                self._attention_names[module] = name
+                dt = first.dtype if first.dtype.is_floating_point else torch.float16
+                for base in ("k", "v"):
+                    module.register_parameter(f"{base}_scale", torch.nn.Parameter(
+                        torch.empty(1, dtype=dt, device=first.device), requires_grad=False))
+                    if not kv.symmetric:
+                        module.register_parameter(f"{base}_zero_point", torch.nn.Parameter(
+                            torch.zeros(1, dtype=kv.zp_dtype, device=first.device), requires_grad=False))
         if bad:
             lines = "\n".join(f"  {n}: columns {k} not divisible by group_size {g}" for n, k, g in bad)
             raise ValueError(
@@ -242,36 +270,83 @@ class QuantizationMixin(HooksMixin):
                 name = a.observer if a.observer not in (None, "memoryless_minmax") else "minmax"
                 module.input_observer = Observer.load_from_registry(name, base_name="input", args=a)
                 self.register_hook(module, _calibrate_input_hook, "forward_pre")
+        for module in self._attention_names:
+            a = module.quantization_scheme.input_activations
+            name = a.observer if a.observer not in (None, "memoryless_minmax") else "minmax"
+            module.k_observer = Observer.load_from_registry(name, base_name="k", args=a)
+            module.v_observer = Observer.load_from_registry(name, base_name="v", args=a)
+            self.register_hook(module, _observing_cache_hook, "forward_pre", with_kwargs=True)
         fuse_weight_observers(model)
 
     @property
     def calibrates_activations(self) -> bool:
         """True when some resolved scheme has statically calibrated input activations."""
         groups = self._resolved if self._resolved is not None else self.resolve_quantization_config()
-        return any(s.input_activations is not None and s.input_activations.dynamic is not True
-                   for s in groups.values())
+        return self.kv_cache_scheme is not None or any(
+            s.input_activations is not None and s.input_activations.dynamic is not True for s in groups.values())
 
     def update_activation_qparams(self, modules) -> None:
         """Epoch end for activation observers: combine the ranks' statistics, then write
         ``input_scale`` / ``input_zero_point`` / ``input_global_scale``
         (quantization/base.py:83-108, calibration.py:109-162)."""
-        mods = [m for m in modules if getattr(m, "input_observer", None) is not None
-                and m.input_observer.has_statistics]
-        if not mods:
-            return
-        if bdist.is_distributed():
-            pending = []
-            for m in mods:
-                pending.extend(m.input_observer.sync_activation_stats())
-            bdist.wait_for_comms(pending)
-        update_qparams(mods, "input")
+        modules = list(modules)
+        pending = []
+        seen = []
+        for base in ("input", "k", "v"):
+            mods = [m for m in modules if getattr(m, f"{base}_observer", None) is not None
+                    and getattr(m, f"{base}_observer").has_statistics]
+            if mods and bdist.is_distributed():
+                for m in mods:
+                    pending.extend(getattr(m, f"{base}_observer").sync_activation_stats())
+            seen.append((base, mods))
+        bdist.wait_for_comms(pending)
+        for base, mods in seen:
+            update_qparams(mods, base)
+            if base == "v":
+                for m in mods:
+                    m.quantization_status = "frozen"
 
     def end_calibration(self, model: torch.nn.Module) -> None:
         self.remove_hooks()
-        for _, module in self.quantized_modules(model):
-            for name in ("weight_observer", "input_observer"):
+        for module in [m for _, m in self.quantized_modules(model)] + list(self._attention_names):
+            for name in ("weight_observer", "input_observer", "k_observer", "v_observer"):
                 if hasattr(module, name):
                     delattr(module, name)
+
+
+KV_CACHE_TARGETS = ("re:.*self_attn$",)   # the reference's match for attention modules (mixin.py:216-218)
+
+
+class _ObservingCache:
+    """Stands in for ``past_key_values`` during a calibration forward of an attention module: the
+    attention calls ``update(key_states, value_states, layer_idx, ...)`` with the post-rotary keys
+    and the values, [batch, kv_heads, tokens, head_dim], which are what a cache would store.  They
+    go to the module's k / v observers and on to the cache that was passed in, if any
+    (compressed-tensors modeling/kvcache.py:29-84, calibration.py:187-196)."""
+
+    def __init__(self, module, inner):
+        self.module, self.inner = module, inner
+
+    def update(self, key_states, value_states, *args, **kwargs):
+        self.module.k_observer(key_states)
+        self.module.v_observer(value_states)
+        if self.inner is not None:
+            return self.inner.update(key_states, value_states, *args, **kwargs)
+        return key_states, value_states
+
+    def __getattr__(self, name):   # anything else an attention implementation asks of a cache
+        inner = self.__dict__.get("inner")
+        if inner is None:
+            raise AttributeError(name)
+        return getattr(inner, name)
+
+
+def _observing_cache_hook(module, args, kwargs):
+    import inspect
+    name = "past_key_values" if "past_key_values" in inspect.signature(module.forward).parameters \
+        else "past_key_value"
+    kwargs[name] = _ObservingCache(module, kwargs.get(name))
+    return args, kwargs
 
 
 def _calibrate_input_hook(module, args):
@@ -299,8 +374,9 @@ def update_qparams(modules: Iterable[torch.nn.Module], base_name: str = "weight"
         qp = obs.get_qparams()
         if hasattr(m, f"{base_name}_scale"):    # absent for locally dynamic activations (global scale only)
             getattr(m, f"{base_name}_scale").data.copy_(qp["scale"].reshape(getattr(m, f"{base_name}_scale").shape))
-            getattr(m, f"{base_name}_zero_point").data.copy_(qp["zero_point"].reshape(
-                getattr(m, f"{base_name}_zero_point").shape))
+            if hasattr(m, f"{base_name}_zero_point"):   # symmetric kv-cache scales carry none
+                getattr(m, f"{base_name}_zero_point").data.copy_(qp["zero_point"].reshape(
+                    getattr(m, f"{base_name}_zero_point").shape))
         if qp["global_scale"] is not None and hasattr(m, f"{base_name}_global_scale"):
             getattr(m, f"{base_name}_global_scale").data.copy_(qp["global_scale"])
         if base_name == "weight":
@@ -324,9 +400,10 @@ class QuantizationModifier(QuantizationMixin):
         self.start_calibration(model)
 
     def on_sequential_epoch_end(self, model, modules: Iterable[torch.nn.Module], **_):
+        modules = list(modules)
+        self.update_activation_qparams(modules)
         modules = [m for m in modules if hasattr(m, "weight_observer")
                    and getattr(m, "quantization_status", None) != "frozen"]
-        self.update_activation_qparams(modules)
         if bdist.is_distributed():
             # owners by weight size; each rank observes its share, scales are broadcast
             items, rank_to, to_rank = bdist.greedy_bin_packing(
@@ -492,8 +569,9 @@ class GPTQModifier(QuantizationMixin):
         return None
 
     def on_sequential_epoch_end(self, model, modules: Iterable[torch.nn.Module], **_):
+        modules = list(modules)
+        self.update_activation_qparams(modules)
         mods = [m for m in modules if m in self._num_samples]
-        self.update_activation_qparams(mods)
         observe(mods, "weight")
         self.compress_modules(mods)
 
@@ -725,6 +803,16 @@ class GPTQModifier(QuantizationMixin):
                              f"compressed: {names}{' ...' if len(missed) > 8 else ''}")
         self._groups, self._num_samples, self._hooked = {}, {}, []
         return True
+
+
+def _plain_args(a: QuantizationArgs) -> dict:
+    """QuantizationArgs as plain recipe / config values."""
+    out = {}
+    for k, v in vars(a).items():
+        if v is None or (k == "observer_kwargs" and not v):
+            continue
+        out[k] = str(v).replace("torch.", "") if isinstance(v, torch.dtype) else v
+    return out
 
 
 def _plain_scheme(g):

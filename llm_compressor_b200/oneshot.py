@@ -235,8 +235,16 @@ def compressed_state_dict(model, compress: bool = True):
     state, formats, groups, ignore = {}, set(), {}, []
     quantised = {n: m for n, m in model.named_modules() if hasattr(m, "quantization_scheme")}
     skip = set()
+    kv_cache_scheme = None
     for name, mod in quantised.items():
         scheme = mod.quantization_scheme
+        if scheme.weights is None and hasattr(mod, "k_scale"):
+            # an attention module that only carries kv-cache scales: no config group of its own, its
+            # k_scale / v_scale are saved as they are (CT quant_config.py:184-208)
+            if getattr(mod, "quantization_status", "frozen") != "frozen":
+                raise ValueError(f"{name} has a kv-cache scheme but its k / v scales were never calibrated")
+            kv_cache_scheme = scheme.input_activations
+            continue
         if scheme.weights is not None and getattr(mod, "quantization_status", "frozen") != "frozen":
             raise ValueError(f"{name} has a weight quantisation scheme but was never calibrated: its scale is "
                              "uninitialised (was it outside the calibrated blocks, or never reached by a forward pass?)")
@@ -278,7 +286,7 @@ def compressed_state_dict(model, compress: bool = True):
                               "input_activations": args_dict(s.input_activations),
                               "output_activations": None, "format": infer_module_format(s)}
                           for g, s in groups.items()},
-        "ignore": ignore, "kv_cache_scheme": None, "sparsity_config": {}, "transform_config": {},
+        "ignore": ignore, "kv_cache_scheme": args_dict(kv_cache_scheme), "sparsity_config": {}, "transform_config": {},
         "global_compression_ratio": None,
     }
     return state, qconfig

@@ -398,3 +398,73 @@ def test_static_input_activation_scales_fp8_and_nvfp4(tmp_path):
         ref = oracle.generate_gparam(torch.tensor([lo], dtype=torch.bfloat16), torch.tensor([hi], dtype=torch.bfloat16))
         assert torch.equal(m.input_global_scale.data.cpu(), ref), n
         assert not hasattr(m, "input_scale")
+
+
+class _RecordingCache:
+    """Records what an attention module hands to its cache (post-rotary keys, values)."""
+
+    def __init__(self):
+        self.keys, self.values = {}, {}
+
+    def update(self, key_states, value_states, layer_idx, *args, **kwargs):
+        self.keys.setdefault(layer_idx, []).append(key_states.detach().float().cpu())
+        self.values.setdefault(layer_idx, []).append(value_states.detach().float().cpu())
+        return key_states, value_states
+
+
+@pytest.mark.parametrize("with_weights", [False, True])
+def test_kv_cache_scales(tmp_path, with_weights):
+    """``kv_cache_scheme``: FP8 per-tensor static scales of the cached keys and values, from the
+    moving average of each calibration batch's min / max (the ``minmax`` observer), written to the
+    attention modules as k_scale / v_scale and into the checkpoint."""
+    base = tiny_llama(seed=5)
+    data = calib(6, 48)
+    rec = _RecordingCache()
+    attn = [base.model.layers[i].self_attn for i in range(2)]
+    hooks = [a.register_forward_pre_hook(lambda m, args, kwargs: (args, {**kwargs, "past_key_values": rec}),
+                                         with_kwargs=True) for a in attn]
+    with torch.no_grad():
+        for row in data:
+            base(input_ids=row[None].to(DEV), use_cache=False)
+    for h in hooks:
+        h.remove()
+    kv = dict(num_bits=8, type="float", symmetric=True, strategy="tensor", dynamic=False)
+    if with_weights:
+        recipe = QuantizationModifier(targets="Linear", scheme="FP8_DYNAMIC", ignore=["lm_head"], kv_cache_scheme=kv)
+    else:
+        recipe = QuantizationModifier(targets=[], kv_cache_scheme=kv)
+    model = oneshot(copy.deepcopy(base), recipe=recipe, dataset=data, output_dir=str(tmp_path / "kv"))
+    spec = oracle.QSpec(num_bits=8, type="float", symmetric=True, strategy="tensor")
+    for i in range(2):
+        m = model.model.layers[i].self_attn
+        for attr, seen in (("k_scale", rec.keys[i]), ("v_scale", rec.values[i])):
+            mn = mx = None
+            for x in seen:
+                lo, hi = x.min().to(torch.bfloat16), x.max().to(torch.bfloat16)
+                mn, mx = (lo, hi) if mn is None else (torch.lerp(mn, lo, 0.01), torch.lerp(mx, hi, 0.01))
+            scale, _zp = oracle.calculate_qparams(mn.reshape(1), mx.reshape(1), spec)
+            got = float(getattr(m, attr).data.float().cpu())
+            # weights untouched (round to nearest leaves them): same activations, same statistics
+            assert abs(got - float(scale)) <= 2.0 ** -7 * float(scale), (i, attr, got, float(scale))
+        assert not hasattr(m, "k_observer") and not hasattr(m, "k_zero_point")
+        assert m.quantization_status == "frozen"
+    import json
+    from safetensors.torch import load_file
+    sd = load_file(str(tmp_path / "kv" / "model.safetensors"))
+    assert "model.layers.1.self_attn.k_scale" in sd and "model.layers.1.self_attn.v_scale" in sd
+    cfg = json.load(open(tmp_path / "kv" / "config.json"))["quantization_config"]
+    assert cfg["kv_cache_scheme"]["num_bits"] == 8 and cfg["kv_cache_scheme"]["type"] == "float"
+    assert cfg["kv_cache_scheme"]["strategy"] == "tensor" and cfg["kv_cache_scheme"]["dynamic"] is False
+    assert all("self_attn" not in t for g in cfg["config_groups"].values() for t in g["targets"])
+    if with_weights:
+        assert sd["model.layers.0.mlp.up_proj.weight"].dtype == torch.float8_e4m3fn
+
+
+def test_kv_cache_scheme_is_validated():
+    with pytest.raises(NotImplementedError, match="per tensor"):
+        QuantizationModifier(targets="Linear", kv_cache_scheme=dict(num_bits=8, type="float", strategy="channel",
+                                                                     dynamic=False))
+    mod = QuantizationModifier(targets=[], kv_cache_scheme=dict(num_bits=8, type="float", strategy="tensor",
+                                                                dynamic=False))
+    with pytest.raises(ValueError, match="no module matches"):
+        mod.on_initialize(torch.nn.Sequential(torch.nn.Linear(8, 8)))
