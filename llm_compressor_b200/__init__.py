@@ -10,6 +10,7 @@ from .observers import Observer  # noqa: F401
 from .gptq import (accumulate_hessian, make_empty_hessian, quantize_weight,  # noqa: F401
                    factor_hessian, finalize_hessian, accumulate_hessian_lower)
 from .modifiers import GPTQModifier, QuantizationModifier, match_named_modules  # noqa: F401
+from .awq import AWQMapping, AWQModifier  # noqa: F401
 from .oneshot import oneshot, save_compressed_model  # noqa: F401
 from .compressors import compress_state_dict, infer_module_format  # noqa: F401
 from .model_free import model_free_ptq  # noqa: F401

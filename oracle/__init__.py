@@ -40,3 +40,4 @@ from .pack import (  # noqa: F401
 from .observers import flatten_weight, observe_minmax, observe_mse, WeightObserver  # noqa: F401
 from .gptq import (make_empty_hessian, accumulate_hessian, accumulate_hessian_running_mean,  # noqa: F401
                    quantize_weight)
+from . import awq  # noqa: F401,E402

@@ -27,3 +27,11 @@ def sgpt_golden():
 
     path = os.path.join(ROOT, "tests", "golden", "sgpt_hessian.pt")
     return torch.load(path, weights_only=False)
+
+
+@pytest.fixture(scope="session")
+def awq_golden():
+    import torch
+
+    path = os.path.join(ROOT, "tests", "golden", "awq.pt")
+    return torch.load(path, weights_only=False)

@@ -20,7 +20,8 @@ What goes into the file
 
 ``sgpt_hessian.pt`` (a separate small file; ``--sgpt-only`` writes it alone) holds the
 running-mean Hessian of modifiers/pruning/sparsegpt/sgpt_sparsify.py:20-56 after each of three
-calls on seeded activations.
+calls on seeded activations.  ``awq.pt`` (``--awq-only``) holds the AWQ grid search of
+modifiers/transform/awq/base.py on small parent modules: per-candidate losses, chosen scales.
 """
 from __future__ import annotations
 
@@ -316,6 +317,96 @@ def write_sgpt_fixture():
     print("wrote", path, os.path.getsize(path) // 1024, "KiB")
 
 
+def _awq_cases():
+    """Outputs of the reference's ``AWQModifier._compute_best_scale`` (modifiers/transform/awq/base.py:607-763),
+    ``_compute_layer_means`` (:907-973) and ``_get_grid_search_params`` (:802-836), run unmodified on the
+    CPU over small parent modules.  ``accelerate`` is not installed here; the one name the import
+    chain wants from it is provided by a stand-in module."""
+    import importlib
+    import types
+
+    ref_loader.load_reference()
+    if "accelerate" not in sys.modules:
+        acc, acca = types.ModuleType("accelerate"), types.ModuleType("accelerate.accelerator")
+        acca.get_state_dict_offloaded_model = lambda m: m.state_dict()
+        acc.accelerator = acca
+        sys.modules["accelerate"], sys.modules["accelerate.accelerator"] = acc, acca
+    os.environ.setdefault("TQDM_DISABLE", "1")
+    base = importlib.import_module("llmcompressor.modifiers.transform.awq.base")
+    from compressed_tensors.quantization import QuantizationArgs, QuantizationScheme
+    from compressed_tensors.quantization.lifecycle.initialize import initialize_module_for_quantization
+    from llmcompressor.pipelines.cache import IntermediatesCache
+
+    class MLP(torch.nn.Module):
+        def __init__(self, K, N):
+            super().__init__()
+            self.gate_proj = torch.nn.Linear(K, N, bias=False)
+            self.up_proj = torch.nn.Linear(K, N, bias=False)
+
+        def forward(self, x):
+            return torch.nn.functional.silu(self.gate_proj(x)) * self.up_proj(x)
+
+    specs = {
+        "mlp_w4a16_duo": dict(kind="mlp", K=256, N=192, duo=True, n_grid=20, scheme="w4a16_g128"),
+        "mlp_w4asym_both": dict(kind="mlp", K=256, N=160, duo="both", n_grid=12, scheme="w4a16_asym_g128"),
+        "linear_w8channel_noduo": dict(kind="linear", K=192, N=96, duo=False, n_grid=10, scheme="w8a16_channel"),
+        "mlp_nvfp4_duo": dict(kind="mlp", K=128, N=96, duo=True, n_grid=8, scheme="nvfp4"),
+    }
+    cases = {}
+    for name, c in specs.items():
+        g = torch.Generator().manual_seed(len(name) * 131)
+        K, N = c["K"], c["N"]
+        parent = MLP(K, N) if c["kind"] == "mlp" else torch.nn.Linear(K, N, bias=False)
+        parent = parent.to(torch.bfloat16)
+        layers = [parent.gate_proj, parent.up_proj] if c["kind"] == "mlp" else [parent]
+        names = ["blk.mlp.gate_proj", "blk.mlp.up_proj"] if c["kind"] == "mlp" else ["blk.attn.o_proj"]
+        args = _ct_args(SCHEMES[c["scheme"]])
+        for layer in layers:
+            layer.weight.data = (torch.randn(N, K, generator=g) * 0.05 *
+                                 (0.5 + torch.rand(K, generator=g))).to(torch.bfloat16)
+            initialize_module_for_quantization(layer, QuantizationScheme(targets=["Linear"], weights=args))
+            layer.quantization_enabled = False     # as during calibration
+        batches = [(torch.randn(2, 24, K, generator=g) * (0.25 + 2 * torch.rand(K, generator=g))).to(torch.bfloat16)
+                   for _ in range(3)]
+        mod = base.AWQModifier(duo_scaling=c["duo"], n_grid=c["n_grid"])
+        smooth = torch.nn.LayerNorm(K, bias=False)
+        mapping = base.ResolvedMapping("blk.norm", smooth, layers, balance_names=names, parent=parent,
+                                       parent_name="blk.parent", activation_hook_target=None)
+        cache = IntermediatesCache(None, None)
+        key = "x" if c["kind"] == "mlp" else "input"
+        for b in batches:
+            cache.append({key: b})
+        mod._parent_args_cache[parent] = cache
+        x_sum = sum(b.abs().flatten(0, -2).float().sum(0) for b in batches)
+        count = torch.tensor(sum(b.flatten(0, -2).size(0) for b in batches))
+        mod._smooth_activation_stats["blk.norm"] = [x_sum.clone(), count.clone()]
+        losses = []
+        inner = mod._compute_loss
+
+        def recording(a, b, inner=inner, losses=losses):
+            v = inner(a, b)
+            losses.append(v)
+            return v
+        object.__setattr__(mod, "_compute_loss", recording)
+        weights = [layer.weight.data.clone() for layer in layers]
+        with torch.no_grad():
+            fp16 = mod._run_samples(parent)
+            w_mean = base.AWQModifier._compute_layer_means(layers) if c["duo"] is not False else None
+            best = mod._compute_best_scale(mapping, fp16, {layer: layer.weight.clone() for layer in layers})
+        cases[name] = dict(kind=c["kind"], args=_clean_args(args), duo=c["duo"], n_grid=c["n_grid"],
+                           weights=weights, batches=batches, x_sum=x_sum, count=int(count), w_mean=w_mean,
+                           grid=mod._get_grid_search_params(), losses=losses, best_scales=best,
+                           metrics=dict(mod._error_metrics[0]))
+    return cases
+
+
+def write_awq_fixture():
+    assert ref_loader.reference_available(), "set LLMC_REFERENCE_ROOT to the llm-compressor checkout"
+    path = os.path.join(HERE, "awq.pt")
+    torch.save(dict(meta=dict(torch=torch.__version__), cases=_awq_cases()), path)
+    print("wrote", path, os.path.getsize(path) // 1024, "KiB")
+
+
 def main():
     ref = ref_loader.load_reference()
     import compressed_tensors
@@ -336,7 +427,10 @@ def main():
 
 if __name__ == "__main__":
     if "--sgpt-only" in sys.argv:
-        write_sgpt_fixture()     # the small separate fixture, without regenerating golden.pt
+        write_sgpt_fixture()     # the small separate fixtures, without regenerating golden.pt
+    elif "--awq-only" in sys.argv:
+        write_awq_fixture()
     else:
         main()
         write_sgpt_fixture()
+        write_awq_fixture()

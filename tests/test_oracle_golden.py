@@ -170,3 +170,28 @@ def test_rounding_rules_match_torch_casts():
     got = oracle.cast_e2m1(ties)
     assert torch.equal(got, exp)
     assert torch.equal(torch.signbit(got), torch.signbit(exp))
+
+
+# ---------------------------------------------------------------- AWQ
+def awq_parent(case):
+    """``run_parent(weights) -> outputs`` of a fixture case: the parent modules the fixture was made with."""
+    import torch.nn.functional as F
+    if case["kind"] == "mlp":
+        return lambda ws: [F.silu(F.linear(x, ws[0])) * F.linear(x, ws[1]) for x in case["batches"]]
+    return lambda ws: [F.linear(x, ws[0]) for x in case["batches"]]
+
+
+def test_awq_cases(awq_golden):
+    """The oracle's AWQ search against the reference's own ``_compute_best_scale``: the same
+    per-candidate losses and the same chosen scales, bit for bit (both run on the CPU)."""
+    for name, c in awq_golden["cases"].items():
+        spec = spec_from(c["args"])
+        specs = [spec] * len(c["weights"])
+        assert oracle.awq.grid_search_params(c["duo"], c["n_grid"]) == c["grid"], name
+        if c["w_mean"] is not None:
+            assert torch.equal(oracle.awq.layer_means(c["weights"], specs), c["w_mean"]), name
+        best, losses = oracle.awq.best_scale(c["x_sum"], c["count"], c["weights"], specs, awq_parent(c),
+                                             duo_scaling=c["duo"], n_grid=c["n_grid"],
+                                             fused=spec.strategy == "tensor_group")
+        assert losses == c["losses"], name
+        assert best.dtype == c["best_scales"].dtype and torch.equal(best, c["best_scales"]), name
