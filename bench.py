@@ -1094,15 +1094,48 @@ def run_micro(args):
         ms = timed(f, args.steps)
         out["results"].append({"kernel": "gptq_sweep", "N": N, "K": K, "ms": ms,
                                "tflops_fp32": (float(N) * K * K + 128.0 * N * K) / (ms * 1e-3) / 1e12})
+    if args.micro == "small":
+        # the batched kernels for many small problems, on the expert shapes of the MoE configuration:
+        # `count` Hessians of K columns factored by one launch, `count` weights [N, K] swept by one launch
+        K, count = args.micro_k, args.micro_count
+        N = 2048 if K <= 1024 else 768
+        xx = torch.randn(2 * K, K, generator=g, device=dev)
+        H0 = (xx.t() @ xx) / K + 0.01 * torch.eye(K, device=dev)
+        del xx
+        Hs = [H0.clone() for _ in range(count)]
+
+        def ff():
+            for H in Hs:
+                H.copy_(H0)
+            ops.gptq_factor_batched(Hs)
+        ms = timed(ff, args.steps) - timed(lambda: [H.copy_(H0) for H in Hs], args.steps)
+        out["results"].append({"kernel": "gptq_factor_batched", "K": K, "count": count, "ms": ms,
+                               "tflops_fp32": count * (2.0 / 3.0) * K ** 3 / (ms * 1e-3) / 1e12})
+        a8 = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="channel")
+        ws = [(torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16) for _ in range(count)]
+        qp = [ops.qparams(*ops.observe_minmax(w, a8), a8) for w in ws]
+        wfs = [torch.empty(N, K, device=dev) for _ in range(count)]
+
+        def restore():
+            for wf, w in zip(wfs, ws):
+                wf.copy_(w)
+
+        def fs():
+            restore()
+            ops.gptq_sweep_batched(wfs, Hs, [q[0] for q in qp], None, a8)
+        ms = timed(fs, args.steps) - timed(restore, args.steps)
+        out["results"].append({"kernel": "gptq_sweep_batched", "N": N, "K": K, "count": count, "ms": ms,
+                               "tflops_fp32": count * (float(N) * K * K + 128.0 * N * K) / (ms * 1e-3) / 1e12})
     print(json.dumps(out))
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["syrk", "pack", "factor", "sweep", "mse", "all"],
+    ap.add_argument("--micro", default=None, choices=["syrk", "pack", "factor", "sweep", "mse", "small", "all"],
                     help="kernel-level micro benchmark instead of the layer step")
     ap.add_argument("--micro-k", type=int, default=4096)
     ap.add_argument("--micro-t", type=int, default=32768)
+    ap.add_argument("--micro-count", type=int, default=128, help="problems per launch of --micro small")
     ap.add_argument("--workload", default="llama8b", choices=["llama8b", "moe", "70b"],
                     help="llama8b: the headline layer step (configs[2]); moe: one Qwen3-30B-A3B-shaped layer "
                          "(configs[3]); 70b: module-level figures at the Llama-3-70B widths (configs[4])")

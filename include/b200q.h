@@ -292,7 +292,7 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
  * status[i][1] = first bad column + 1 (in reversed column order) when problem i failed.
  *
  * b200q_gptq_sweep_batched: the sweep of b200q_gptq_sweep for `count` weights of one shape
- * [N, K], one quantisation scheme and one scale dtype, blocksize 128.  A thread block carries 128
+ * [N, K], one quantisation scheme and one scale dtype, blocksize 128.  A thread block carries 64
  * rows of one weight through every column block, trailing updates included (float32 FMA).
  * U may be NULL (identity for all) and so may zp, col_group and global_scale (absent for all);
  * losses[i]: float [N]. */

@@ -4,10 +4,11 @@
 // a layer with hundreds of small modules then needs tens of thousands of launches and is bound by
 // the host.  Here one launch serves a whole batch of equally shaped problems, given as device
 // arrays of pointers:
-//   * sweep_fused_kernel: a CTA owns 128 rows of one module through ALL column blocks - the
+//   * sweep_fused_kernel: a CTA owns 64 rows of one module through ALL column blocks - the
 //     128-column block sweep (the lane-per-row scheme of sweep_block_kernel) followed by the
 //     trailing update of those rows, W[rows, after] -= Err * U[block, after], as a float32 FMA
-//     tile product inside the CTA (error panel and the streamed slices of U in shared memory);
+//     tile product inside the CTA (the error panel in shared memory, slices of U streamed in by
+//     asynchronous copies);
 //   * factor_small_kernel (gptq_solve.cu): a CTA factors one small Hessian completely.
 #include "common.cuh"
 
@@ -15,10 +16,11 @@ namespace b200q {
 namespace small {
 
 constexpr int NB = 128;
-constexpr int kRows = 128;                 // rows of a module per CTA (4 row-owning warps)
-constexpr int kThreads = 256;
+constexpr int kRows = 64;                  // rows of a module per CTA (2 row-owning warps)
+constexpr int kThreads = 128;
+constexpr int kSweepWarps = kRows / 32;
 constexpr int kSub = 16;
-constexpr int kWLD = kRows + 1;
+constexpr int kWLD = kRows + 4;            // stride of a column of the block's tile: columns start 16-byte aligned
 constexpr int kColChunk = 64;              // columns of the trailing update per pass
 
 struct SweepBatch {
@@ -30,8 +32,10 @@ struct SweepBatch {
   QRange qr;
 };
 
+// Two CTAs fit one SM (about 100 KB each): while one of them is in its latency-bound sweep phase
+// the other one's trailing update keeps the FMA pipes busy.
 __host__ __device__ constexpr size_t sweep_smem_bytes() {
-  return ((size_t)NB * NB + (size_t)NB * kWLD + (size_t)NB * kRows) * sizeof(float);
+  return ((size_t)NB * NB + (size_t)NB * kWLD) * sizeof(float);
 }
 
 template <bool SB>
@@ -40,13 +44,21 @@ __device__ __noinline__ float quant_one(float wi, float s, float rs, float z, co
   return dequant_code<SB>(q, s, z);
 }
 
+__device__ __forceinline__ void cp_async16(float* dst_smem, const float* src, int src_bytes) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst_smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 template <int SDT, bool GLOBAL>
-__global__ void __launch_bounds__(kThreads, 1) sweep_fused_kernel(SweepBatch b) {
+__global__ void __launch_bounds__(kThreads, 2) sweep_fused_kernel(SweepBatch b) {
   constexpr bool SB = Elem<SDT>::is_bf16 && !GLOBAL;
   extern __shared__ float sm[];
-  float* sU = sm;                          // [128][128] diagonal block, later [128][64] slices of U
-  float* sW = sU + NB * NB;                // [128 cols][kWLD]: the block's columns of this CTA's rows
-  float* sErrT = sW + NB * kWLD;           // [128 cols][128 rows]: scaled errors of the block
+  float* sU = sm;                          // [128][128] diagonal block; during the trailing update two [128][64] slices of U
+  float* sW = sU + NB * NB;                // [128 cols][kWLD]: the block's columns of this CTA's rows, then their errors
   __shared__ float s_rd[NB];
   __shared__ int s_grp[NB];
   const int job = blockIdx.y;
@@ -59,10 +71,13 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_fused_kernel(SweepBatch b) 
   const bool has_zp = zp != nullptr;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row_base = (int64_t)blockIdx.x * kRows;
-  const int64_t row = row_base + warp * 32 + lane;          // meaningful for warps 0..3
-  const bool live = warp < 4 && row < b.N;
+  const int64_t row = row_base + warp * 32 + lane;          // meaningful for the sweeping warps
+  const bool sweeper = warp < kSweepWarps;
+  const bool live = sweeper && row < b.N;
+  const bool vecw = ((b.ldw & 3) == 0) && ((((uintptr_t)W) & 15) == 0);
+  const bool vecu = U && ((b.ldu & 3) == 0) && ((((uintptr_t)U) & 15) == 0);
   int64_t pbase = 0;
-  if (warp < 4) {
+  if (sweeper) {
     switch (b.strategy) {
       case B200Q_TENSOR: pbase = 0; break;
       case B200Q_CHANNEL: pbase = row; break;
@@ -75,6 +90,7 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_fused_kernel(SweepBatch b) 
     const int bs = (int)((b.K - i1) < NB ? (b.K - i1) : NB);
     const int64_t i2 = i1 + bs;
     // ---- diagonal block of U, reciprocal pivots, parameter column of every column
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < NB * NB / 4; idx += kThreads) {
       const int r = idx >> 5, c = (idx & 31) << 2;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -84,10 +100,14 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_fused_kernel(SweepBatch b) 
           v.z = (r == c + 2) ? 1.0f : 0.0f; v.w = (r == c + 3) ? 1.0f : 0.0f;
         } else {
           const float* src = U + (i1 + r) * b.ldu + (i1 + c);
-          if (c < bs) v.x = src[0];
-          if (c + 1 < bs) v.y = src[1];
-          if (c + 2 < bs) v.z = src[2];
-          if (c + 3 < bs) v.w = src[3];
+          if (vecu && c + 3 < bs) {
+            v = *reinterpret_cast<const float4*>(src);
+          } else {
+            if (c < bs) v.x = src[0];
+            if (c + 1 < bs) v.y = src[1];
+            if (c + 2 < bs) v.z = src[2];
+            if (c + 3 < bs) v.w = src[3];
+          }
         }
       }
       *reinterpret_cast<float4*>(sU + idx * 4) = v;
@@ -105,22 +125,28 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_fused_kernel(SweepBatch b) 
       s_grp[i] = grp;
     }
     __syncthreads();
-    // ---- the block's columns, swept by the four row-owning warps
-    if (warp < 4) {
+    // ---- the block's columns, swept by the row-owning warps (a lane per row)
+    if (sweeper) {
       float* myW = sW + warp * 32;
-      const int64_t row0 = row_base + warp * 32;
-#pragma unroll 4
-      for (int r = 0; r < 32; ++r) {
-        const int64_t rr = row0 + r;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int c = lane + 32 * k;
-          float v = 0.0f;
-          if (rr < b.N && c < bs) v = W[rr * b.ldw + i1 + c];
-          myW[c * kWLD + r] = v;
+      {
+        const float* src = W + row * b.ldw + i1;
+#pragma unroll 8
+        for (int c = 0; c < NB; c += 4) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (live) {
+            if (vecw && c + 3 < bs) {
+              v = *reinterpret_cast<const float4*>(src + c);
+            } else {
+              if (c < bs) v.x = src[c];
+              if (c + 1 < bs) v.y = src[c + 1];
+              if (c + 2 < bs) v.z = src[c + 2];
+              if (c + 3 < bs) v.w = src[c + 3];
+            }
+          }
+          myW[(c + 0) * kWLD + lane] = v.x; myW[(c + 1) * kWLD + lane] = v.y;
+          myW[(c + 2) * kWLD + lane] = v.z; myW[(c + 3) * kWLD + lane] = v.w;
         }
       }
-      __syncwarp();
       int cur_grp = -1;
       float s = 1.0f, z = 0.0f, rs = 1.0f;
 #pragma unroll 1
@@ -163,12 +189,22 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_fused_kernel(SweepBatch b) 
             }
           }
         }
+        // the sub-block's columns are final: out to the weight, and their errors take their
+        // place in the tile for the trailing update
+        if (live) {
+          float* dst = W + row * b.ldw + i1 + c0;
+          if (vecw && c0 + kSub <= bs) {
 #pragma unroll
-        for (int t = 0; t < kSub; ++t) {
-          myW[(c0 + t) * kWLD + lane] = w[t];
-          sErrT[(c0 + t) * kRows + warp * 32 + lane] = e[t];
+            for (int t = 0; t < kSub; t += 4)
+              *reinterpret_cast<float4*>(dst + t) = make_float4(w[t], w[t + 1], w[t + 2], w[t + 3]);
+          } else {
+#pragma unroll
+            for (int t = 0; t < kSub; ++t)
+              if (c0 + t < bs) dst[t] = w[t];
+          }
         }
-        __syncwarp();
+#pragma unroll
+        for (int t = 0; t < kSub; ++t) myW[(c0 + t) * kWLD + lane] = e[t];
 #pragma unroll 1
         for (int c = c0 + kSub; c < bs; c += 4) {
           float v0 = myW[(c + 0) * kWLD + lane], v1 = myW[(c + 1) * kWLD + lane];
@@ -185,50 +221,81 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_fused_kernel(SweepBatch b) 
           myW[(c + 2) * kWLD + lane] = v2; myW[(c + 3) * kWLD + lane] = v3;
         }
       }
-      __syncwarp();
-      for (int r = 0; r < 32; ++r) {
-        const int64_t rr = row0 + r;
-        if (rr >= b.N) break;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int c = lane + 32 * k;
-          if (c < bs) W[rr * b.ldw + i1 + c] = myW[c * kWLD + r];
-        }
-      }
     }
     __syncthreads();
-    // ---- trailing update of this CTA's rows: W[rows, i2:] -= Err[rows, bs] * U[i1:i2, i2:]
+    // ---- trailing update of this CTA's rows: W[rows, i2:] -= Err[rows, bs] * U[i1:i2, i2:],
+    // 64 columns at a time; the slices of U arrive by asynchronous copies, one slice ahead
     if (U && i2 < b.K) {
-      const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;     // 16 x 16 threads, 8 rows x 4 columns each
-      float* sUc = sU;                                            // [128][64]
-      for (int64_t j0 = i2; j0 < b.K; j0 += kColChunk) {
+      const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;     // 8 x 16 threads, 8 rows x 4 columns each
+      const float* sErr = sW;                                     // [k][kWLD]
+      const int nchunks = (int)((b.K - i2 + kColChunk - 1) / kColChunk);
+      auto stage = [&](int chunk) {
+        float* buf = sU + (chunk & 1) * (NB * kColChunk);
+        const int64_t j0 = i2 + (int64_t)chunk * kColChunk;
+#pragma unroll 4
         for (int idx = threadIdx.x; idx < NB * kColChunk / 4; idx += kThreads) {
           const int k = idx >> 4, c = (idx & 15) << 2;
-          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (k < bs) {
-            const float* src = U + (i1 + k) * b.ldu + j0 + c;
-            if (j0 + c + 3 < b.K && ((b.ldu & 3) == 0) && ((((uintptr_t)U) & 15) == 0) && (((j0 + c) & 3) == 0)) {
-              v = *reinterpret_cast<const float4*>(src);
-            } else {
-              if (j0 + c < b.K) v.x = src[0];
-              if (j0 + c + 1 < b.K) v.y = src[1];
-              if (j0 + c + 2 < b.K) v.z = src[2];
-              if (j0 + c + 3 < b.K) v.w = src[3];
+          float* dst = buf + k * kColChunk + c;
+          const int64_t col = j0 + c;
+          if (vecu) {
+            int bytes = 0;
+            if (k < bs && col < b.K) bytes = (b.K - col) >= 4 ? 16 : (int)(b.K - col) * 4;
+            cp_async16(dst, bytes ? U + (i1 + k) * b.ldu + col : U, bytes);
+          } else {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k < bs) {
+              const float* src = U + (i1 + k) * b.ldu + col;
+              if (col < b.K) v.x = src[0];
+              if (col + 1 < b.K) v.y = src[1];
+              if (col + 2 < b.K) v.z = src[2];
+              if (col + 3 < b.K) v.w = src[3];
             }
+            *reinterpret_cast<float4*>(dst) = v;
           }
-          *reinterpret_cast<float4*>(sUc + k * kColChunk + c) = v;
+        }
+        cp_async_commit();
+      };
+      stage(0);
+      for (int chunk = 0; chunk < nchunks; ++chunk) {
+        if (chunk + 1 < nchunks) {
+          stage(chunk + 1);
+          cp_async_wait<1>();
+        } else {
+          cp_async_wait<0>();
         }
         __syncthreads();
+        const float* buf = sU + (chunk & 1) * (NB * kColChunk);
+        const int64_t j0 = i2 + (int64_t)chunk * kColChunk;
+        const int64_t col = j0 + tx * 4;
+        const bool whole = vecw && col + 3 < b.K;
+        // this thread's part of W, on its way while the products are formed
+        float4 wv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int64_t rr = row_base + ty * 8 + i;
+          wv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (rr < b.N) {
+            const float* src = W + rr * b.ldw + col;
+            if (whole) {
+              wv[i] = *reinterpret_cast<const float4*>(src);
+            } else {
+              if (col < b.K) wv[i].x = src[0];
+              if (col + 1 < b.K) wv[i].y = src[1];
+              if (col + 2 < b.K) wv[i].z = src[2];
+              if (col + 3 < b.K) wv[i].w = src[3];
+            }
+          }
+        }
         float acc[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
         for (int k = 0; k < bs; ++k) {
-          const float4 a0 = *reinterpret_cast<const float4*>(sErrT + k * kRows + ty * 8);
-          const float4 a1 = *reinterpret_cast<const float4*>(sErrT + k * kRows + ty * 8 + 4);
-          const float4 u = *reinterpret_cast<const float4*>(sUc + k * kColChunk + tx * 4);
+          const float4 a0 = *reinterpret_cast<const float4*>(sErr + k * kWLD + ty * 8);
+          const float4 a1 = *reinterpret_cast<const float4*>(sErr + k * kWLD + ty * 8 + 4);
+          const float4 u = *reinterpret_cast<const float4*>(buf + k * kColChunk + tx * 4);
           const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -240,10 +307,17 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_fused_kernel(SweepBatch b) 
         for (int i = 0; i < 8; ++i) {
           const int64_t rr = row_base + ty * 8 + i;
           if (rr >= b.N) continue;
-          float* dst = W + rr * b.ldw + j0 + tx * 4;
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj)
-            if (j0 + tx * 4 + jj < b.K) dst[jj] = __fsub_rn(dst[jj], acc[i][jj]);
+          float* dst = W + rr * b.ldw + col;
+          const float4 r = make_float4(__fsub_rn(wv[i].x, acc[i][0]), __fsub_rn(wv[i].y, acc[i][1]),
+                                       __fsub_rn(wv[i].z, acc[i][2]), __fsub_rn(wv[i].w, acc[i][3]));
+          if (whole) {
+            *reinterpret_cast<float4*>(dst) = r;
+          } else {
+            if (col < b.K) dst[0] = r.x;
+            if (col + 1 < b.K) dst[1] = r.y;
+            if (col + 2 < b.K) dst[2] = r.z;
+            if (col + 3 < b.K) dst[3] = r.w;
+          }
         }
         __syncthreads();
       }
