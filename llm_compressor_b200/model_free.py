@@ -154,16 +154,26 @@ def _is_weight_candidate(name: str, t: torch.Tensor) -> bool:
 
 
 def process_shard(tensors: Dict[str, torch.Tensor], scheme, ignore: Iterable[str],
-                  own: Optional[set] = None, run: Optional[Callable] = None):
+                  own: Optional[set] = None, run: Optional[Callable] = None, converter=None):
     """Quantise and compress the selected weights among ``tensors`` (already on the device).
     ``scheme``: one QuantizationScheme or ``{group name: QuantizationScheme}``.
     ``own``: names to keep in the result (default all); the others were only loaded as fused
     partners.  Returns ``(state_dict on cpu, quantization_config or None)``.
 
-    ``run(model, modifier)`` drives the modifier (default: its data-free life cycle)."""
+    ``run(model, modifier)`` drives the modifier (default: its data-free life cycle).
+    ``converter``: see ``model_free_ptq``; applied after fused expert tensors have been split
+    (process.py:107-112)."""
     from .oneshot import _run_data_free, compressed_state_dict
 
     tensors = split_fused_moe_experts(tensors)
+    if converter is not None:
+        before = set(tensors)
+        if hasattr(converter, "validate"):
+            converter.validate(tensors)
+        converted = converter.process(tensors)
+        tensors = tensors if converted is None else converted     # in place, or a new dict
+        if own is not None:   # renamed or new tensors belong to this shard
+            own = set(own) | (set(tensors) - before)
     weights = {n: t for n, t in tensors.items() if _is_weight_candidate(n, t)}
     model = build_module_tree(weights)
     groups = dict(scheme) if isinstance(scheme, dict) else {"group_0": scheme}
@@ -186,6 +196,31 @@ def process_shard(tensors: Dict[str, torch.Tensor], scheme, ignore: Iterable[str
         state = {k: v for k, v in state.items()
                  if k in keep or k.rpartition(".")[0] in keep}
     return state, (qconfig if quantised else None)
+
+
+def _merge_configs(existing, new: Optional[dict]) -> Optional[dict]:
+    """The converter's quantization config with this run's config groups appended and the ignore
+    lists united; the format becomes "mixed-precision" when the two differ."""
+    if existing is None:
+        return new
+    if hasattr(existing, "model_dump"):
+        existing = existing.model_dump(mode="json")
+    merged = dict(existing)
+    merged.setdefault("quant_method", "compressed-tensors")
+    if new is None:
+        return merged
+    groups = dict(merged.get("config_groups") or {})
+    for name, g in new["config_groups"].items():
+        key = name
+        while key in groups:
+            key = f"{key}_ptq"
+        groups[key] = g
+    merged["config_groups"] = groups
+    merged["ignore"] = sorted(set(merged.get("ignore") or []) | set(new.get("ignore") or []))
+    if merged.get("format") != new.get("format"):
+        merged["format"] = "mixed-precision"
+    merged["quantization_status"] = "compressed"
+    return merged
 
 
 def _weight_map(model_dir: str) -> Dict[str, str]:
@@ -213,12 +248,14 @@ def model_free_ptq(model_stub, save_directory, scheme=None, config=None, ignore:
     object with those attributes (a compressed-tensors ``QuantizationConfig``); the first group
     whose targets select a module applies to it.  ``ignore``: module names / ``re:`` patterns left
     alone (names ending in "norm" always are); ``device``: one device or a list (default: every
-    visible GPU).  Checkpoint converters are not supported."""
+    visible GPU).  ``converter``: an object with ``process(tensors)`` (in place, or returning the new
+    dict), optionally ``validate(tensors)`` and ``create_config()`` (compressed-tensors'
+    ``Converter`` protocol): it turns a checkpoint of another format into the compressed-tensors
+    layout shard by shard before the remaining floating-point weights are quantised, and its
+    config is the starting point that this run's groups are appended to (save_utils.py:64-125)."""
     from safetensors import safe_open
     from safetensors.torch import load_file, save_file
 
-    if converter is not None:
-        raise NotImplementedError("checkpoint converters are outside this package's path")
     if (scheme is None) == (config is None):
         raise ValueError("Please specify either `config` or `scheme`")
     if not os.path.isdir(model_stub):
@@ -265,7 +302,8 @@ def model_free_ptq(model_stub, save_directory, scheme=None, config=None, ignore:
             for name, src in partners.get(shard, {}).items():
                 with safe_open(os.path.join(model_stub, src), framework="pt", device=str(dev)) as f:
                     tensors[name] = f.get_tensor(name)
-            state, qconfig = process_shard(tensors, scheme, ignore, own=own if partners.get(shard) else None)
+            state, qconfig = process_shard(tensors, scheme, ignore, own=own if partners.get(shard) else None,
+                                           converter=converter)
             save_file(state, os.path.join(save_directory, shard), metadata={"format": "pt"})
         return shard, {k: shard for k in state}, sum(v.numel() * v.element_size() for v in state.values()), qconfig
 
@@ -283,6 +321,9 @@ def model_free_ptq(model_stub, save_directory, scheme=None, config=None, ignore:
                 qconfig = qc
     if qconfig is not None:
         qconfig["ignore"] = sorted(set(ignored))
+    if converter is not None and hasattr(converter, "create_config"):
+        qconfig = _merge_configs(converter.create_config(), qconfig)
+    if qconfig is not None:
         cfg_path = os.path.join(save_directory, "config.json")
         cfg = {}
         if os.path.exists(cfg_path):

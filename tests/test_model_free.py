@@ -189,3 +189,81 @@ def test_model_free_against_the_oracle_and_with_two_groups(tmp_path):
     assert checked == 14
     qc = json.loads((out / "config.json").read_text())["quantization_config"]
     assert len(qc["config_groups"]) == 2 and qc["format"] == "mixed-precision" and "version" in qc
+
+
+class _RenamingConverter:
+    """A converter in the shape of compressed-tensors' ``Converter`` protocol: the source checkpoint
+    calls its tensors ``transformer.*`` and holds the attention projections already compressed in a
+    foreign layout (``.qweight`` int8 + ``.scales``), which become ``weight`` / ``weight_scale``."""
+
+    def __init__(self):
+        self.validated = 0
+
+    def validate(self, tensors):
+        self.validated += 1
+        if not any(k.startswith("transformer.") for k in tensors):
+            raise ValueError("not a checkpoint of the foreign format")
+
+    def process(self, tensors):
+        out = {}
+        for k, v in tensors.items():
+            k = k.replace("transformer.", "", 1)
+            if k.endswith(".qweight"):
+                k = k[: -len(".qweight")] + ".weight"
+            elif k.endswith(".scales"):
+                k = k[: -len(".scales")] + ".weight_scale"
+            out[k] = v
+        return out
+
+    def create_config(self):
+        return {"quant_method": "compressed-tensors", "format": "int-quantized", "quantization_status": "compressed",
+                "config_groups": {"group_0": {"targets": ["re:.*self_attn\\..*_proj"], "format": "int-quantized",
+                                              "weights": {"num_bits": 8, "type": "int", "symmetric": True,
+                                                          "strategy": "channel"}}},
+                "ignore": ["lm_head"], "kv_cache_scheme": None}
+
+
+@pytest.mark.gpu
+def test_model_free_with_a_converter(tmp_path):
+    from safetensors.torch import load_file, save_file
+
+    import oracle
+
+    torch.manual_seed(4)
+    model = _Model(layers=1).to(torch.bfloat16)
+    sd = {}
+    for k, v in model.state_dict().items():
+        if "self_attn" in k:     # "already compressed" by the foreign tool
+            base = k[: -len(".weight")]
+            scale = (v.float().abs().amax(dim=1, keepdim=True) / 127).to(torch.bfloat16)
+            sd[f"transformer.{base}.qweight"] = torch.round(v.float() / scale.float()).clamp(-128, 127).to(torch.int8)
+            sd[f"transformer.{base}.scales"] = scale
+        else:
+            sd[f"transformer.{k}"] = v.detach().clone()
+    src, out = tmp_path / "src", tmp_path / "out"
+    src.mkdir()
+    save_file(sd, str(src / "model.safetensors"))
+    (src / "config.json").write_text(json.dumps({"model_type": "toy"}))
+    conv = _RenamingConverter()
+    mf.model_free_ptq(str(src), str(out), scheme="FP8_DYNAMIC", ignore=["lm_head"], device="cuda:0", converter=conv)
+    assert conv.validated == 1
+    got = load_file(str(out / "model.safetensors"))
+    assert not any(k.startswith("transformer.") for k in got)
+    # converted tensors pass through under their new names, untouched
+    q = "layers.0.self_attn.q_proj"
+    assert torch.equal(got[f"{q}.weight"], sd[f"transformer.{q}.qweight"])
+    assert torch.equal(got[f"{q}.weight_scale"], sd[f"transformer.{q}.scales"])
+    # the floating-point weights that were left are quantised by this run, as the oracle does it
+    spec = oracle.preset("FP8_DYNAMIC")
+    w = sd["transformer.layers.0.mlp.down_proj.weight"]
+    qp = oracle.WeightObserver(spec)(w).get_qparams()
+    ref = oracle.compress_weight({"weight": w, "weight_scale": qp["scale"].to(w.dtype),
+                                  "weight_zero_point": qp["zero_point"]}, spec, fmt="float-quantized")
+    for k, v in ref.items():
+        g = got[f"layers.0.mlp.down_proj.{k}"]
+        assert g.dtype == v.dtype and torch.equal(g.view(torch.uint8), v.view(torch.uint8)), k
+    assert torch.equal(got["lm_head.weight"], sd["transformer.lm_head.weight"])
+    qc = json.loads((out / "config.json").read_text())["quantization_config"]
+    assert set(qc["config_groups"]) == {"group_0", "group_0_ptq"} and qc["format"] == "mixed-precision"
+    assert qc["config_groups"]["group_0"]["weights"]["num_bits"] == 8
+    assert "lm_head" in qc["ignore"] and "version" in qc
