@@ -91,14 +91,57 @@ def _as_broadcastable(t: torch.Tensor) -> torch.Tensor:
     return t.view(torch.uint8) if t.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else t
 
 
+_BUCKET_BYTES = 256 << 20     # parameters of one owner travel in buckets of at most this size
+
+
 def broadcast_module_params(modules: Sequence, module_to_rank: dict, names: Sequence[str]) -> None:
-    """Broadcast the named parameters of every module from its owner."""
-    pending = []
+    """Broadcast the named parameters of every module from its owner.  The parameters of one
+    owner are packed into byte buckets (one collective per bucket instead of one per tensor: a
+    layer of a mixture of experts has more than a thousand small tensors); a tensor larger than a
+    bucket, or not contiguous, goes by itself."""
+    me = rank()
+    by_src: dict = {}
     for m in modules:
         src = module_to_rank[m]
         for name in names:
             p = getattr(m, name, None)
-            if p is None:
+            if p is not None:
+                by_src.setdefault(src, []).append(p.data)
+    pending, unpack = [], []
+    for src in sorted(by_src):
+        bucket, size = [], 0
+
+        def flush():
+            nonlocal bucket, size
+            if not bucket:
+                return
+            if len(bucket) == 1:
+                pending.append(dist.broadcast(_as_broadcastable(bucket[0]), src=src, async_op=True))
+            else:
+                offsets, total = [], 0
+                for t in bucket:
+                    offsets.append(total)
+                    total += (t.numel() * t.element_size() + 15) // 16 * 16
+                buf = torch.empty(total, dtype=torch.uint8, device=bucket[0].device)
+                views = [buf[o: o + t.numel() * t.element_size()] for o, t in zip(offsets, bucket)]
+                if me == src:
+                    torch._foreach_copy_(views, [t.reshape(-1).view(torch.uint8) for t in bucket])
+                pending.append(dist.broadcast(buf, src=src, async_op=True))
+                if me != src:
+                    unpack.append((bucket, views))
+            bucket, size = [], 0
+
+        for t in by_src[src]:
+            nbytes = t.numel() * t.element_size()
+            if not t.is_contiguous() or nbytes > _BUCKET_BYTES or nbytes == 0:
+                if nbytes:
+                    pending.append(dist.broadcast(_as_broadcastable(t), src=src, async_op=True))
                 continue
-            pending.append(dist.broadcast(_as_broadcastable(p.data), src=src, async_op=True))
+            if size + nbytes > _BUCKET_BYTES:
+                flush()
+            bucket.append(t)
+            size += nbytes
+        flush()
     wait_for_comms(pending)
+    for tensors, views in unpack:
+        torch._foreach_copy_([t.reshape(-1).view(torch.uint8) for t in tensors], views)
