@@ -460,6 +460,37 @@ def test_kv_cache_scales(tmp_path, with_weights):
         assert sd["model.layers.0.mlp.up_proj.weight"].dtype == torch.float8_e4m3fn
 
 
+def test_kv_cache_scales_with_gptq():
+    """The same calibration inside a GPTQ run: layer 0 sees unquantised inputs, so its scales are
+    those of the plain model; later layers are calibrated on the quantised prefix."""
+    base = tiny_llama(seed=6)
+    data = calib(6, 48)
+    rec = _RecordingCache()
+    attn = base.model.layers[0].self_attn
+    h = attn.register_forward_pre_hook(lambda m, args, kwargs: (args, {**kwargs, "past_key_values": rec}),
+                                       with_kwargs=True)
+    with torch.no_grad():
+        for row in data:
+            base(input_ids=row[None].to(DEV), use_cache=False)
+    h.remove()
+    kv = dict(num_bits=8, type="float", symmetric=True, strategy="tensor", dynamic=False)
+    recipe = GPTQModifier(targets="Linear", scheme="W4A16", ignore=["lm_head"], kv_cache_scheme=kv)
+    model = oneshot(copy.deepcopy(base), recipe=recipe, dataset=data)
+    spec = oracle.QSpec(num_bits=8, type="float", symmetric=True, strategy="tensor")
+    m = model.model.layers[0].self_attn
+    for attr, seen in (("k_scale", rec.keys[0]), ("v_scale", rec.values[0])):
+        mn = mx = None
+        for x in seen:
+            lo, hi = x.min().to(torch.bfloat16), x.max().to(torch.bfloat16)
+            mn, mx = (lo, hi) if mn is None else (torch.lerp(mn, lo, 0.01), torch.lerp(mx, hi, 0.01))
+        scale, _zp = oracle.calculate_qparams(mn.reshape(1), mx.reshape(1), spec)
+        got = float(getattr(m, attr).data.float().cpu())
+        assert abs(got - float(scale)) <= 2.0 ** -7 * float(scale), (attr, got, float(scale))
+    last = model.model.layers[1].self_attn
+    assert float(last.k_scale) > 0 and float(last.v_scale) > 0 and last.quantization_status == "frozen"
+    assert model.model.layers[1].mlp.down_proj.quantization_status == "frozen"
+
+
 def test_kv_cache_scheme_is_validated():
     with pytest.raises(NotImplementedError, match="per tensor"):
         QuantizationModifier(targets="Linear", kv_cache_scheme=dict(num_bits=8, type="float", strategy="channel",
