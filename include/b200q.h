@@ -209,6 +209,14 @@ int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* 
  * src/modifiers/gptq/base.py:336 (H / num_samples) is scale = 1/n. */
 int b200q_hessian_finalize(float* H, int64_t K, int64_t ldh, float scale, void* stream);
 
+/* b200q_hessian_syrk splits long token ranges over several thread blocks per tile and adds the
+ * partial tiles with floating-point atomics: H is then reproducible to rounding error (about 1e-7
+ * relative), not bit for bit, and a GPTQ solve on it may differ in a few codes from run to run.
+ * b200q_set_reproducible(1) makes every later call accumulate each tile in one place (bitwise
+ * reproducible results for equal inputs and call sequences; slower for narrow Hessians).  Process-wide. */
+void b200q_set_reproducible(int on);
+int b200q_get_reproducible(void);
+
 /* ------------------------------------------------------------------ GPTQ: solve */
 
 /* perm = stable argsort(diag(H), descending)  (gptq_quantize.py:267-278). */

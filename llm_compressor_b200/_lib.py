@@ -65,6 +65,8 @@ SIGNATURES = {
     "b200q_nvfp4_quantize_pack": (_i, [_p, _i, _i64, _i64, _i64, _p, _p, _p, _p, _p]),
     "b200q_hessian_syrk": (_i, [_p, _i64, _i64, _i64, _p, _i64, _f, _p, _p]),
     "b200q_hessian_finalize": (_i, [_p, _i64, _i64, _f, _p]),
+    "b200q_set_reproducible": (None, [_i]),
+    "b200q_get_reproducible": (_i, []),
     "b200q_actorder_perm": (_i, [_p, _i64, _i64, _p, _p]),
     "b200q_gather_columns_f32": (_i, [_p, _i, _i64, _i64, _i64, _p, _p, _i64, _p]),
     "b200q_permute_hessian": (_i, [_p, _i64, _i64, _p, _p, _i64, _p]),

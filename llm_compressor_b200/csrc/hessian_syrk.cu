@@ -24,6 +24,8 @@
 #include <cstdlib>
 #include <mutex>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace b200q {
@@ -740,6 +742,11 @@ static int pair_capacity() {
 
 using namespace b200q;
 
+// Token splits add their partial tiles with floating-point atomics, whose order varies from run to
+// run (H then differs in its last bits).  With this flag set every tile is accumulated by one CTA
+// (pair) over all tokens: bitwise reproducible, slower when the tiles alone do not fill the GPU.
+static std::atomic<int> g_reproducible{0};
+
 extern "C" {
 
 int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* H, int64_t ldh,
@@ -780,7 +787,7 @@ int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* 
       const double eff = (double)units / (double)(waves * pairs);
       if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
     }
-    p.splits = best;
+    p.splits = g_reproducible.load(std::memory_order_relaxed) ? 1 : best;
     const int64_t tps = (T + p.splits - 1) / p.splits;
     p.tokens_per_split = ((tps + kBlockT - 1) / kBlockT) * kBlockT;
     const int64_t units = (int64_t)p.tiles * p.splits;
@@ -813,7 +820,7 @@ int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* 
     // prefer fewer splits unless the gain is real (atomics + epilogues are not free)
     if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
   }
-  p.splits = best;
+  p.splits = g_reproducible.load(std::memory_order_relaxed) ? 1 : best;
   int64_t tps = (T + p.splits - 1) / p.splits;
   p.tokens_per_split = ((tps + kBlockT - 1) / kBlockT) * kBlockT;
 
@@ -824,6 +831,9 @@ int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* 
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
+
+void b200q_set_reproducible(int on) { g_reproducible.store(on ? 1 : 0, std::memory_order_relaxed); }
+int b200q_get_reproducible(void) { return g_reproducible.load(std::memory_order_relaxed); }
 
 int b200q_hessian_finalize(float* H, int64_t K, int64_t ldh, float scale, void* stream) {
   if (!H || K <= 0 || ldh < K) return B200Q_ERR_ARG;

@@ -106,14 +106,104 @@ class _PhaseClock:
         self.t = now
 
 
-def _run_sequential(model, modifiers, batches, sequential_targets, phase_times=None):
+def _tree_map(fn, obj):
+    if isinstance(obj, torch.Tensor):
+        return fn(obj)
+    if isinstance(obj, tuple):
+        return tuple(_tree_map(fn, o) for o in obj)
+    if isinstance(obj, list):
+        return [_tree_map(fn, o) for o in obj]
+    if isinstance(obj, dict):
+        return {k: _tree_map(fn, v) for k, v in obj.items()}
+    return obj
+
+
+class _ActivationStore:
+    """The inputs of the current sequential block, one ``(args, kwargs)`` per calibration batch.
+
+    By default everything stays in device memory (a whole calibration set of hidden states is a few
+    GB against 180 GB of HBM).  With ``offload`` (a device, e.g. "cpu") tensors of at least 1 MiB
+    are parked there between uses - in pinned memory when it is the host - and brought back per
+    batch; with ``prefetch`` the next batch is fetched on a copy stream while the current one runs
+    (src/llmcompressor/pipelines/cache.py:244-375, pipelines/sequential/pipeline.py:28-47)."""
+
+    _MIN_BYTES = 1 << 20
+
+    def __init__(self, device, offload=None, prefetch: bool = False):
+        self.device = torch.device(device)
+        self.offload = None if offload is None else torch.device(offload)
+        if self.offload is not None and self.offload == self.device:
+            self.offload = None
+        self.prefetch = bool(prefetch) and self.offload is not None and self.device.type == "cuda"
+        self.items: list = []
+        self._copy_stream = torch.cuda.Stream(device=self.device) if self.prefetch else None
+
+    def __len__(self):
+        return len(self.items)
+
+    def _park(self, t: torch.Tensor) -> torch.Tensor:
+        if self.offload is None or t.device != self.device or t.numel() * t.element_size() < self._MIN_BYTES:
+            return t
+        if self.offload.type == "cpu" and t.is_cuda:
+            out = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+            out.copy_(t, non_blocking=True)
+            return out
+        return t.to(self.offload)
+
+    def append(self, value) -> None:
+        self.items.append(_tree_map(self._park, value))
+
+    def settle(self) -> None:
+        """Wait for the copies of ``append`` (the parked host buffers are read only after this)."""
+        if self.offload is not None and self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).synchronize()
+
+    def _fetch(self, i: int):
+        return _tree_map(lambda t: t.to(self.device, non_blocking=True) if t.device != self.device else t,
+                         self.items[i])
+
+    def batches(self, release: bool = False):
+        """Yield every batch on the device, in order; ``release`` drops a batch once it has been
+        handed out (its block is done with it)."""
+        n = len(self.items)
+        if not self.prefetch:
+            for i in range(n):
+                value = self._fetch(i)
+                if release:
+                    self.items[i] = None
+                yield value
+            return
+        current = torch.cuda.current_stream(self.device)
+
+        def start(i):
+            self._copy_stream.wait_stream(current)
+            with torch.cuda.stream(self._copy_stream):
+                value = self._fetch(i)
+            done = torch.cuda.Event()
+            done.record(self._copy_stream)
+            return value, done
+
+        nxt = start(0) if n else None
+        for i in range(n):
+            value, done = nxt
+            nxt = start(i + 1) if i + 1 < n else None
+            current.wait_event(done)
+            _tree_map(lambda t: t.record_stream(current) if t.is_cuda else None, value)
+            if release:
+                self.items[i] = None
+            yield value
+
+
+def _run_sequential(model, modifiers, batches, sequential_targets, phase_times=None, offload_device=None,
+                    prefetch: bool = False, propagate_error: bool = True):
     clock = _PhaseClock(phase_times)
     layers = _sequential_layers(model, sequential_targets)
     first = layers[0][1]
-    captured = []
+    device = next(model.parameters()).device
+    store = _ActivationStore(device, offload_device, prefetch)
 
     def grab(_m, args, kwargs):
-        captured.append((args, kwargs))
+        store.append((args, kwargs))
         raise _StopForward()
 
     handle = first.register_forward_pre_hook(grab, with_kwargs=True)
@@ -131,28 +221,36 @@ def _run_sequential(model, modifiers, batches, sequential_targets, phase_times=N
         handle.remove()
         if use_cache is not None:
             model.config.use_cache = use_cache
+    store.settle()
     for m in modifiers:
         m.on_calibration_start(model)
     clock.mark("capture")
     for _name, layer in layers:
+        nxt = _ActivationStore(device, offload_device, prefetch)
         with torch.no_grad():
-            for args, kwargs in captured:  # calibration pass: hooks fire
-                layer(*args, **kwargs)
+            # calibration pass: hooks fire.  Without error propagation its outputs (those of the
+            # block before it is quantised) are the next block's inputs and there is no second pass
+            for args, kwargs in store.batches(release=not propagate_error):
+                out = layer(*args, **kwargs)
+                if not propagate_error:
+                    nxt.append(_with_hidden(args, kwargs, out[0] if isinstance(out, (tuple, list)) else out))
+                del out
         clock.mark("calibrate")
         members = list(layer.modules())
         for m in modifiers:
             m.on_sequential_epoch_end(model, members)
         clock.mark("compress")
-        nxt = []
-        with torch.no_grad(), HooksMixin.disable_hooks():
-            for i, (args, kwargs) in enumerate(captured):  # propagation pass with the quantised weights
-                out = layer(*args, **kwargs)
-                hidden = out[0] if isinstance(out, (tuple, list)) else out
-                nxt.append(_with_hidden(args, kwargs, hidden))
-                captured[i] = None   # this block's input is not needed again
-        captured = nxt
+        if propagate_error:
+            with torch.no_grad(), HooksMixin.disable_hooks():
+                # propagation pass with the quantised weights; a batch is released once consumed
+                for args, kwargs in store.batches(release=True):
+                    out = layer(*args, **kwargs)
+                    hidden = out[0] if isinstance(out, (tuple, list)) else out
+                    nxt.append(_with_hidden(args, kwargs, hidden))
+        nxt.settle()
+        store = nxt
         clock.mark("propagate")
-    del captured
+    del store
     # targeted modules outside the blocks (an lm_head that is not ignored, a head or adapter behind
     # the stack): one more pass over the whole model, whose blocks now carry their quantised
     # weights, calibrates them; modules that are already done ignore their hooks
@@ -192,6 +290,7 @@ def oneshot(model, recipe=None, dataset=None, num_calibration_samples: int = 512
             max_seq_length: Optional[int] = None, batch_size: int = 1, pipeline: str = "independent",
             sequential_targets=None, moe_calibrate_all_experts: bool = True,
             output_dir: Optional[str] = None, save_compressed: bool = True, phase_times: Optional[dict] = None,
+            sequential_offload_device=None, sequential_prefetch: bool = False, propagate_error: bool = True,
             **_ignored):
     """Apply the recipe's modifiers to ``model`` in one calibration pass and return it.
 
@@ -199,7 +298,10 @@ def oneshot(model, recipe=None, dataset=None, num_calibration_samples: int = 512
     ``dataset`` is a DataLoader, a list of ``{"input_ids": ...}`` dicts / id tensors, or a
     [samples, length] tensor of token ids; it may be None for data-free recipes.  ``phase_times``
     (a dict) asks for wall seconds per phase of the sequential driver (capture, calibrate, compress,
-    propagate), at the price of a device synchronisation at every phase boundary."""
+    propagate), at the price of a device synchronisation at every phase boundary.
+    ``sequential_offload_device`` (default None: activations stay in device memory; the reference
+    defaults to "cpu"), ``sequential_prefetch`` and ``propagate_error`` are the reference's dataset
+    arguments of the same names (src/llmcompressor/args/dataset_arguments.py:244-300)."""
     if isinstance(model, str):
         raise NotImplementedError("pass an instantiated model; loading checkpoints is outside this package")
     if recipe is None:
@@ -218,7 +320,9 @@ def oneshot(model, recipe=None, dataset=None, num_calibration_samples: int = 512
             batches = _as_batches(dataset, num_calibration_samples, max_seq_length, batch_size, device)
             if not batches:
                 raise ValueError(f"{type(m).__name__} needs calibration data but no dataset was given")
-            _run_sequential(model, [m], batches, sequential_targets, phase_times)
+            _run_sequential(model, [m], batches, sequential_targets, phase_times,
+                            offload_device=sequential_offload_device, prefetch=sequential_prefetch,
+                            propagate_error=propagate_error)
         else:
             _run_data_free(model, [m])
     for m in modifiers:

@@ -297,6 +297,15 @@ def hessian_finalize(H: torch.Tensor, scale: float = 1.0):
 
 
 # ---------------------------------------------------------------------------- GPTQ solve
+def set_reproducible(on: bool) -> bool:
+    """Bitwise reproducible Hessian accumulation (no atomics across token splits) for all later
+    calls in this process; returns the previous setting."""
+    lib = _lib.load()
+    before = bool(lib.b200q_get_reproducible())
+    lib.b200q_set_reproducible(int(bool(on)))
+    return before
+
+
 def actorder_perm(H: torch.Tensor) -> torch.Tensor:
     _need_cuda(H)
     K = H.shape[0]

@@ -87,6 +87,29 @@ def test_hessian_running_mean_golden(sgpt_golden):
             assert rel_fro(H, step["H"]) < HESSIAN_RTOL, name
 
 
+def test_reproducible_mode_gives_equal_bits():
+    """Token splits add partial tiles with atomics (last-bit differences from run to run);
+    b200q_set_reproducible(1) accumulates every tile in one place."""
+    K, T = 256, 8192
+    x = synth_acts(1, T, K, seed=77)[0].to(DEV)
+    before = ops.set_reproducible(True)
+    try:
+        assert ops.set_reproducible(True) is True
+        Hs = []
+        for _ in range(3):
+            H = torch.zeros(K, K, device=DEV)
+            ops.hessian_syrk(x, H, alpha=2.0)
+            ops.hessian_finalize(H, 1.0)
+            Hs.append(H)
+        assert torch.equal(Hs[0], Hs[1]) and torch.equal(Hs[0], Hs[2])
+    finally:
+        ops.set_reproducible(before)
+    H = torch.zeros(K, K, device=DEV)
+    ops.hessian_syrk(x, H, alpha=2.0)
+    ops.hessian_finalize(H, 1.0)
+    assert rel_fro(H, Hs[0]) < HESSIAN_RTOL     # a longer accumulation per tile: 3e-5 here, both within the tolerance
+
+
 def test_hessian_noncontiguous_and_3d():
     x = synth_acts(3, 100, 136, seed=9)  # [B,S,K] with K % 8 == 0
     H_ref, n_ref = oracle.accumulate_hessian(x, oracle.make_empty_hessian(136), 0)

@@ -499,3 +499,78 @@ def test_kv_cache_scheme_is_validated():
                                                                 dynamic=False))
     with pytest.raises(ValueError, match="no module matches"):
         mod.on_initialize(torch.nn.Sequential(torch.nn.Linear(8, 8)))
+
+
+def _gptq_weights(model):
+    return {n: p.data.clone() for n, p in model.named_parameters() if n.endswith("proj.weight")}
+
+
+def test_activation_offload_and_prefetch_do_not_change_results():
+    """Parking the blocks' inputs in pinned host memory between uses, with or without prefetching
+    the next batch on a copy stream, moves data only."""
+    base = tiny_llama(seed=21)
+    data = calib(12, 640)      # [1, 640, 256] bf16 hidden states are below the 1 MiB parking limit ...
+    batch = 4                  # ... four sequences per batch are above it
+
+    def run(**kw):
+        recipe = GPTQModifier(targets="Linear", scheme="W4A16", ignore=["lm_head"])
+        return _gptq_weights(oneshot(copy.deepcopy(base), recipe=recipe, dataset=data, batch_size=batch, **kw))
+
+    from llm_compressor_b200 import ops
+    before = ops.set_reproducible(True)     # no atomics across token splits: equal inputs, equal bits
+    try:
+        ref = run()
+        for kw in (dict(sequential_offload_device="cpu"),
+                   dict(sequential_offload_device="cpu", sequential_prefetch=True)):
+            got = run(**kw)
+            for n in ref:
+                assert torch.equal(ref[n], got[n]), (kw, n)
+    finally:
+        ops.set_reproducible(before)
+
+
+def test_activation_store_parks_large_tensors_on_the_host():
+    from llm_compressor_b200.oneshot import _ActivationStore
+    store = _ActivationStore(torch.device(DEV), "cpu", prefetch=True)
+    big = torch.randn(4, 640, 256, device=DEV).to(torch.bfloat16)
+    small = torch.arange(640, device=DEV)
+    for i in range(3):
+        store.append(((big + i,), {"position_ids": small, "flag": True, "pair": (small, None)}))
+    store.settle()
+    (parked,), kw = store.items[0]
+    assert parked.device.type == "cpu" and parked.is_pinned() and kw["position_ids"].is_cuda
+    seen = list(store.batches(release=True))
+    assert all(x is None for x in store.items)
+    for i, ((t,), kw) in enumerate(seen):
+        assert t.is_cuda and torch.equal(t, big + i) and kw["flag"] is True and kw["pair"][1] is None
+
+
+def test_propagate_error_false_feeds_unquantised_outputs():
+    """Without error propagation block 1 is calibrated on the outputs of the unquantised block 0:
+    the same as a run that quantises block 1 only."""
+    from llm_compressor_b200 import ops
+    before = ops.set_reproducible(True)
+    try:
+        _check_propagate_error_false()
+    finally:
+        ops.set_reproducible(before)
+
+
+def _check_propagate_error_false():
+    base = tiny_llama(seed=22)
+    data = calib(8, 64)
+    both = oneshot(copy.deepcopy(base), recipe=GPTQModifier(targets="Linear", scheme="W4A16", ignore=["lm_head"]),
+                   dataset=data, propagate_error=False)
+    only1 = oneshot(copy.deepcopy(base), dataset=data, recipe=GPTQModifier(
+        targets="Linear", scheme="W4A16", ignore=["lm_head", "re:.*layers\\.0\\..*"]))
+    default = oneshot(copy.deepcopy(base), dataset=data,
+                      recipe=GPTQModifier(targets="Linear", scheme="W4A16", ignore=["lm_head"]))
+    a, b, c = _gptq_weights(both), _gptq_weights(only1), _gptq_weights(default)
+    differs = 0
+    for n in a:
+        if ".layers.1." in n:
+            assert torch.equal(a[n], b[n]), n
+            differs += int(not torch.equal(a[n], c[n]))
+        else:
+            assert torch.equal(a[n], c[n]), n     # block 0 sees the same inputs either way
+    assert differs > 0
