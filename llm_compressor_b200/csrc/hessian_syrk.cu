@@ -747,6 +747,15 @@ using namespace b200q;
 // (pair) over all tokens: bitwise reproducible, slower when the tiles alone do not fill the GPU.
 static std::atomic<int> g_reproducible{0};
 
+static int64_t max_chain_tokens() {
+  static const int64_t v = [] {
+    const char* e = getenv("B200Q_SYRK_MAX_CHAIN");
+    const long long x = e ? atoll(e) : (1ll << 40);
+    return (int64_t)(x < 512 ? 512 : x);
+  }();
+  return v;
+}
+
 extern "C" {
 
 int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* H, int64_t ldh,
@@ -786,6 +795,11 @@ int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* 
       const int64_t waves = (units + pairs - 1) / pairs;
       const double eff = (double)units / (double)(waves * pairs);
       if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    }
+    {
+      // bound the length of one tensor-core accumulation chain: its float32 error grows with it
+      const int64_t need = (T + max_chain_tokens() - 1) / max_chain_tokens();
+      if (best < need) best = (int)(need < 64 ? need : 64);
     }
     p.splits = g_reproducible.load(std::memory_order_relaxed) ? 1 : best;
     const int64_t tps = (T + p.splits - 1) / p.splits;
