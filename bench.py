@@ -796,24 +796,32 @@ def run_moe(args):
     tms = torch.tensor([ms, wall_ms], device=dev)
     if world > 1:
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-    # parity of one expert's down projection (K = 768, its own Hessian) against the CPU oracle
+    # parity against the CPU oracle of one expert's down projection (K = 768, its own Hessian) and
+    # of one gate projection (K = 2048, the Hessian all experts share): both go through the batched
+    # factor / fused sweep launches
     parity = None
     if rank == 0 and world == 1:
         from llm_compressor_b200 import gptq
-        name, lin, key, off = next(m for m in mods if m[0] == "experts_3_down_proj")
-        Hh = torch.zeros(MI, MI, device=dev)
-        for t0 in range(0, tokens, chunk):
-            t1 = min(tokens, t0 + chunk)
-            gptq.accumulate_hessian_lower(X["down_in"][off + t0: off + t1].view(-1, SEQ_LEN, MI), Hh, 0)
-        gptq.finalize_hessian(Hh, seqs)
         spec = oracle.preset("FP8_DYNAMIC", actorder="static")
-        loss_ref, ref = oracle.quantize_weight(W0[name].cpu(), spec, Hh.cpu())
-        match = float((lin.weight.data.cpu().view(torch.int16) == ref["weight"].view(torch.int16)).float().mean())
-        parity = {"module": name, "code_match": round(match, 6),
-                  "scale_equal": bool(torch.equal(lin.weight_scale.data.cpu().view(torch.int16).flatten(),
-                                                  ref["weight_scale"].view(torch.int16).flatten())),
-                  "loss_rel": round(abs(mod.losses[name] - loss_ref) / abs(loss_ref), 6)}
-        parity["ok"] = parity["code_match"] >= 0.995 and parity["scale_equal"] and parity["loss_rel"] <= 0.01
+        parity = {"ok": True, "modules": []}
+        for wanted in ("experts_3_down_proj", "experts_5_gate_proj"):
+            name, lin, key, off = next(m for m in mods if m[0] == wanted)
+            src = X["hidden"] if key == "mlp" else X[key]
+            K_ = src.shape[1]
+            Hh = torch.zeros(K_, K_, device=dev)
+            for t0 in range(0, tokens, chunk):
+                t1 = min(tokens, t0 + chunk)
+                gptq.accumulate_hessian_lower(src[off + t0: off + t1].view(-1, SEQ_LEN, K_), Hh, 0)
+            gptq.finalize_hessian(Hh, seqs)
+            loss_ref, ref = oracle.quantize_weight(W0[name].cpu(), spec, Hh.cpu())
+            match = float((lin.weight.data.cpu().view(torch.int16) == ref["weight"].view(torch.int16)).float().mean())
+            one = {"module": name, "code_match": round(match, 6),
+                   "scale_equal": bool(torch.equal(lin.weight_scale.data.cpu().view(torch.int16).flatten(),
+                                                   ref["weight_scale"].view(torch.int16).flatten())),
+                   "loss_rel": round(abs(mod.losses[name] - loss_ref) / abs(loss_ref), 6)}
+            one["ok"] = one["code_match"] >= 0.995 and one["scale_equal"] and one["loss_rel"] <= 0.01
+            parity["modules"].append(one)
+            parity["ok"] = parity["ok"] and one["ok"]
     if rank == 0:
         print(json.dumps({
             "metric": "gptq_fp8_qwen3_30b_a3b_layer_ms", "value": float(tms[0]), "unit": "ms", "n_gpus": world,
