@@ -216,6 +216,8 @@ def _sweep_input(module, quant_args, hessian, percdamp, factor) -> _SweepInput:
     if actorder == "group":
         observer.delete_statistics(check_fused=False)
         observer(W)
+    elif not observer.has_statistics:
+        observer(weight)     # memoryless: the statistics of the weight as it is now
 
     col_group = None
     g_idx = None
@@ -254,8 +256,9 @@ def quantize_weight(module, quant_args, hessian: Optional[torch.Tensor], blocksi
     """GPTQ-quantise ``module.weight`` given its Hessian (already divided by the sample
     count).  Returns ``(loss, dict)`` with the fake-quantised weight in the original dtype,
     ``weight_scale``, ``weight_zero_point`` and, where they apply, ``weight_global_scale`` and
-    ``weight_g_idx``.  ``hessian`` is consumed.  ``module.weight_observer`` must hold
-    statistics unless act-order "group" re-observes; ``module.weight`` is not touched.
+    ``weight_g_idx``.  ``hessian`` is consumed.  ``module.weight_observer`` is asked to
+    observe the weight if it holds no statistics yet (act-order "group" always re-observes the
+    permuted weight); ``module.weight`` is not touched.
 
     ``factor`` (from ``factor_hessian`` with the same ``percdamp`` and act-order setting) may
     be passed instead of ``hessian`` when several modules share one Hessian.

@@ -572,7 +572,8 @@ class GPTQModifier(QuantizationMixin):
         modules = list(modules)
         self.update_activation_qparams(modules)
         mods = [m for m in modules if m in self._num_samples]
-        observe(mods, "weight")
+        # the weight observers are called by the solves themselves (gptq._sweep_input), on the rank
+        # and stream that quantises the module, next to the rest of its work
         self.compress_modules(mods)
 
     def _trace(self, event, module=None):
@@ -709,7 +710,11 @@ class GPTQModifier(QuantizationMixin):
                     module.weight.data.copy_(val)
                 elif hasattr(module, attr):
                     p = getattr(module, attr)
-                    p.data.copy_(val.reshape(p.shape))
+                    val = val.reshape(p.shape)
+                    if val.dtype == p.dtype and val.device == p.device and val.is_contiguous():
+                        p.data = val        # a fresh tensor of the solve: no copy into the placeholder
+                    else:
+                        p.data.copy_(val)
                 else:
                     module.register_parameter(attr, torch.nn.Parameter(val, requires_grad=False))
             module.quantization_status = "frozen"
@@ -768,7 +773,10 @@ class GPTQModifier(QuantizationMixin):
             key = (tuple(module.weight.shape), module.weight.dtype, repr(qargs))
             by_shape.setdefault(key, []).append((module, qargs, holder[0]))
         queued = []
-        for items in by_shape.values():
+        # the class with the most device work first: its sweep runs while the host prepares the others
+        classes = sorted(by_shape.values(), key=lambda it: -len(it) * it[0][0].weight.shape[0]
+                         * it[0][0].weight.shape[1] ** 2)
+        for items in classes:
             with torch.no_grad():
                 if len(items) >= 4:
                     done = gptq.quantize_weights_batched([m for m, _, _ in items], items[0][1],
