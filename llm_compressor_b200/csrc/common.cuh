@@ -162,11 +162,35 @@ __device__ __forceinline__ float quant_code_fast(float x, float s, float rs, flo
   }
   return quant_code<CB>(x, s, zp, r);
 }
+// round_code with the code type known at compile time
+template <int KIND>
+__device__ __forceinline__ float round_code_k(float v, float qmin, float qmax) {
+  v = fminf(fmaxf(v, qmin), qmax);
+  if constexpr (KIND == kInt) return rintf(v);
+  else if constexpr (KIND == kFp8) return e4m3_round(v);
+  else return e2m1_round(v);
+}
 // (q - zp) * s in the scale's dtype (SB: bf16).
 template <bool SB>
 __device__ __forceinline__ float dequant_code(float q, float s, float zp) {
   float d = rnd_if<SB>(q - zp);
   return rnd_if<SB>(d * s);
+}
+
+// Fake-quantised value of a float32 weight, as the GPTQ sweep needs it once per column on its
+// critical path: the same result as dequant_code<SB>(quant_code<false>(x, s, zp, r), s, zp), with
+// the code type a compile-time constant and the division replaced by the product with rs = 1/s
+// whenever both ends of a 2^-20 interval around it give the same code (else the division is redone).
+template <int KIND, bool SB>
+__device__ __forceinline__ float fake_quant_f32(float x, float s, float rs, float zp, float qmin, float qmax) {
+  const float qa = x * rs;
+  const float aq = fabsf(qa);
+  const float a = round_code_k<KIND>(qa * (1.0f - 0x1p-20f) + zp, qmin, qmax);
+  const float b = round_code_k<KIND>(qa * (1.0f + 0x1p-20f) + zp, qmin, qmax);
+  float q = a;   // both ends have the sign of qa, so this is also the code's sign of zero
+  if (!((aq < 1e30f) && (aq > 1e-30f || aq == 0.0f) && (a == b)))
+    q = round_code_k<KIND>(__fdiv_rn(x, s) + zp, qmin, qmax);
+  return dequant_code<SB>(q, s, zp);
 }
 
 __device__ __forceinline__ float load_zp(const void* zp, int zp_kind, int64_t i) {

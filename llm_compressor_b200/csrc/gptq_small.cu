@@ -38,12 +38,6 @@ __host__ __device__ constexpr size_t sweep_smem_bytes() {
   return ((size_t)NB * NB + (size_t)NB * kWLD) * sizeof(float);
 }
 
-template <bool SB>
-__device__ __noinline__ float quant_one(float wi, float s, float rs, float z, const QRange qr) {
-  const float q = quant_code_fast<false>(wi, s, rs, z, qr);
-  return dequant_code<SB>(q, s, z);
-}
-
 __device__ __forceinline__ void cp_async16(float* dst_smem, const float* src, int src_bytes) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst_smem);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
@@ -53,9 +47,10 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int SDT, bool GLOBAL>
+template <int SDT, bool GLOBAL, int KIND>
 __global__ void __launch_bounds__(kThreads, 2) sweep_fused_kernel(SweepBatch b) {
   constexpr bool SB = Elem<SDT>::is_bf16 && !GLOBAL;
+  const float qmin = b.qr.qmin, qmax = b.qr.qmax;
   extern __shared__ float sm[];
   float* sU = sm;                          // [128][128] diagonal block; during the trailing update two [128][64] slices of U
   float* sW = sU + NB * NB;                // [128 cols][kWLD]: the block's columns of this CTA's rows, then their errors
@@ -172,7 +167,7 @@ __global__ void __launch_bounds__(kThreads, 2) sweep_fused_kernel(SweepBatch b) 
               }
             }
             const float wi = w[t];
-            const float q = quant_one<SB>(wi, s, rs, z, b.qr);
+            const float q = fake_quant_f32<KIND, SB>(wi, s, rs, z, qmin, qmax);
             const float diff = __fsub_rn(wi, q);
             const float tt = __fmul_rn(diff, s_rd[i]);
             loss = fmaf(tt, tt, loss);
@@ -354,9 +349,16 @@ int b200q_gptq_sweep_batched(float* const* W, const float* const* U, const void*
   b.zp_kind = qa->zp_kind;
   b.groups_per_row = pm.groups_per_row;
   void (*kern)(SweepBatch) = nullptr;
-  if (sdtype == B200Q_BF16) kern = gscale ? sweep_fused_kernel<B200Q_BF16, true> : sweep_fused_kernel<B200Q_BF16, false>;
-  else if (sdtype == B200Q_F32) kern = gscale ? sweep_fused_kernel<B200Q_F32, true> : sweep_fused_kernel<B200Q_F32, false>;
+#define B200Q_SWEEP_PICK(SDT)                                                                              \
+  do {                                                                                                     \
+    if (b.qr.kind == kInt) kern = gscale ? sweep_fused_kernel<SDT, true, kInt> : sweep_fused_kernel<SDT, false, kInt>;      \
+    else if (b.qr.kind == kFp8) kern = gscale ? sweep_fused_kernel<SDT, true, kFp8> : sweep_fused_kernel<SDT, false, kFp8>; \
+    else kern = gscale ? sweep_fused_kernel<SDT, true, kFp4> : sweep_fused_kernel<SDT, false, kFp4>;       \
+  } while (0)
+  if (sdtype == B200Q_BF16) B200Q_SWEEP_PICK(B200Q_BF16);
+  else if (sdtype == B200Q_F32) B200Q_SWEEP_PICK(B200Q_F32);
   else return B200Q_ERR_UNSUPPORTED;
+#undef B200Q_SWEEP_PICK
   B200Q_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sweep_smem_bytes()));
   dim3 grid((unsigned)((N + kRows - 1) / kRows), (unsigned)count, 1);
   kern<<<grid, kThreads, sweep_smem_bytes(), (cudaStream_t)stream>>>(b);

@@ -47,30 +47,22 @@ constexpr int kCtaThreads = 256;  // all threads help with the loads of the U bl
 constexpr int kSub = 16;          // columns kept in registers at a time (code size grows with its square)
 
 __host__ __device__ inline size_t sweep_smem_bytes(int warps) {
-  return ((size_t)kMaxBlock * kMaxBlock + (size_t)kMaxBlock * (32 * warps + 1) + (size_t)warps * kSub * 33 + 64) *
-         sizeof(float);
+  return ((size_t)kMaxBlock * kMaxBlock + (size_t)kMaxBlock * (32 * warps + 1) + 64) * sizeof(float);
 }
 
-// One column of one row: fake-quantised value.  Kept out of line: the column loop is unrolled and
-// the kernel has to stay inside the instruction cache (a single warp per SM runs it for small N).
-template <bool SB>
-__device__ __noinline__ float sweep_quant(float wi, float s, float rs, float z, const QRange qr) {
-  // w is float32, so the quantise arithmetic is float32 (quant_code_fast gives the same code as the
-  // true division); only the dequantised value takes the scale's dtype
-  const float q = quant_code_fast<false>(wi, s, rs, z, qr);
-  return dequant_code<SB>(q, s, z);
-}
-
-template <int SDT, bool GLOBAL>
+// KIND: the code type (CodeKind), a compile-time constant so that the quantisation of a column - the
+// critical path of the whole sweep - is a short inline sequence without dispatch.
+template <int SDT, bool GLOBAL, int KIND>
 __global__ void __launch_bounds__(kCtaThreads) sweep_block_kernel(Params p, int warps) {
   constexpr bool SB = Elem<SDT>::is_bf16 && !GLOBAL;
+  const float qmin = p.qr.qmin, qmax = p.qr.qmax;
   extern __shared__ float sm[];
   const int WLD = 32 * warps + 1;
   float* sU = sm;                                   // [128][128] row i, local column c (identity when U is null)
   float* sW = sU + kMaxBlock * kMaxBlock;           // [128][WLD] column c, row slot
-  float* sEall = sW + kMaxBlock * WLD;              // [warps][kSub][33]
   __shared__ float s_rd[kMaxBlock];                 // 1 / U[i][i]
   __shared__ int s_grp[kMaxBlock];                  // parameter column (group / block column) of each column
+  __shared__ int s_same[kMaxBlock / kSub];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bs = p.bs;
   // U block (only c >= r is ever read): 16-byte loads when the layout allows, several in flight
@@ -113,9 +105,14 @@ __global__ void __launch_bounds__(kCtaThreads) sweep_block_kernel(Params p, int 
     s_grp[i] = grp;
   }
   __syncthreads();
+  if (threadIdx.x < kMaxBlock / kSub) {   // does one (scale, zero point) govern the whole sub-block?
+    bool same = true;
+    for (int t = 1; t < kSub; ++t) same = same && s_grp[threadIdx.x * kSub + t] == s_grp[threadIdx.x * kSub];
+    s_same[threadIdx.x] = same ? 1 : 0;
+  }
+  __syncthreads();
   const float g = GLOBAL ? *p.gscale : 1.0f;
   const bool has_zp = p.zp != nullptr;
-  float* sE = sEall + warp * (kSub * 33);
   float* myW = sW + warp * 32;   // this warp's 32 row slots
   const int64_t batches = (p.N + 31) / 32;
   if (warp >= warps) return;   // no CTA-wide barrier below this point
@@ -149,76 +146,94 @@ __global__ void __launch_bounds__(kCtaThreads) sweep_block_kernel(Params p, int 
 #pragma unroll 1
     for (int sub = 0; sub * kSub < bs; ++sub) {
       const int c0 = sub * kSub;
-      float w[kSub], e[kSub];
+      // Quantisation parameters of the sub-block's columns, fetched before the dependent chain
+      // starts.  Columns at or beyond bs (the ragged last block) are zero columns with a unit
+      // pivot and zero rows of U: they run through the same code and change nothing.
+      float sv[kSub], rsv[kSub], zv[kSub];
+      if (s_same[sub]) {   // uniform
+        const int grp = s_grp[c0];
+        if (grp != cur_grp) {
+          cur_grp = grp;
+          if (live) {
+            const int64_t pi = pbase + grp;
+            s = Elem<SDT>::load((const typename Elem<SDT>::type*)p.scale + pi);
+            if (GLOBAL) s = __fdiv_rn(s, g);
+            rs = __frcp_rn(s);
+            if (has_zp) z = load_zp(p.zp, p.zp_kind, pi);
+          }
+        }
 #pragma unroll
-      for (int t = 0; t < kSub; ++t) w[t] = myW[(c0 + t) * WLD + lane];
+        for (int t = 0; t < kSub; ++t) { sv[t] = s; rsv[t] = rs; zv[t] = z; }
+      } else {             // act-order: every column may have its own group
+        cur_grp = -1;
+#pragma unroll
+        for (int t = 0; t < kSub; ++t) {
+          float st = 1.0f, zt = 0.0f;
+          if (live) {
+            const int64_t pi = pbase + s_grp[c0 + t];
+            st = Elem<SDT>::load((const typename Elem<SDT>::type*)p.scale + pi);
+            if (GLOBAL) st = __fdiv_rn(st, g);
+            if (has_zp) zt = load_zp(p.zp, p.zp_kind, pi);
+          }
+          sv[t] = st; rsv[t] = __frcp_rn(st); zv[t] = zt;
+        }
+      }
+      float w[kSub], e[kSub], rd[kSub];
+#pragma unroll
+      for (int t = 0; t < kSub; ++t) { w[t] = myW[(c0 + t) * WLD + lane]; rd[t] = s_rd[c0 + t]; }
 #pragma unroll
       for (int t = 0; t < kSub; ++t) {
         const int i = c0 + t;
-        e[t] = 0.0f;
-        if (i < bs) {   // uniform
-          const int grp = s_grp[i];
-          if (grp != cur_grp) {   // uniform
-            cur_grp = grp;
-            if (live) {
-              const int64_t pi = pbase + grp;
-              s = Elem<SDT>::load((const typename Elem<SDT>::type*)p.scale + pi);
-              if (GLOBAL) s = __fdiv_rn(s, g);
-              rs = __frcp_rn(s);
-              if (has_zp) z = load_zp(p.zp, p.zp_kind, pi);
-            }
-          }
-          const float wi = w[t];
-          const float q = sweep_quant<SB>(wi, s, rs, z, p.qr);
-          const float diff = __fsub_rn(wi, q);
-          // loss and error use the reciprocal of the pivot (an ulp from the reference's divisions)
-          const float tt = __fmul_rn(diff, s_rd[i]);
-          loss = fmaf(tt, tt, loss);
-          e[t] = tt;
-          w[t] = q;
-          const float4* urow = reinterpret_cast<const float4*>(sU + i * kMaxBlock + c0);
+        const float wi = w[t];
+        const float q = fake_quant_f32<KIND, SB>(wi, sv[t], rsv[t], zv[t], qmin, qmax);
+        const float diff = __fsub_rn(wi, q);
+        // loss and error use the reciprocal of the pivot (an ulp from the reference's divisions)
+        const float tt = __fmul_rn(diff, rd[t]);
+        loss = fmaf(tt, tt, loss);
+        e[t] = tt;
+        w[t] = q;
+        const float4* urow = reinterpret_cast<const float4*>(sU + i * kMaxBlock + c0);
 #pragma unroll
-          for (int k4 = (t + 1) / 4; k4 < kSub / 4; ++k4) {
-            const float4 u = urow[k4];
-            if (4 * k4 + 0 > t) w[4 * k4 + 0] = __fsub_rn(w[4 * k4 + 0], __fmul_rn(tt, u.x));
-            if (4 * k4 + 1 > t) w[4 * k4 + 1] = __fsub_rn(w[4 * k4 + 1], __fmul_rn(tt, u.y));
-            if (4 * k4 + 2 > t) w[4 * k4 + 2] = __fsub_rn(w[4 * k4 + 2], __fmul_rn(tt, u.z));
-            if (4 * k4 + 3 > t) w[4 * k4 + 3] = __fsub_rn(w[4 * k4 + 3], __fmul_rn(tt, u.w));
-          }
+        for (int k4 = (t + 1) / 4; k4 < kSub / 4; ++k4) {
+          const float4 u = urow[k4];
+          if (4 * k4 + 0 > t) w[4 * k4 + 0] = __fsub_rn(w[4 * k4 + 0], __fmul_rn(tt, u.x));
+          if (4 * k4 + 1 > t) w[4 * k4 + 1] = __fsub_rn(w[4 * k4 + 1], __fmul_rn(tt, u.y));
+          if (4 * k4 + 2 > t) w[4 * k4 + 2] = __fsub_rn(w[4 * k4 + 2], __fmul_rn(tt, u.z));
+          if (4 * k4 + 3 > t) w[4 * k4 + 3] = __fsub_rn(w[4 * k4 + 3], __fmul_rn(tt, u.w));
         }
       }
-      // quantised values back into the tile, errors to the staging tile
+      // quantised values back into the tile; the errors go straight to the panel the trailing
+      // update reads: 16 consecutive floats per row
 #pragma unroll
-      for (int t = 0; t < kSub; ++t) {
-        myW[(c0 + t) * WLD + lane] = w[t];
-        sE[t * 33 + lane] = e[t];
+      for (int t = 0; t < kSub; ++t) myW[(c0 + t) * WLD + lane] = w[t];
+      if (live) {
+        float4* dst = reinterpret_cast<float4*>(p.err + row * p.lde + c0);
+#pragma unroll
+        for (int t = 0; t < kSub; t += 4) dst[t / 4] = make_float4(e[t], e[t + 1], e[t + 2], e[t + 3]);
       }
-      __syncwarp();
-      {
-        // kSub columns x 32 rows out, two rows per instruction
-        const int ec = lane & (kSub - 1), er = lane / kSub;
-        if (c0 + ec < bs) {
-#pragma unroll 4
-          for (int r = er; r < 32; r += 32 / kSub) {
-            const int64_t rr = row0 + r;
-            if (rr < p.N) p.err[rr * p.lde + c0 + ec] = sE[ec * 33 + r];
-          }
-        }
-      }
-      __syncwarp();
-      // the later columns of the block take this sub-block's corrections
+      // the later columns of the block take this sub-block's corrections: v -= e * u as a packed
+      // product and a packed sum with -e (two float32 lanes per instruction, each rounded like the
+      // scalar operations)
+      uint64_t ne2[kSub];
+#pragma unroll
+      for (int t = 0; t < kSub; ++t) asm("mov.b64 %0, {%1, %1};" : "=l"(ne2[t]) : "f"(-e[t]));
 #pragma unroll 1
       for (int c = c0 + kSub; c < bs; c += 4) {
-        float v0 = myW[(c + 0) * WLD + lane], v1 = myW[(c + 1) * WLD + lane];
-        float v2 = myW[(c + 2) * WLD + lane], v3 = myW[(c + 3) * WLD + lane];
+        uint64_t v01, v23;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(v01) : "f"(myW[(c + 0) * WLD + lane]), "f"(myW[(c + 1) * WLD + lane]));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(v23) : "f"(myW[(c + 2) * WLD + lane]), "f"(myW[(c + 3) * WLD + lane]));
 #pragma unroll
         for (int t = 0; t < kSub; ++t) {
-          const float4 u = *reinterpret_cast<const float4*>(sU + (c0 + t) * kMaxBlock + c);
-          v0 = __fsub_rn(v0, __fmul_rn(e[t], u.x));
-          v1 = __fsub_rn(v1, __fmul_rn(e[t], u.y));
-          v2 = __fsub_rn(v2, __fmul_rn(e[t], u.z));
-          v3 = __fsub_rn(v3, __fmul_rn(e[t], u.w));
+          const ulonglong2 u = *reinterpret_cast<const ulonglong2*>(sU + (c0 + t) * kMaxBlock + c);
+          uint64_t p01, p23;
+          asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p01) : "l"(ne2[t]), "l"(u.x));
+          asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p23) : "l"(ne2[t]), "l"(u.y));
+          asm("add.rn.f32x2 %0, %1, %2;" : "=l"(v01) : "l"(v01), "l"(p01));
+          asm("add.rn.f32x2 %0, %1, %2;" : "=l"(v23) : "l"(v23), "l"(p23));
         }
+        float v0, v1, v2, v3;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(v0), "=f"(v1) : "l"(v01));
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(v2), "=f"(v3) : "l"(v23));
         myW[(c + 0) * WLD + lane] = v0; myW[(c + 1) * WLD + lane] = v1;
         myW[(c + 2) * WLD + lane] = v2; myW[(c + 3) * WLD + lane] = v3;
       }
@@ -293,9 +308,16 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
   int warps = (int)((batches + kNumSMs - 1) / kNumSMs);
   warps = warps < 1 ? 1 : (warps > kMaxWarps ? kMaxWarps : warps);
   void (*kern)(Params, int) = nullptr;
-  if (sdtype == B200Q_BF16) kern = gscale ? sweep_block_kernel<B200Q_BF16, true> : sweep_block_kernel<B200Q_BF16, false>;
-  else if (sdtype == B200Q_F32) kern = gscale ? sweep_block_kernel<B200Q_F32, true> : sweep_block_kernel<B200Q_F32, false>;
+#define B200Q_SWEEP_PICK(SDT)                                                                              \
+  do {                                                                                                     \
+    if (p.qr.kind == kInt) kern = gscale ? sweep_block_kernel<SDT, true, kInt> : sweep_block_kernel<SDT, false, kInt>;      \
+    else if (p.qr.kind == kFp8) kern = gscale ? sweep_block_kernel<SDT, true, kFp8> : sweep_block_kernel<SDT, false, kFp8>; \
+    else kern = gscale ? sweep_block_kernel<SDT, true, kFp4> : sweep_block_kernel<SDT, false, kFp4>;       \
+  } while (0)
+  if (sdtype == B200Q_BF16) B200Q_SWEEP_PICK(B200Q_BF16);
+  else if (sdtype == B200Q_F32) B200Q_SWEEP_PICK(B200Q_F32);
   else return B200Q_ERR_UNSUPPORTED;
+#undef B200Q_SWEEP_PICK
   // always the largest size: host threads on other streams launch the same kernel with other sizes
   B200Q_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)sweep_smem_bytes(kMaxWarps)));
