@@ -185,11 +185,16 @@ template <int KIND, bool SB>
 __device__ __forceinline__ float fake_quant_f32(float x, float s, float rs, float zp, float qmin, float qmax) {
   const float qa = x * rs;
   const float aq = fabsf(qa);
-  const float a = round_code_k<KIND>(qa * (1.0f - 0x1p-20f) + zp, qmin, qmax);
-  const float b = round_code_k<KIND>(qa * (1.0f + 0x1p-20f) + zp, qmin, qmax);
+  const float a = round_code_k<KIND>(fmaf(qa, 1.0f - 0x1p-20f, zp), qmin, qmax);
+  const float b = round_code_k<KIND>(fmaf(qa, 1.0f + 0x1p-20f, zp), qmin, qmax);
   float q = a;   // both ends have the sign of qa, so this is also the code's sign of zero
   if (!((aq < 1e30f) && (aq > 1e-30f || aq == 0.0f) && (a == b)))
     q = round_code_k<KIND>(__fdiv_rn(x, s) + zp, qmin, qmax);
+  if constexpr (KIND == kInt) {
+    // an integer code minus an integer zero point is at most 255 in magnitude: exact in bf16 too,
+    // so only the product with the scale is rounded
+    return rnd_if<SB>((q - zp) * s);
+  }
   return dequant_code<SB>(q, s, zp);
 }
 

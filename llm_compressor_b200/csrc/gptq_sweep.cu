@@ -26,7 +26,8 @@ struct Params {
   int strategy, group_size, block_h, zp_kind;
   int64_t groups_per_row;
   QRange qr;
-  float* err; int64_t lde;   // [N, bs]
+  float* err_hi; float* err_lo; int64_t lde;   // the block's errors [N, lde] as the hi / lo operand split of the
+                                               // trailing update's tile products (null: no trailing update)
   float* losses;
   int i1, bs;                // block start and width (<= 128)
   int first;                 // first block: losses are overwritten
@@ -206,10 +207,17 @@ __global__ void __launch_bounds__(kCtaThreads) sweep_block_kernel(Params p, int 
       // update reads: 16 consecutive floats per row
 #pragma unroll
       for (int t = 0; t < kSub; ++t) myW[(c0 + t) * WLD + lane] = w[t];
-      if (live) {
-        float4* dst = reinterpret_cast<float4*>(p.err + row * p.lde + c0);
+      if (live && p.err_hi) {
+        float4* dh = reinterpret_cast<float4*>(p.err_hi + row * p.lde + c0);
+        float4* dl = reinterpret_cast<float4*>(p.err_lo + row * p.lde + c0);
 #pragma unroll
-        for (int t = 0; t < kSub; t += 4) dst[t / 4] = make_float4(e[t], e[t + 1], e[t + 2], e[t + 3]);
+        for (int t = 0; t < kSub; t += 4) {
+          float h[4], l[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { h[j] = tgemm::tf32_rn(e[t + j]); l[j] = tgemm::tf32_rn(e[t + j] - h[j]); }
+          dh[t / 4] = make_float4(h[0], h[1], h[2], h[3]);
+          dl[t / 4] = make_float4(l[0], l[1], l[2], l[3]);
+        }
       }
       // the later columns of the block take this sub-block's corrections: v -= e * u as a packed
       // product and a packed sum with -e (two float32 lanes per instruction, each rounded like the
@@ -217,25 +225,38 @@ __global__ void __launch_bounds__(kCtaThreads) sweep_block_kernel(Params p, int 
       uint64_t ne2[kSub];
 #pragma unroll
       for (int t = 0; t < kSub; ++t) asm("mov.b64 %0, {%1, %1};" : "=l"(ne2[t]) : "f"(-e[t]));
+      // eight columns per pass: four independent chains of packed sums hide the latency of the adds
+      // (the tile is 128 columns wide, so a ragged block's last pass stays inside it)
 #pragma unroll 1
-      for (int c = c0 + kSub; c < bs; c += 4) {
-        uint64_t v01, v23;
-        asm("mov.b64 %0, {%1, %2};" : "=l"(v01) : "f"(myW[(c + 0) * WLD + lane]), "f"(myW[(c + 1) * WLD + lane]));
-        asm("mov.b64 %0, {%1, %2};" : "=l"(v23) : "f"(myW[(c + 2) * WLD + lane]), "f"(myW[(c + 3) * WLD + lane]));
+      for (int c = c0 + kSub; c < bs; c += 8) {
+        uint64_t v[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h)
+          asm("mov.b64 %0, {%1, %2};" : "=l"(v[h]) : "f"(myW[(c + 2 * h) * WLD + lane]), "f"(myW[(c + 2 * h + 1) * WLD + lane]));
 #pragma unroll
         for (int t = 0; t < kSub; ++t) {
-          const ulonglong2 u = *reinterpret_cast<const ulonglong2*>(sU + (c0 + t) * kMaxBlock + c);
-          uint64_t p01, p23;
-          asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p01) : "l"(ne2[t]), "l"(u.x));
-          asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p23) : "l"(ne2[t]), "l"(u.y));
-          asm("add.rn.f32x2 %0, %1, %2;" : "=l"(v01) : "l"(v01), "l"(p01));
-          asm("add.rn.f32x2 %0, %1, %2;" : "=l"(v23) : "l"(v23), "l"(p23));
+          const ulonglong2 ua = *reinterpret_cast<const ulonglong2*>(sU + (c0 + t) * kMaxBlock + c);
+          const ulonglong2 ub = *reinterpret_cast<const ulonglong2*>(sU + (c0 + t) * kMaxBlock + c + 4);
+          const uint64_t u[4] = {ua.x, ua.y, ub.x, ub.y};
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            uint64_t pr;
+            asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(pr) : "l"(ne2[t]), "l"(u[h]));
+            asm("add.rn.f32x2 %0, %1, %2;" : "=l"(v[h]) : "l"(v[h]), "l"(pr));
+          }
         }
-        float v0, v1, v2, v3;
-        asm("mov.b64 {%0, %1}, %2;" : "=f"(v0), "=f"(v1) : "l"(v01));
-        asm("mov.b64 {%0, %1}, %2;" : "=f"(v2), "=f"(v3) : "l"(v23));
-        myW[(c + 0) * WLD + lane] = v0; myW[(c + 1) * WLD + lane] = v1;
-        myW[(c + 2) * WLD + lane] = v2; myW[(c + 3) * WLD + lane] = v3;
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          float lo, hi;
+          asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v[h]));
+          myW[(c + 2 * h) * WLD + lane] = lo; myW[(c + 2 * h + 1) * WLD + lane] = hi;
+        }
+      }
+    }
+    if (live && p.err_hi) {   // zero padding of the operand rows up to their leading dimension
+      for (int c = (bs + kSub - 1) / kSub * kSub; c < (int)p.lde; c += 4) {
+        *reinterpret_cast<float4*>(p.err_hi + row * p.lde + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(p.err_lo + row * p.lde + c) = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
     __syncwarp();
@@ -295,10 +316,11 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
   // header of the workspace: a status word that a bounded wait expiring inside one of the
   // trailing-update GEMMs sets to B200Q_ERR_DEVICE (cleared here, read by the caller afterwards)
   int* gemm_status = (int*)workspace;
-  p.err = (float*)((char*)workspace + kSweepHeaderBytes);
-  p.lde = 128;
+  float* ws_f = (float*)((char*)workspace + kSweepHeaderBytes);
+  p.err_hi = p.err_lo = nullptr;
+  p.lde = tgemm::split_ld(blocksize);
   const size_t np128 = (size_t)((N + 127) / 128 * 128) * 128, kp128 = (size_t)((K + 127) / 128 * 128) * 128;
-  float* sa_base = p.err + np128;            // [2][hi, lo][np128]
+  float* sa_base = ws_f + np128;             // [2][hi, lo][np128]: the sweep kernel writes a block's errors here
   float* sb_base = sa_base + 4 * np128;      // [2][hi, lo][kp128]
   p.losses = losses;
   cudaStream_t st = (cudaStream_t)stream;
@@ -344,33 +366,45 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
   // updates while the next block is swept.
   bool side_busy = false;
   int blk = 0;
+  auto split_u = [&](int64_t j1, int which, cudaStream_t on) -> int {
+    // hi / lo operand form of U[j1 : j1 + bs, j1 + bs :] (independent of the sweep: kept off its chain)
+    const int bsj = (int)((K - j1) < blocksize ? (K - j1) : blocksize);
+    const int64_t j2 = j1 + bsj;
+    float* hi = sb_base + (size_t)which * 2 * kp128;
+    return tgemm::split_transposed(U + j1 * ldu + j2, ldu, bsj, (int)(K - j2), hi, hi + kp128, on);
+  };
+  if (U && K > blocksize) { rc = split_u(0, 0, st); if (rc) return rc; }
   for (int64_t i1 = 0; i1 < K; i1 += blocksize, ++blk) {
     const int bs = (int)((K - i1) < blocksize ? (K - i1) : blocksize);
+    const int64_t i2 = i1 + bs;
+    const bool trailing = i2 < K && U;
+    float* sa_hi = sa_base + (size_t)(blk & 1) * 2 * np128;
+    float* sa_lo = sa_hi + np128;
     p.i1 = (int)i1; p.bs = bs; p.first = (i1 == 0);
+    p.err_hi = trailing ? sa_hi : nullptr; p.err_lo = trailing ? sa_lo : nullptr;
+    p.lde = tgemm::split_ld(bs);
     kern<<<grid, kCtaThreads, smem, st>>>(p, warps);
     B200Q_LAUNCH_CHECK();
-    const int64_t i2 = i1 + bs;
-    if (i2 < K && U) {
+    if (trailing) {
       // W[:, i2:] -= Err[N, bs] * U[i1:i2, i2:]   (3xTF32 on the tensor cores)
       const int rest = (int)(K - i2);
-      float* sa_hi = sa_base + (size_t)(blk & 1) * 2 * np128;
-      float* sa_lo = sa_hi + np128;
       float* sb_hi = sb_base + (size_t)(blk & 1) * 2 * kp128;
       float* sb_lo = sb_hi + kp128;
       const int64_t ld = tgemm::split_ld(bs);
-      rc = tgemm::split(p.err, p.lde, (int)N, bs, sa_hi, sa_lo, st); if (rc) return rc;
-      rc = tgemm::split_transposed(U + i1 * ldu + i2, ldu, bs, rest, sb_hi, sb_lo, st); if (rc) return rc;
       const tgemm::Split A{sa_hi, sa_lo, ld};
+      const bool more = K - i2 > blocksize;     // the next block has a trailing update too
       if (!side) {
         rc = tgemm::launch(tgemm::kNT, A, tgemm::Split{sb_hi, sb_lo, ld}, Wf + i2, ldf, (int)N, rest, bs, -1.0f, 1.0f,
                            tgemm::kAllTiles, gemm_status, st);
         if (rc) return rc;
+        if (more) { rc = split_u(i2, (blk + 1) & 1, st); if (rc) return rc; }
         continue;
       }
       const int near = rest < 128 ? rest : 128;
       B200Q_TRY(cudaEventRecord(side->ready, st));
       B200Q_TRY(cudaStreamWaitEvent(side->stream, side->ready, 0));
-      if (side_busy) B200Q_TRY(cudaStreamWaitEvent(st, side->done, 0));   // far columns of the block before
+      // the far columns of the block before, and this block's operand form of U made behind them
+      if (side_busy) B200Q_TRY(cudaStreamWaitEvent(st, side->done, 0));
       rc = tgemm::launch(tgemm::kNT, A, tgemm::Split{sb_hi, sb_lo, ld}, Wf + i2, ldf, (int)N, near, bs, -1.0f, 1.0f,
                          tgemm::kAllTiles, gemm_status, st);
       if (rc) return rc;
@@ -379,8 +413,15 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
                            Wf + i2 + near, ldf, (int)N, rest - near, bs, -1.0f, 1.0f, tgemm::kAllTiles, gemm_status,
                            side->stream, 0, kNumSMs - reserve);
         if (rc) return rc;
+        // the next block's slice of U: its buffer was last read by the block before this one
+        // (near part before `ready`, far part earlier on the helper stream)
+        if (more) { rc = split_u(i2, (blk + 1) & 1, side->stream); if (rc) return rc; }
         B200Q_TRY(cudaEventRecord(side->done, side->stream));
         side_busy = true;
+      } else if (more) {
+        // no far part (blocks narrower than the 128 near columns): the helper stream is idle and
+        // was waited for above, the slice is made on the caller's stream
+        rc = split_u(i2, (blk + 1) & 1, st); if (rc) return rc;
       }
     }
   }

@@ -394,11 +394,6 @@ tgemm_kernel(const __grid_constant__ CUtensorMap a_hi, const __grid_constant__ C
 
 // hi = tf32(x) (round to nearest even on 10 mantissa bits), lo = tf32(x - hi); both stored as
 // float32 words whose low 13 mantissa bits are zero.  dst rows are zero-padded to ld_dst.
-__device__ __forceinline__ float tf32_rn(float x) {
-  uint32_t b = __float_as_uint(x);
-  b = (b + 0xFFFu + ((b >> 13) & 1u)) & 0xFFFFE000u;
-  return __uint_as_float(b);
-}
 __global__ void split_kernel(const float* __restrict__ src, int64_t ld_src, int rows, int cols,
                              float* __restrict__ hi, float* __restrict__ lo, int64_t ld_dst) {
   const int64_t total = (int64_t)rows * ld_dst;

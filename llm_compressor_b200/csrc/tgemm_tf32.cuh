@@ -25,6 +25,14 @@ struct Split {       // a split operand: hi / lo arrays with a common leading di
 
 inline int64_t split_ld(int64_t cols) { return (cols + 31) / 32 * 32; }
 
+// One half of an operand split: x rounded to nearest even on 10 mantissa bits, as a float32 word
+// whose low 13 mantissa bits are zero.  hi = tf32_rn(x), lo = tf32_rn(x - hi).
+__device__ __forceinline__ float tf32_rn(float x) {
+  uint32_t b = __float_as_uint(x);
+  b = (b + 0xFFFu + ((b >> 13) & 1u)) & 0xFFFFE000u;
+  return __uint_as_float(b);
+}
+
 // src [rows][cols] -> hi/lo [rows][split_ld(cols)]
 int split(const float* src, int64_t ld_src, int rows, int cols, float* hi, float* lo, cudaStream_t st);
 // src [rows][cols] -> hi/lo [cols][split_ld(rows)]
