@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(kThreads, 2) sweep_fused_kernel(SweepBatch b) 
   float* sW = sU + NB * NB;                // [128 cols][kWLD]: the block's columns of this CTA's rows, then their errors
   __shared__ float s_rd[NB];
   __shared__ int s_grp[NB];
+  __shared__ int s_same[NB / kSub];
   const int job = blockIdx.y;
   float* __restrict__ W = b.W[job];
   const float* __restrict__ U = b.U ? b.U[job] : nullptr;
@@ -120,6 +121,12 @@ __global__ void __launch_bounds__(kThreads, 2) sweep_fused_kernel(SweepBatch b) 
       s_grp[i] = grp;
     }
     __syncthreads();
+    if (threadIdx.x < NB / kSub) {   // does one (scale, zero point) govern the whole sub-block?
+      bool same = true;
+      for (int t = 1; t < kSub; ++t) same = same && s_grp[threadIdx.x * kSub + t] == s_grp[threadIdx.x * kSub];
+      s_same[threadIdx.x] = same ? 1 : 0;
+    }
+    __syncthreads();
     // ---- the block's columns, swept by the row-owning warps (a lane per row)
     if (sweeper) {
       float* myW = sW + warp * 32;
@@ -147,41 +154,58 @@ __global__ void __launch_bounds__(kThreads, 2) sweep_fused_kernel(SweepBatch b) 
 #pragma unroll 1
       for (int sub = 0; sub * kSub < bs; ++sub) {
         const int c0 = sub * kSub;
-        float w[kSub], e[kSub];
+        // parameters of the sub-block's columns, fetched before the dependent chain starts (columns
+        // at or beyond bs are zero columns with a unit pivot: they run through and change nothing)
+        float sv[kSub], rsv[kSub], zv[kSub];
+        if (s_same[sub]) {   // uniform
+          const int grp = s_grp[c0];
+          if (grp != cur_grp) {
+            cur_grp = grp;
+            if (live) {
+              const int64_t pi = pbase + grp;
+              s = Elem<SDT>::load((const typename Elem<SDT>::type*)scale + pi);
+              if (GLOBAL) s = __fdiv_rn(s, g);
+              rs = __frcp_rn(s);
+              if (has_zp) z = load_zp(zp, b.zp_kind, pi);
+            }
+          }
 #pragma unroll
-        for (int t = 0; t < kSub; ++t) w[t] = myW[(c0 + t) * kWLD + lane];
+          for (int t = 0; t < kSub; ++t) { sv[t] = s; rsv[t] = rs; zv[t] = z; }
+        } else {             // act-order: every column may have its own group
+          cur_grp = -1;
+#pragma unroll
+          for (int t = 0; t < kSub; ++t) {
+            float st = 1.0f, zt = 0.0f;
+            if (live) {
+              const int64_t pi = pbase + s_grp[c0 + t];
+              st = Elem<SDT>::load((const typename Elem<SDT>::type*)scale + pi);
+              if (GLOBAL) st = __fdiv_rn(st, g);
+              if (has_zp) zt = load_zp(zp, b.zp_kind, pi);
+            }
+            sv[t] = st; rsv[t] = __frcp_rn(st); zv[t] = zt;
+          }
+        }
+        float w[kSub], e[kSub], rd[kSub];
+#pragma unroll
+        for (int t = 0; t < kSub; ++t) { w[t] = myW[(c0 + t) * kWLD + lane]; rd[t] = s_rd[c0 + t]; }
 #pragma unroll
         for (int t = 0; t < kSub; ++t) {
           const int i = c0 + t;
-          e[t] = 0.0f;
-          if (i < bs) {   // uniform
-            const int grp = s_grp[i];
-            if (grp != cur_grp) {   // uniform
-              cur_grp = grp;
-              if (live) {
-                const int64_t pi = pbase + grp;
-                s = Elem<SDT>::load((const typename Elem<SDT>::type*)scale + pi);
-                if (GLOBAL) s = __fdiv_rn(s, g);
-                rs = __frcp_rn(s);
-                if (has_zp) z = load_zp(zp, b.zp_kind, pi);
-              }
-            }
-            const float wi = w[t];
-            const float q = fake_quant_f32<KIND, SB>(wi, s, rs, z, qmin, qmax);
-            const float diff = __fsub_rn(wi, q);
-            const float tt = __fmul_rn(diff, s_rd[i]);
-            loss = fmaf(tt, tt, loss);
-            e[t] = tt;
-            w[t] = q;
-            const float4* urow = reinterpret_cast<const float4*>(sU + i * NB + c0);
+          const float wi = w[t];
+          const float q = fake_quant_f32<KIND, SB>(wi, sv[t], rsv[t], zv[t], qmin, qmax);
+          const float diff = __fsub_rn(wi, q);
+          const float tt = __fmul_rn(diff, rd[t]);
+          loss = fmaf(tt, tt, loss);
+          e[t] = tt;
+          w[t] = q;
+          const float4* urow = reinterpret_cast<const float4*>(sU + i * NB + c0);
 #pragma unroll
-            for (int k4 = (t + 1) / 4; k4 < kSub / 4; ++k4) {
-              const float4 u = urow[k4];
-              if (4 * k4 + 0 > t) w[4 * k4 + 0] = __fsub_rn(w[4 * k4 + 0], __fmul_rn(tt, u.x));
-              if (4 * k4 + 1 > t) w[4 * k4 + 1] = __fsub_rn(w[4 * k4 + 1], __fmul_rn(tt, u.y));
-              if (4 * k4 + 2 > t) w[4 * k4 + 2] = __fsub_rn(w[4 * k4 + 2], __fmul_rn(tt, u.z));
-              if (4 * k4 + 3 > t) w[4 * k4 + 3] = __fsub_rn(w[4 * k4 + 3], __fmul_rn(tt, u.w));
-            }
+          for (int k4 = (t + 1) / 4; k4 < kSub / 4; ++k4) {
+            const float4 u = urow[k4];
+            if (4 * k4 + 0 > t) w[4 * k4 + 0] = __fsub_rn(w[4 * k4 + 0], __fmul_rn(tt, u.x));
+            if (4 * k4 + 1 > t) w[4 * k4 + 1] = __fsub_rn(w[4 * k4 + 1], __fmul_rn(tt, u.y));
+            if (4 * k4 + 2 > t) w[4 * k4 + 2] = __fsub_rn(w[4 * k4 + 2], __fmul_rn(tt, u.z));
+            if (4 * k4 + 3 > t) w[4 * k4 + 3] = __fsub_rn(w[4 * k4 + 3], __fmul_rn(tt, u.w));
           }
         }
         // the sub-block's columns are final: out to the weight, and their errors take their
@@ -200,20 +224,35 @@ __global__ void __launch_bounds__(kThreads, 2) sweep_fused_kernel(SweepBatch b) 
         }
 #pragma unroll
         for (int t = 0; t < kSub; ++t) myW[(c0 + t) * kWLD + lane] = e[t];
+        // the later columns of the block take this sub-block's corrections: v -= e * u as a packed
+        // product and a packed sum with -e, eight columns (four independent chains) per pass
+        uint64_t ne2[kSub];
+#pragma unroll
+        for (int t = 0; t < kSub; ++t) asm("mov.b64 %0, {%1, %1};" : "=l"(ne2[t]) : "f"(-e[t]));
 #pragma unroll 1
-        for (int c = c0 + kSub; c < bs; c += 4) {
-          float v0 = myW[(c + 0) * kWLD + lane], v1 = myW[(c + 1) * kWLD + lane];
-          float v2 = myW[(c + 2) * kWLD + lane], v3 = myW[(c + 3) * kWLD + lane];
+        for (int c = c0 + kSub; c < bs; c += 8) {
+          uint64_t v[4];
+#pragma unroll
+          for (int h = 0; h < 4; ++h)
+            asm("mov.b64 %0, {%1, %2};" : "=l"(v[h]) : "f"(myW[(c + 2 * h) * kWLD + lane]), "f"(myW[(c + 2 * h + 1) * kWLD + lane]));
 #pragma unroll
           for (int t = 0; t < kSub; ++t) {
-            const float4 u = *reinterpret_cast<const float4*>(sU + (c0 + t) * NB + c);
-            v0 = __fsub_rn(v0, __fmul_rn(e[t], u.x));
-            v1 = __fsub_rn(v1, __fmul_rn(e[t], u.y));
-            v2 = __fsub_rn(v2, __fmul_rn(e[t], u.z));
-            v3 = __fsub_rn(v3, __fmul_rn(e[t], u.w));
+            const ulonglong2 ua = *reinterpret_cast<const ulonglong2*>(sU + (c0 + t) * NB + c);
+            const ulonglong2 ub = *reinterpret_cast<const ulonglong2*>(sU + (c0 + t) * NB + c + 4);
+            const uint64_t u[4] = {ua.x, ua.y, ub.x, ub.y};
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              uint64_t pr;
+              asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(pr) : "l"(ne2[t]), "l"(u[h]));
+              asm("add.rn.f32x2 %0, %1, %2;" : "=l"(v[h]) : "l"(v[h]), "l"(pr));
+            }
           }
-          myW[(c + 0) * kWLD + lane] = v0; myW[(c + 1) * kWLD + lane] = v1;
-          myW[(c + 2) * kWLD + lane] = v2; myW[(c + 3) * kWLD + lane] = v3;
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            float lo, hi;
+            asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v[h]));
+            myW[(c + 2 * h) * kWLD + lane] = lo; myW[(c + 2 * h + 1) * kWLD + lane] = hi;
+          }
         }
       }
     }
