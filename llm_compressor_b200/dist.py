@@ -98,7 +98,8 @@ def broadcast_module_params(modules: Sequence, module_to_rank: dict, names: Sequ
     """Broadcast the named parameters of every module from its owner.  The parameters of one
     owner are packed into byte buckets (one collective per bucket instead of one per tensor: a
     layer of a mixture of experts has more than a thousand small tensors); a tensor larger than a
-    bucket, or not contiguous, goes by itself."""
+    bucket goes by itself.  Which tensor travels in which collective depends on the tensors' sizes
+    only, never on a rank's local memory layout."""
     me = rank()
     by_src: dict = {}
     for m in modules:
@@ -107,41 +108,53 @@ def broadcast_module_params(modules: Sequence, module_to_rank: dict, names: Sequ
             p = getattr(m, name, None)
             if p is not None:
                 by_src.setdefault(src, []).append(p.data)
-    pending, unpack = [], []
+    pending, after = [], []
+
+    def as_bytes(t):
+        return t.contiguous().reshape(-1).view(torch.uint8)      # a copy when t is not contiguous
+
+    def alone(t, src):
+        buf = t if t.is_contiguous() else t.contiguous()
+        pending.append(dist.broadcast(_as_broadcastable(buf), src=src, async_op=True))
+        if buf is not t and me != src:
+            after.append(lambda: t.copy_(buf))
+
+    def packed(bucket, src):
+        offsets, total = [], 0
+        for t in bucket:
+            offsets.append(total)
+            total += (t.numel() * t.element_size() + 15) // 16 * 16
+        buf = torch.empty(total, dtype=torch.uint8, device=bucket[0].device)
+        views = [buf[o: o + t.numel() * t.element_size()] for o, t in zip(offsets, bucket)]
+        if me == src:
+            torch._foreach_copy_(views, [as_bytes(t) for t in bucket])
+        pending.append(dist.broadcast(buf, src=src, async_op=True))
+        if me != src:
+            def unpack():
+                dense = [(t, v) for t, v in zip(bucket, views) if t.is_contiguous()]
+                if dense:
+                    torch._foreach_copy_([as_bytes(t) for t, _ in dense], [v for _, v in dense])
+                for t, v in zip(bucket, views):
+                    if not t.is_contiguous():
+                        t.copy_(v.view(t.dtype).view(t.shape))
+            after.append(unpack)
+
     for src in sorted(by_src):
         bucket, size = [], 0
-
-        def flush():
-            nonlocal bucket, size
-            if not bucket:
-                return
-            if len(bucket) == 1:
-                pending.append(dist.broadcast(_as_broadcastable(bucket[0]), src=src, async_op=True))
-            else:
-                offsets, total = [], 0
-                for t in bucket:
-                    offsets.append(total)
-                    total += (t.numel() * t.element_size() + 15) // 16 * 16
-                buf = torch.empty(total, dtype=torch.uint8, device=bucket[0].device)
-                views = [buf[o: o + t.numel() * t.element_size()] for o, t in zip(offsets, bucket)]
-                if me == src:
-                    torch._foreach_copy_(views, [t.reshape(-1).view(torch.uint8) for t in bucket])
-                pending.append(dist.broadcast(buf, src=src, async_op=True))
-                if me != src:
-                    unpack.append((bucket, views))
-            bucket, size = [], 0
-
         for t in by_src[src]:
             nbytes = t.numel() * t.element_size()
-            if not t.is_contiguous() or nbytes > _BUCKET_BYTES or nbytes == 0:
-                if nbytes:
-                    pending.append(dist.broadcast(_as_broadcastable(t), src=src, async_op=True))
+            if nbytes == 0:
                 continue
-            if size + nbytes > _BUCKET_BYTES:
-                flush()
+            if nbytes > _BUCKET_BYTES:
+                alone(t, src)
+                continue
+            if size + nbytes > _BUCKET_BYTES and bucket:
+                (alone(bucket[0], src) if len(bucket) == 1 else packed(bucket, src))
+                bucket, size = [], 0
             bucket.append(t)
             size += nbytes
-        flush()
+        if bucket:
+            (alone(bucket[0], src) if len(bucket) == 1 else packed(bucket, src))
     wait_for_comms(pending)
-    for tensors, views in unpack:
-        torch._foreach_copy_([t.reshape(-1).view(torch.uint8) for t in tensors], views)
+    for fn in after:
+        fn()

@@ -134,6 +134,34 @@ def _worker(rank, world, port, q):
         lin.weight.data.fill_(float(rank + 5))
         lin.weight_scale = torch.nn.Parameter(torch.full((4, 1), float(rank)), requires_grad=False)
         bdist.broadcast_module_params([lin], {lin: 1}, ("weight", "weight_scale", "weight_g_idx"))
+        # many tensors of two owners, mixed dtypes (float8 travels as bytes), one non-contiguous, and a
+        # bucket limit small enough to need several buckets per owner
+        g = torch.Generator().manual_seed(7)
+        mods, owner = [], {}
+        for i in range(6):
+            m = torch.nn.Module()
+            src = torch.randn(5, 3 + i, generator=g)
+            m.weight = torch.nn.Parameter((src if rank == i % 2 else torch.zeros_like(src)).to(torch.bfloat16),
+                                          requires_grad=False)
+            sc = torch.rand(5, 1, generator=g) + 0.5
+            m.weight_scale = torch.nn.Parameter(sc if rank == i % 2 else torch.zeros_like(sc), requires_grad=False)
+            zp = (torch.rand(5, 1, generator=g) * 4).to(torch.float8_e4m3fn)
+            m.weight_zero_point = torch.nn.Parameter(zp if rank == i % 2 else torch.zeros_like(zp), requires_grad=False)
+            gi = torch.arange(2 * (3 + i), dtype=torch.int32)[::2]          # not contiguous
+            m.weight_g_idx = torch.nn.Parameter(gi if rank == i % 2 else torch.zeros_like(gi), requires_grad=False)
+            m.expect = (src.to(torch.bfloat16), sc, zp, gi.clone())
+            mods.append(m)
+            owner[m] = i % 2
+        old_limit, bdist._BUCKET_BYTES = bdist._BUCKET_BYTES, 96
+        try:
+            bdist.broadcast_module_params(mods, owner, ("weight", "weight_scale", "weight_zero_point", "weight_g_idx"))
+        finally:
+            bdist._BUCKET_BYTES = old_limit
+        for m in mods:
+            w, sc, zp, gi = m.expect
+            assert torch.equal(m.weight.data, w) and torch.equal(m.weight_scale.data, sc)
+            assert torch.equal(m.weight_zero_point.data.view(torch.uint8), zp.view(torch.uint8))
+            assert torch.equal(m.weight_g_idx.data, gi)
         q.put((rank, res, float(lin.weight[0, 0]), float(lin.weight_scale[0, 0])))
     finally:
         torch.distributed.destroy_process_group()
