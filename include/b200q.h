@@ -304,6 +304,17 @@ int b200q_gptq_sweep(float* Wf, int64_t N, int64_t K, int64_t ldf, const float* 
  * rows of one weight through every column block, trailing updates included (float32 FMA).
  * U may be NULL (identity for all) and so may zp, col_group and global_scale (absent for all);
  * losses[i]: float [N]. */
+/* The gather / scatter around the batched sweep, for `count` weights of one shape (device arrays
+ * of device pointers): Wf[i] = float32 copy of W[i] with its columns permuted by perm[i] (perm
+ * NULL: identity for all) and the columns whose dead_diag[i][c] is 0 zeroed (dead_diag NULL: none),
+ * as b200q_gather_columns_f32 followed by b200q_gptq_zero_dead_columns; and the way back,
+ * out[i][:, perm[i][c]] = cast(Wf[i][:, c]), as b200q_scatter_columns_cast. */
+int b200q_gather_columns_f32_batched(const void* const* W, int wdtype, const int32_t* const* perm,
+                                     const float* const* dead_diag, float* const* Wf, int count, int64_t N,
+                                     int64_t K, int64_t ldw, int64_t ldf, void* stream);
+int b200q_scatter_columns_cast_batched(const float* const* Wf, const int32_t* const* perm, void* const* out,
+                                       int odtype, int count, int64_t N, int64_t K, int64_t ldf, int64_t ldo,
+                                       void* stream);
 size_t b200q_gptq_factor_batched_workspace_bytes(int64_t K, int count);
 int b200q_gptq_factor_batched(float* const* H, float* const* scratch, int count, int64_t K, int64_t ldh,
                               int* status, void* stream);

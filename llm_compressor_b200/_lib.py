@@ -81,6 +81,8 @@ SIGNATURES = {
     "b200q_gptq_sweep": (_i, [_p, _i64, _i64, _i64, _p, _i64, _p, _i, _p, _p, _p, _qa, _i, _p, _p, _p]),
     "b200q_gptq_factor_batched_workspace_bytes": (C.c_size_t, [_i64, _i]),
     "b200q_gptq_factor_batched": (_i, [_p, _p, _i, _i64, _i64, _p, _p]),
+    "b200q_gather_columns_f32_batched": (_i, [_p, _i, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _p]),
+    "b200q_scatter_columns_cast_batched": (_i, [_p, _p, _p, _i, _i, _i64, _i64, _i64, _i64, _p]),
     "b200q_gptq_sweep_batched": (_i, [_p, _p, _p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _qa, _i, _p]),
 }
 

@@ -74,6 +74,47 @@ __global__ void gather_cols_kernel(const void* __restrict__ W, int64_t N, int64_
   }
 }
 
+// Batched forms for many weights of one shape (device arrays of pointers, blockIdx.y = problem):
+// the gather also zeroes the columns whose Hessian diagonal entry (after the permutation) is zero.
+template <int DT>
+__global__ void gather_cols_batched_kernel(const void* const* __restrict__ W, int64_t N, int64_t K, int64_t ldw,
+                                           const int32_t* const* __restrict__ perm,
+                                           const float* const* __restrict__ diag, float* const* __restrict__ out,
+                                           int64_t ldo) {
+  using E = Elem<DT>;
+  const int j = blockIdx.y;
+  const typename E::type* w = (const typename E::type*)W[j];
+  const int32_t* pm = perm ? perm[j] : nullptr;
+  const float* dg = diag ? diag[j] : nullptr;
+  float* o = out[j];
+  const int64_t total = N * K;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / K, c = i - r * K;
+    const int64_t src = pm ? perm_at(pm, c, K) : c;
+    const bool dead = dg && dg[c] == 0.0f;
+    o[r * ldo + c] = dead ? 0.0f : E::load(w + r * ldw + src);
+  }
+}
+
+template <int DT>
+__global__ void scatter_cols_batched_kernel(const float* const* __restrict__ Wf, int64_t N, int64_t K, int64_t ldf,
+                                            const int32_t* const* __restrict__ perm, void* const* __restrict__ out,
+                                            int64_t ldo) {
+  using E = Elem<DT>;
+  const int j = blockIdx.y;
+  const float* wf = Wf[j];
+  const int32_t* pm = perm ? perm[j] : nullptr;
+  typename E::type* o = (typename E::type*)out[j];
+  const int64_t total = N * K;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / K, c = i - r * K;
+    const int64_t dst = pm ? perm_at(pm, c, K) : c;
+    E::store(o + r * ldo + dst, wf[r * ldf + c]);
+  }
+}
+
 __global__ void permute_hessian_kernel(const float* __restrict__ H, int64_t K, int64_t ldh,
                                        const int32_t* __restrict__ perm, float* __restrict__ out,
                                        int64_t ldo) {
@@ -548,6 +589,38 @@ int b200q_scatter_columns_cast(const float* Wf, int64_t N, int64_t K, int64_t ld
   cudaStream_t st = (cudaStream_t)stream;
   if (odtype == B200Q_BF16) scatter_cols_kernel<B200Q_BF16><<<grid, 256, 0, st>>>(Wf, N, K, ldf, perm, out, ldo);
   else if (odtype == B200Q_F32) scatter_cols_kernel<B200Q_F32><<<grid, 256, 0, st>>>(Wf, N, K, ldf, perm, out, ldo);
+  else return B200Q_ERR_UNSUPPORTED;
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_gather_columns_f32_batched(const void* const* W, int wdtype, const int32_t* const* perm,
+                                     const float* const* dead_diag, float* const* Wf, int count, int64_t N,
+                                     int64_t K, int64_t ldw, int64_t ldf, void* stream) {
+  if (!W || !Wf || count <= 0 || count > 65535 || N <= 0 || K <= 0 || ldw < K || ldf < K) return B200Q_ERR_ARG;
+  int gx = grid_for((N * K + 255) / 256, 8);
+  const int cap = 8 * kNumSMs / count + 1;          // enough blocks over all problems to fill the machine
+  if (gx > cap) gx = cap;
+  dim3 grid((unsigned)gx, (unsigned)count, 1);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (wdtype == B200Q_BF16) gather_cols_batched_kernel<B200Q_BF16><<<grid, 256, 0, st>>>(W, N, K, ldw, perm, dead_diag, Wf, ldf);
+  else if (wdtype == B200Q_F32) gather_cols_batched_kernel<B200Q_F32><<<grid, 256, 0, st>>>(W, N, K, ldw, perm, dead_diag, Wf, ldf);
+  else return B200Q_ERR_UNSUPPORTED;
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_scatter_columns_cast_batched(const float* const* Wf, const int32_t* const* perm, void* const* out,
+                                       int odtype, int count, int64_t N, int64_t K, int64_t ldf, int64_t ldo,
+                                       void* stream) {
+  if (!Wf || !out || count <= 0 || count > 65535 || N <= 0 || K <= 0 || ldf < K || ldo < K) return B200Q_ERR_ARG;
+  int gx = grid_for((N * K + 255) / 256, 8);
+  const int cap = 8 * kNumSMs / count + 1;
+  if (gx > cap) gx = cap;
+  dim3 grid((unsigned)gx, (unsigned)count, 1);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (odtype == B200Q_BF16) scatter_cols_batched_kernel<B200Q_BF16><<<grid, 256, 0, st>>>(Wf, N, K, ldf, perm, out, ldo);
+  else if (odtype == B200Q_F32) scatter_cols_batched_kernel<B200Q_F32><<<grid, 256, 0, st>>>(Wf, N, K, ldf, perm, out, ldo);
   else return B200Q_ERR_UNSUPPORTED;
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;

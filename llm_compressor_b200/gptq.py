@@ -189,7 +189,9 @@ class _SweepInput:
     final_dtype: torch.dtype
 
 
-def _sweep_input(module, quant_args, hessian, percdamp, factor) -> _SweepInput:
+def _sweep_input(module, quant_args, hessian, percdamp, factor, W=None) -> _SweepInput:
+    """``W``: the float32 copy of the weight, already permuted and with its dead columns zeroed (the
+    batched path makes it for all modules at once); made here when not given."""
     args = QuantizationArgs.of(quant_args)
     strategy, actorder = args.strategy, args.actorder
     weight = module.weight.data if isinstance(module.weight, torch.nn.Parameter) else module.weight
@@ -211,7 +213,9 @@ def _sweep_input(module, quant_args, hessian, percdamp, factor) -> _SweepInput:
         raise ValueError("factor does not match this module / act-order setting")
     perm = factor.perm
 
-    W = ops.gather_columns_f32(weight, perm)
+    prepared = W is not None
+    if not prepared:
+        W = ops.gather_columns_f32(weight, perm)
 
     if actorder == "group":
         observer.delete_statistics(check_fused=False)
@@ -229,15 +233,17 @@ def _sweep_input(module, quant_args, hessian, percdamp, factor) -> _SweepInput:
             col_group = g_idx
 
     qparams = observer.get_qparams()
-    ops.gptq_zero_dead_columns(factor.diag, W)
+    if not prepared:
+        ops.gptq_zero_dead_columns(factor.diag, W)
     return _SweepInput(args, actorder, factor, W, qparams["scale"], qparams["zero_point"], qparams["global_scale"],
                        col_group, g_idx, weight.dtype)
 
 
-def _sweep_output(inp: _SweepInput) -> dict:
+def _sweep_output(inp: _SweepInput, weight=None) -> dict:
+    """``weight``: the swept weight already scattered back and cast (batched path)."""
     perm = inp.factor.perm
     out = {
-        "weight": ops.scatter_columns_cast(inp.W, inp.final_dtype, perm),
+        "weight": weight if weight is not None else ops.scatter_columns_cast(inp.W, inp.final_dtype, perm),
         "weight_scale": inp.scale.to(inp.final_dtype),
         "weight_zero_point": inp.zero_point.to(inp.args.zp_dtype),
     }
@@ -290,7 +296,14 @@ def quantize_weights_batched(modules, quant_args, factors, blocksize: int = 128,
     device tensors and the dicts carry no ``"_status"`` (the batched sweep has no bounded wait).
     As with the deferred single call, the caller resolves the factors afterwards and redoes the
     modules whose factorisation failed."""
-    inputs = [_sweep_input(m, quant_args, None, percdamp, f) for m, f in zip(modules, factors)]
+    weights = [m.weight.data if isinstance(m.weight, torch.nn.Parameter) else m.weight for m in modules]
+    perms = [f.perm for f in factors]
+    if any((p is None) != (perms[0] is None) for p in perms):
+        raise ValueError("the factors of a batch must all carry a permutation or none")
+    # one launch: float32 copies, permuted, dead columns zeroed
+    Wf = ops.gather_columns_f32_batched(weights, None if perms[0] is None else perms, [f.diag for f in factors])
+    inputs = [_sweep_input(m, quant_args, None, percdamp, f, W=Wf[k])
+              for k, (m, f) in enumerate(zip(modules, factors))]
     first = inputs[0]
 
     def column(name):
@@ -303,4 +316,6 @@ def quantize_weights_batched(modules, quant_args, factors, blocksize: int = 128,
                                     column("zero_point"), first.args, col_groups=column("col_group"),
                                     global_scales=column("global_scale"), blocksize=blocksize)
     sums = losses.sum(dim=1)
-    return [(sums[k], _sweep_output(i)) for k, i in enumerate(inputs)]
+    back = ops.scatter_columns_cast_batched([i.W for i in inputs], first.final_dtype,
+                                            None if perms[0] is None else perms)
+    return [(sums[k], _sweep_output(i, weight=back[k])) for k, i in enumerate(inputs)]

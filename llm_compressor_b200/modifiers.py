@@ -700,6 +700,10 @@ class GPTQModifier(QuantizationMixin):
             values = torch.stack([results[i][1].reshape(()) for i in on_device]).tolist()
             for i, v in zip(on_device, values):
                 results[i] = (results[i][0], v, results[i][2])
+        # the weights go back in one multi-tensor copy
+        if results:
+            torch._foreach_copy_([module.weight.data for module, _, _ in results],
+                                 [out["weight"] for _, _, out in results])
         for module, loss, out in results:
             loss = float(loss)
             name = self._module_names.get(module, type(module).__name__)
@@ -707,7 +711,7 @@ class GPTQModifier(QuantizationMixin):
             self._log_metric(name, time.perf_counter() - t0, loss)
             for attr, val in out.items():
                 if attr == "weight":
-                    module.weight.data.copy_(val)
+                    continue
                 elif hasattr(module, attr):
                     p = getattr(module, attr)
                     val = val.reshape(p.shape)

@@ -439,6 +439,46 @@ def gptq_factor_batched(Hs) -> torch.Tensor:
     return status
 
 
+def gather_columns_f32_batched(ws, perms=None, dead_diags=None) -> torch.Tensor:
+    """float32 copies [count, N, K] of weights of one shape, columns permuted by ``perms[i]`` and the
+    columns with ``dead_diags[i][c] == 0`` zeroed, in one launch (either list may be None)."""
+    count = len(ws)
+    N, K, ld = _2d(ws[0])
+    for w in ws:
+        if _2d(w) != (N, K, ld) or w.dtype != ws[0].dtype:
+            raise ValueError("batched gather needs weights of one shape, layout and dtype")
+    _need_cuda(*ws)
+    out = torch.empty((count, N, K), dtype=torch.float32, device=ws[0].device)
+    if perms is not None:
+        perms = [p.to(torch.int32).contiguous() for p in perms]
+    if dead_diags is not None:
+        dead_diags = [d.to(torch.float32).contiguous() for d in dead_diags]
+    table = _pointer_table([ws, perms, dead_diags, list(out.unbind(0))])
+    check(_lib.load().b200q_gather_columns_f32_batched(
+        ptr(table[0]), _dt(ws[0]), ptr(table[1]) if perms is not None else None,
+        ptr(table[2]) if dead_diags is not None else None, ptr(table[3]), count, N, K, ld, K, stream_ptr()),
+        "b200q_gather_columns_f32_batched")
+    return out
+
+
+def scatter_columns_cast_batched(wfs, dtype: torch.dtype, perms=None) -> torch.Tensor:
+    """The way back: [count, N, K] in ``dtype`` with ``out[i][:, perms[i][c]] = wfs[i][:, c]``."""
+    count = len(wfs)
+    N, K, ld = _2d(wfs[0])
+    for w in wfs:
+        if _2d(w) != (N, K, ld) or w.dtype != torch.float32:
+            raise ValueError("batched scatter needs float32 matrices of one shape and layout")
+    _need_cuda(*wfs)
+    out = torch.empty((count, N, K), dtype=dtype, device=wfs[0].device)
+    if perms is not None:
+        perms = [p.to(torch.int32).contiguous() for p in perms]
+    table = _pointer_table([wfs, perms, list(out.unbind(0))])
+    check(_lib.load().b200q_scatter_columns_cast_batched(
+        ptr(table[0]), ptr(table[1]) if perms is not None else None, ptr(table[2]), _DT[dtype], count, N, K, ld, K,
+        stream_ptr()), "b200q_scatter_columns_cast_batched")
+    return out
+
+
 def gptq_sweep_batched(wfs, Us, scales, zps, args: QuantizationArgs, col_groups=None, global_scales=None,
                        blocksize=128) -> torch.Tensor:
     """The column sweep, in place, on a list of float32 weights of one shape that share the
