@@ -41,15 +41,16 @@ GROUP_K = {"attn_in": HIDDEN, "o_in": HIDDEN, "mlp_in": HIDDEN, "down_in": INTER
 
 
 # DRAM traffic of one rank-k update launch (dram__bytes_read.sum + dram__bytes_write.sum of ncu
-# captures): 620 MB at K = 4096 (32768 tokens); 6.7 GB at K = 14336 with 16384 tokens, i.e. about
-# 12.6 GB with the 32768 tokens a launch of the layer step holds (the re-read X panels scale with the
-# tokens, the 0.8 GB of H does not).  A step runs 96 launches of width 4096 and 32 of width 14336.
+# captures at the launch sizes of the layer step, 32768 tokens): 620 MB at K = 4096, 10.3 GB at
+# K = 14336 (four token splits per tile: 8.7 GB read, 1.6 GB written).  A step runs 96 launches of
+# width 4096 and 32 of width 14336.
 SYRK_TRAFFIC = {
-    "K4096": 0.62e9, "K14336": 12.6e9,
-    "per_launch_weighted": (96 * 0.62e9 + 32 * 12.6e9) / 128,
+    "K4096": 0.62e9, "K14336": 10.3e9,
+    "per_launch_weighted": (96 * 0.62e9 + 32 * 10.3e9) / 128,
     "note": "mean bytes per launch over a step's 96 K=4096 launches (0.62e9 each, algorithmic 0.34e9) and 32 "
-            "K=14336 launches (12.6e9 each, scaled from a 16384-token capture; algorithmic 1.76e9): X panels are "
-            "re-read by every band of 8 block rows; DRAM stays at 19-32 % of its peak, the kernel is tensor bound",
+            "K=14336 launches (10.3e9 each, algorithmic 1.76e9): X panels are re-read by every band of 8 block "
+            "rows and the partial tiles of the four token splits are added into H; DRAM stays at 19-27 % of its "
+            "peak, the kernel is tensor bound",
 }
 
 
