@@ -628,7 +628,6 @@ def run_oneshot_arm(rank, world, dev, seqs, batch_size):
     from transformers import LlamaConfig, LlamaForCausalLM
 
     from llm_compressor_b200 import GPTQModifier, oneshot
-    from llm_compressor_b200.oneshot import compressed_state_dict  # noqa: F401  (pack is timed below)
     from llm_compressor_b200 import compressors
 
     cfg = LlamaConfig(hidden_size=HIDDEN, intermediate_size=INTER, num_hidden_layers=LAYERS, num_attention_heads=32,

@@ -12,7 +12,7 @@ from __future__ import annotations
 import json
 import os
 import re
-from typing import Iterable, Optional
+from typing import Optional
 
 import torch
 
