@@ -212,8 +212,9 @@ int b200q_hessian_finalize(float* H, int64_t K, int64_t ldh, float scale, void* 
 /* b200q_hessian_syrk splits long token ranges over several thread blocks per tile and adds the
  * partial tiles with floating-point atomics: H is then reproducible to rounding error (about 1e-7
  * relative), not bit for bit, and a GPTQ solve on it may differ in a few codes from run to run.
- * b200q_set_reproducible(1) makes every later call accumulate each tile in one place (bitwise
- * reproducible results for equal inputs and call sequences; slower for narrow Hessians).  Process-wide. */
+ * b200q_set_reproducible(1) makes every later call give whole tiles to a thread-block pair, which
+ * adds the token splits of its tile one after the other without atomics (bitwise reproducible
+ * results for equal inputs and call sequences; slower for narrow Hessians).  Process-wide. */
 void b200q_set_reproducible(int on);
 int b200q_get_reproducible(void);
 

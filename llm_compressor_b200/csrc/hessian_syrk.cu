@@ -172,6 +172,8 @@ struct Params {
   int nb;                    // block rows of the tile grid
   int splits;
   int64_t tokens_per_split;  // multiple of kBlockT
+  int tile_major;            // pair kernel: a CTA pair takes whole tiles, all token splits of a tile one after
+                             // the other, and adds them into H without atomics (bitwise reproducible)
   float alpha;
   int* status;
 };
@@ -456,6 +458,21 @@ __device__ __forceinline__ void decode_pair_tile(int idx, int nb, int& bi, int& 
   }
 }
 
+// The i-th unit (tile, token split) of a CTA pair.  Default: units are dealt out round robin over
+// all pairs, split-major (the splits of a tile land on different pairs and meet in H through
+// atomics).  tile_major: a pair owns whole tiles.
+__device__ __forceinline__ bool pair_unit(const Params& p, int pair, int num_pairs, int i, int& tile, int& split) {
+  if (p.tile_major) {
+    tile = pair + (i / p.splits) * num_pairs;
+    split = i % p.splits;
+    return tile < p.tiles;
+  }
+  const int u = pair + i * num_pairs;
+  tile = u % p.tiles;
+  split = u / p.tiles;
+  return u < p.tiles * p.splits;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 syrk_pair_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
   extern __shared__ unsigned char smem_raw[];
@@ -502,10 +519,10 @@ syrk_pair_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int u = pair; u < total_units && ok; u += num_pairs) {
+      int tile, split;
+      for (int i = 0; ok && pair_unit(p, pair, num_pairs, i, tile, split); ++i) {
         int bi, bj;
-        decode_pair_tile(u % p.tiles, p.nb, bi, bj);
-        const int split = u / p.tiles;
+        decode_pair_tile(tile, p.nb, bi, bj);
         const int64_t t_begin = (int64_t)split * p.tokens_per_split;
         const int64_t t_end = min(p.T, t_begin + p.tokens_per_split);
         const int iters = (int)((t_end - t_begin + kBlockT - 1) / kBlockT);
@@ -532,8 +549,8 @@ syrk_pair_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int u = pair; u < total_units && ok; u += num_pairs, ++local) {
-        const int split = u / p.tiles;
+      int tile, split;
+      for (; ok && pair_unit(p, pair, num_pairs, local, tile, split); ++local) {
         const int64_t t_begin = (int64_t)split * p.tokens_per_split;
         const int64_t t_end = min(p.T, t_begin + p.tokens_per_split);
         const int iters = (int)((t_end - t_begin + kBlockT - 1) / kBlockT);
@@ -569,10 +586,10 @@ syrk_pair_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
     const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;
     int local = 0;
     bool ok = true;
-    for (int u = pair; u < total_units && ok; u += num_pairs, ++local) {
+    int tile, split;
+    for (; ok && pair_unit(p, pair, num_pairs, local, tile, split); ++local) {
       int bi, bj;
-      decode_pair_tile(u % p.tiles, p.nb, bi, bj);
-      const int split = u / p.tiles;
+      decode_pair_tile(tile, p.nb, bi, bj);
       const int64_t t_begin = (int64_t)split * p.tokens_per_split;
       const int64_t t_end = min(p.T, t_begin + p.tokens_per_split);
       if (t_end <= t_begin) continue;
@@ -596,7 +613,7 @@ syrk_pair_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
         __syncwarp();
         const int cc = col0 + sub_col;
         if (cc < p.K) {
-          if (p.splits > 1) {
+          if (p.splits > 1 && !p.tile_major) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int lr = i * 4 + sub_row, row = row0 + lr;
@@ -743,8 +760,9 @@ static int pair_capacity() {
 using namespace b200q;
 
 // Token splits add their partial tiles with floating-point atomics, whose order varies from run to
-// run (H then differs in its last bits).  With this flag set every tile is accumulated by one CTA
-// (pair) over all tokens: bitwise reproducible, slower when the tiles alone do not fill the GPU.
+// run (H then differs in its last bits).  With this flag set a CTA pair owns whole tiles and adds
+// the token splits of a tile one after the other without atomics: bitwise reproducible, the
+// accumulation chains bounded all the same, slower when the tiles alone do not fill the GPU.
 static std::atomic<int> g_reproducible{0};
 
 static int64_t max_chain_tokens() {
@@ -784,6 +802,7 @@ int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* 
 
   Params p;
   p.H = H; p.ldh = ldh; p.K = (int)K; p.T = T; p.alpha = alpha; p.status = status;
+  p.tile_major = 0;
   cudaStream_t st = (cudaStream_t)stream;
   const int pairs = pair_capacity();
   if (pairs > 0) {
@@ -805,10 +824,19 @@ int b200q_hessian_syrk(const void* X, int64_t T, int64_t K, int64_t ldx, float* 
       const int64_t need = (T + max_chain_tokens() - 1) / max_chain_tokens();
       if (best < need) best = (int)(need < 64 ? need : 64);
     }
-    p.splits = g_reproducible.load(std::memory_order_relaxed) ? 1 : best;
+    p.tile_major = g_reproducible.load(std::memory_order_relaxed) ? 1 : 0;
+    if (p.tile_major) {
+      // whole tiles per pair: the splits only bound the accumulation chains
+      const int64_t need = (T + max_chain_tokens() - 1) / max_chain_tokens();
+      best = (int)(need < 1 ? 1 : (need > 64 ? 64 : need));
+    }
+    p.splits = best;
     const int64_t tps = (T + p.splits - 1) / p.splits;
     p.tokens_per_split = ((tps + kBlockT - 1) / kBlockT) * kBlockT;
-    const int64_t units = (int64_t)p.tiles * p.splits;
+    // rounding the split length up can leave the last split empty; in tile-major order an empty
+    // unit would sit between used ones and upset the alternation of the two accumulators
+    if (p.tile_major) p.splits = (int)((T + p.tokens_per_split - 1) / p.tokens_per_split);
+    const int64_t units = p.tile_major ? (int64_t)p.tiles : (int64_t)p.tiles * p.splits;   // pairs that get work
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * (units < pairs ? units : pairs)), 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
