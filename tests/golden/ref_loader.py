@@ -17,8 +17,11 @@ import types
 
 os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
 
-# the llm-compressor checkout to load; fixture generation and the plug-in test need it set
-REF_ROOT = os.environ.get("LLMC_REFERENCE_ROOT", "")
+# the llm-compressor checkout to load (fixture generation and the plug-in test need one):
+# LLMC_REFERENCE_ROOT, else a checkout named "reference" next to this repository if there is one
+_SIBLING = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference"))
+REF_ROOT = os.environ.get("LLMC_REFERENCE_ROOT", "") or (
+    _SIBLING if os.path.isdir(os.path.join(_SIBLING, "src", "llmcompressor")) else "")
 
 
 def reference_available() -> bool:

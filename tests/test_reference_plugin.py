@@ -2,7 +2,8 @@
 REFERENCE's observer registry and driven through the reference's own ``Observer.forward`` ->
 ``flatten_for_calibration`` -> ``update_statistics_from_observed`` -> ``get_qparams`` chain.
 
-Runs where an llm-compressor checkout is available (LLMC_REFERENCE_ROOT).  There is no GPU there,
+Runs where an llm-compressor checkout is available (LLMC_REFERENCE_ROOT, or a checkout named
+"reference" next to the repository).  There is no GPU there,
 so the two kernel calls are stood in for by the CPU oracle: what is under test is the seam - the
 registration, the shapes handed to the kernels for every strategy, and that the reference's
 qparams come out identical to its own observers'."""
